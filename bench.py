@@ -1,0 +1,286 @@
+"""Benchmark of the quantized decode matmul path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+A "step" is one pass over every weight matmul of a Llama-8B-shaped decoder (32 layers
+x {q,k,v,o,gate,up,down} + LM head, int4 / group 32, binary16 scales) for a batch of B
+token rows: 4.22 GB of packed weights stream from HBM once per step, which makes the
+inputs larger than L2 by construction (no flush needed).  With N > 1 (launched by
+torch.distributed.run, one rank per GPU) the matmuls are tensor-parallel, column- then
+row-sharded with an all-reduce after each row-parallel matmul; the total work is fixed,
+so scaling is "strong".
+
+Prints ONE JSON line.  `value` is tok/s with inputs resident in HBM (device-timed);
+`e2e` is the same metric through host buffers (x copied in, logits copied out every
+step); `roofline` relates the GEMV kernel's algorithmic bytes to its measured time;
+`cpu_baseline` is the CPU oracle (the reference's shader arithmetic restated in C)
+timed on this machine's host cores on a bounded sample.
+
+`--impl reference` times that CPU restatement alone.  The reference's own WGSL path
+needs Deno + a WebGPU adapter, neither of which exists on these machines.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return json.load(open(path)), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.lines = []
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [l.split(", ") for t, l in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l.split(", ") for _, l in self.lines]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.strip().lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(batch: int, threads: int, steps: int):
+    """Times the CPU restatement of the shader arithmetic (f32, sequential K, one f32
+    multiply per weight for the dequant) on full decode steps: one layer's seven matmuls
+    run 32 times (the same host weights stand in for every layer) plus the LM head.
+    Returns (tok/s, seconds per step, sample description, threads used)."""
+    import oracle
+    from karume_b200.decode_step import DecodeConfig, synth_weight
+    cfg = DecodeConfig()
+    rng = np.random.default_rng(0)
+    mats = []
+    for _, k, n, _ in cfg.layer_matmuls() + [("lm_head", cfg.hidden, cfg.vocab, "col")]:
+        payload, scale = synth_weight(rng, n, k)
+        x = rng.standard_normal((batch, k)).astype(np.float32)
+        mats.append((x, payload, scale.astype(np.float32), np.zeros(n, np.float32), n, k))
+    cores = threads if threads > 0 else oracle.max_threads()
+    oracle.linear_i4(*mats[1][:4], mats[1][4], mats[1][5], 32, threads, f64=False)  # warm the thread pool
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        for _layer in range(cfg.layers):
+            for x, payload, scale, bias, n, k in mats[:-1]:
+                oracle.linear_i4(x, payload, scale, bias, n, k, 32, threads, f64=False)
+        x, payload, scale, bias, n, k = mats[-1]
+        oracle.linear_i4(x, payload, scale, bias, n, k, 32, threads, f64=False)
+        times.append(time.perf_counter() - t0)
+    step_s = float(np.median(times))
+    desc = (f"{steps} full decode steps (32 x 7 layer matmuls + lm_head, 7505M weights each; one layer's host "
+            f"weights reused for all 32 layers) on {cores} threads, f32 sequential-K shader arithmetic")
+    return batch / step_s, step_s, desc, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from karume_b200.decode_step import DecodeConfig
+    cfg = DecodeConfig()
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    import oracle
+    oracle.build()
+    if warm:
+        cpu_sample(args.batch, 0, 1)
+    tok_s, step_s, desc, cores = cpu_sample(args.batch, 0, min(steps, 20))
+    line = {
+        "impl": "reference", "metric": "decode_matmul_tok_per_s", "value": tok_s, "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": step_s * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"{cfg.name}: 32 layers x (q,k,v,o,gate,up,down) + lm_head, int4 g32, fp16 scales, batch {args.batch}",
+                   "batch": args.batch, "note": "CPU restatement of the reference's WGSL arithmetic (Deno/WebGPU unavailable on this box)"},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_cuda(args):
+    import torch
+    import torch.distributed as dist
+
+    import karume_b200 as kb
+    from karume_b200.decode_step import DecodeConfig, DecodeStep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = DecodeConfig()
+    gpu = kb.acquire_gpu(local)
+    step = DecodeStep(gpu, cfg, args.batch, rank=rank, world=world, seed=0)
+    step.record()
+    rng = np.random.default_rng(1)
+    step.host_x[...] = rng.standard_normal(step.host_x.shape).astype(np.float32)
+    step.x.copy_(torch.from_numpy(step.host_x.copy()))
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(run, steps):
+        ev0 = torch.cuda.Event(enable_timing=True)
+        ev1 = torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(step._stream):
+            ev0.record()
+        for _ in range(steps):
+            run()
+        with torch.cuda.stream(step._stream):
+            ev1.record()
+        step.sync()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    warm = max(3, args.warmup)
+    for _ in range(warm):
+        step.run_device()
+        step.run_host()
+    step.sync()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    t0 = time.time()
+    launches_before = gpu.launch_count
+    ms_dev = timed(step.run_device, args.steps)
+    launches = gpu.launch_count - launches_before
+    ms_e2e = timed(step.run_host, args.steps)
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+
+    logits_ok = bool(np.all(np.isfinite(step.host_logits)))
+    per_step_ms = ms_dev / args.steps
+    per_step_e2e = ms_e2e / args.steps
+    tok_s = args.batch / (per_step_ms * 1e-3)
+    tok_s_e2e = args.batch / (per_step_e2e * 1e-3)
+
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        bytes_rank = cfg.algorithmic_bytes(args.batch, world)
+        launches_per_step = step.kernels_per_step
+        achieved = bytes_rank / (per_step_ms * 1e-3) / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            tok_cpu, _, desc, cores = cpu_sample(args.batch, 0, 5)
+            cpu = {"value": tok_cpu, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc}
+        line = {
+            "metric": "decode_matmul_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": per_step_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": f"{cfg.name}: 32 layers x (q,k,v,o,gate,up,down) + lm_head, int4 g32, fp16 scales, batch {args.batch}",
+                "batch": args.batch, "activations": "f32", "parallelism": f"tp{world}",
+                "weight_bytes": cfg.weight_bytes(), "l2": "inputs larger than L2 (4.2 GB of weights per step)"},
+            "e2e": {"value": tok_s_e2e, "unit": "tok/s", "ms_per_step": per_step_e2e,
+                    "h2d_bytes_per_step": int(step.x.numel() * 4),
+                    "d2h_bytes_per_step": int(step.logits.numel() * 4)},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "qgemv_i4_kernel", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "frac_of_8tbs": achieved / 8000.0,
+                         "launches_per_step": launches_per_step,
+                         "algorithmic_bytes_per_launch": bytes_rank / max(1, launches_per_step),
+                         "traffic": None},
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+            "finite_outputs": logits_ok,
+        }
+        print(json.dumps(line))
+    step.close()
+    gpu.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="kq", choices=["kq", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cuda(args)
+
+
+if __name__ == "__main__":
+    main()

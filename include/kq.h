@@ -1,0 +1,199 @@
+/*
+ * kq.h — C ABI of libkq.so: karume's quantized `linear` op on NVIDIA B200 (sm_100a).
+ *
+ * karume has no native plugin interface: its backend seam is WebGPU.  The entry
+ * points below stand where the TypeScript runtime issues WebGPU calls for a
+ * `linear` node whose weight initializer is stored as packed int4 or int8, and each
+ * one names the reference code it replaces (paths relative to the karume
+ * repository).  Everything is expressible as `Deno.dlopen` symbol descriptors:
+ * parameters are i32 / u32 / u64 / pointer / buffer, results are i32 status codes or
+ * u64, out-values go through caller-provided pointers, there are no structs by
+ * value, callbacks or varargs.
+ *
+ * Conventions
+ *  - Every call returns a kq_status (0 = ok).  On failure the context keeps a
+ *    human-readable message (kq_last_error).  Nothing falls back to another
+ *    implementation: an unsupported request is an error.
+ *  - Device memory is addressed by plain 64-bit device pointers (`uint64_t`); a
+ *    buffer made by kq_buffer_alloc and a pointer obtained elsewhere in the same
+ *    process (e.g. a framework tensor) are interchangeable.
+ *  - One context = one CUDA device = one calling thread at a time (the reference
+ *    serialises the runs of a Session the same way,
+ *    packages/runtime/src/runtime/executor.ts:975-1008).  Calls enqueue work on the
+ *    context's stream and return; kq_sync is the fence (the reference's single
+ *    mapAsync fence, executor.ts:1423-1462).
+ *  - Same inputs give bit-identical outputs from run to run: reductions use fixed
+ *    trees and no floating-point atomics.
+ */
+#ifndef KQ_H_
+#define KQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KQ_API __attribute__((visibility("default")))
+
+typedef struct kq_ctx kq_ctx;
+typedef uint64_t kq_weight; /* opaque handle, 0 is never valid */
+typedef uint64_t kq_graph;  /* opaque handle, 0 is never valid */
+
+enum kq_status {
+  KQ_OK = 0,
+  KQ_ERR_BAD_ARG = 1,     /* null pointer, unknown enum value, stale handle */
+  KQ_ERR_SHAPE = 2,       /* a shape / size predicate of the storage contract is violated */
+  KQ_ERR_OOM = 3,         /* device allocation failed */
+  KQ_ERR_CUDA = 4,        /* a CUDA runtime call failed; message carries the CUDA error */
+  KQ_ERR_UNSUPPORTED = 5, /* valid request this build has no kernel for (never a silent alternate path) */
+  KQ_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up (multi-GPU exchange) */
+  KQ_ERR_RANGE = 7,       /* an activation was outside the domain a kernel documents */
+  KQ_ERR_STATE = 8        /* call not legal now (e.g. graph capture already open) */
+};
+
+/* storage.dtype of the weight initializer (docs/ir-v1.md:124-150, :164-186). */
+enum kq_storage { KQ_STORAGE_I4 = 4, KQ_STORAGE_I8 = 8 };
+
+/* Element types of activations, outputs and companion scales. */
+enum kq_dtype { KQ_F32 = 0, KQ_F16 = 1, KQ_BF16 = 2 };
+
+/* How a weight is cut for tensor-parallel execution (no reference counterpart:
+ * karume is single-device).  COLUMN keeps rows [rank*n/world, (rank+1)*n/world) of
+ * W and of the scale; ROW keeps the K range [rank*k/world, (rank+1)*k/world) of
+ * every row (k/world must be a multiple of the group size) and the matching scale
+ * columns. */
+enum kq_shard { KQ_SHARD_NONE = 0, KQ_SHARD_COLUMN = 1, KQ_SHARD_ROW = 2 };
+
+/* ---- context --------------------------------------------------------------
+ * Replaces acquireGpu() -> GpuContext (packages/runtime/src/gpu/device.ts:1182-1218):
+ * one device per context.  `device` is a CUDA ordinal.  workspace_bytes sizes the
+ * context-owned scratch the split-K kernels use (0 = default 16 MiB). */
+KQ_API int kq_init(int device, uint64_t workspace_bytes, kq_ctx** out);
+KQ_API void kq_destroy(kq_ctx* ctx);
+
+/* Message of the last failing call on this context ("" if none); with ctx == NULL
+ * the message of the last failing kq_init.  The pointer stays valid until the next
+ * failing call.  Mirrors the reference's typed, never-swallowed errors
+ * (packages/runtime/mod.ts:13-113). */
+KQ_API const char* kq_last_error(kq_ctx* ctx);
+
+/* Work is enqueued on the context's own stream unless a foreign cudaStream_t is
+ * installed here (pass 0 to return to the own stream). */
+KQ_API int kq_set_stream(kq_ctx* ctx, uint64_t cuda_stream);
+KQ_API int kq_sync(kq_ctx* ctx);
+
+/* Programmatic dependent launch between consecutive kq_linear kernels (each kernel
+ * prefetches its weights while its predecessor drains).  On by default. */
+KQ_API int kq_set_overlap(kq_ctx* ctx, int enabled);
+
+/* ---- device buffers ---------------------------------------------------------
+ * Replace the run arena's storage buffers and queue.writeBuffer / mapAsync readback
+ * (packages/runtime/src/runtime/recipe-builder.ts:409-418,
+ *  packages/runtime/src/runtime/executor.ts:1423-1462). */
+KQ_API int kq_buffer_alloc(kq_ctx* ctx, uint64_t bytes, uint64_t* out_dptr);
+KQ_API int kq_buffer_free(kq_ctx* ctx, uint64_t dptr);
+/* Asynchronous on the context's stream; the host range must stay valid until kq_sync
+ * unless it is pageable memory (then the copy is staged before the call returns). */
+KQ_API int kq_buffer_write(kq_ctx* ctx, uint64_t dptr, uint64_t offset, const void* host, uint64_t bytes);
+KQ_API int kq_buffer_read(kq_ctx* ctx, uint64_t dptr, uint64_t offset, void* host, uint64_t bytes);
+/* Page-locked host memory for the two calls above (what a Deno host would wrap in an
+ * ArrayBuffer via Deno.UnsafePointerView). */
+KQ_API int kq_host_alloc(kq_ctx* ctx, uint64_t bytes, void** out_host);
+KQ_API int kq_host_free(kq_ctx* ctx, void* host);
+
+/* ---- weights ------------------------------------------------------------------
+ * Replaces the i4 / i8 branch of Session.#build that uploads the packed payload and
+ * its companion scale once per Session
+ * (packages/runtime/src/runtime/executor.ts:830-896).
+ *
+ * payload: the safetensors bytes of the weight, logical shape [n, k] row-major.
+ *   I4: n*k/2 bytes, flat element i in byte i>>1, low nibble when i is even, stored
+ *       nibble u = q + 8 (packages/runtime/src/format/i4.ts:63-118);
+ *       group_size is a power of two >= 16 dividing k
+ *       (packages/runtime/src/kernels/weight-storage.ts:56-70); the scale is
+ *       [n, k/group_size] row-major.
+ *   I8: n*k signed bytes (packages/runtime/src/format/i8.ts:80-117); group_size
+ *       must be 0; the scale is [n] (the keepdim form [n,1] flattened).
+ * scale_dtype: KQ_F32 is the reference's companion format; KQ_F16 is accepted as
+ *   well and is widened exactly to f32 before the dequant multiply, so the
+ *   dequantised weight is the same single-rounding f32 value either way.
+ * payload_bytes / scale_bytes must equal the sizes the shape implies.
+ * The device layout is private to the library (the bytes may be permuted for
+ * coalesced streaming); no weight is ever expanded:
+ * kq_weight_resident_bytes == payload_bytes + scale_bytes, the invariant the
+ * reference asserts on Session.diagnostics().storage.residentCompressedBytes
+ * (packages/runtime/tests/gpu_i4_weights_test.ts:170-174). */
+KQ_API int kq_weight_upload(kq_ctx* ctx, int storage, const void* payload, uint64_t payload_bytes,
+                            const void* scale, uint64_t scale_bytes, int scale_dtype, uint32_t n,
+                            uint32_t k, uint32_t group_size, kq_weight* out);
+/* Same, keeping only this rank's shard (see kq_shard).  The host passes the FULL
+ * payload and scale; the shard is cut and laid out on the device. */
+KQ_API int kq_weight_upload_shard(kq_ctx* ctx, int storage, const void* payload,
+                                  uint64_t payload_bytes, const void* scale, uint64_t scale_bytes,
+                                  int scale_dtype, uint32_t n, uint32_t k, uint32_t group_size,
+                                  int shard, uint32_t rank, uint32_t world, kq_weight* out);
+KQ_API int kq_weight_free(kq_ctx* ctx, kq_weight w);
+KQ_API uint64_t kq_weight_resident_bytes(kq_ctx* ctx, kq_weight w);
+/* Logical [n, k] of the (possibly sharded) weight held on this device. */
+KQ_API int kq_weight_shape(kq_ctx* ctx, kq_weight w, uint32_t* out_n, uint32_t* out_k);
+
+/* Expands the resident weight to f32 [n, k] row-major with the kernels' own dequant
+ * rule.  Replaces the load-time CPU expansion of ineligible initializers
+ * (decodeI4 / decodeI8, executor.ts:851, :887) and is what the bit-exactness tests
+ * read (packages/runtime/tests/gpu_i4_weights_test.ts:404-459,
+ *       packages/runtime/tests/gpu_i8_weights_test.ts:612-660). */
+KQ_API int kq_weight_dequant(kq_ctx* ctx, kq_weight w, uint64_t out_f32_dptr);
+
+/* ---- the op ---------------------------------------------------------------------
+ * out[m, n] = sum_k x[m, k] * W[n, k] + bias[n], f32 accumulate, f32 output.
+ * Replaces RecipeBuilder.#buildLinear's pipeline lookup + dispatch
+ * (packages/runtime/src/runtime/recipe-builder.ts:1311-1392; bindings 1 x, 2 w,
+ * 3 bias, 4 out, 5 wscale — packages/runtime/src/kernels/gemm.ts:1223-1227).
+ * x is [m, k] row-major of x_dtype (leading dims flattened by the caller, as
+ * #buildLinear does); bias is f32 [n] and always present (arity 3 is fixed,
+ * packages/runtime/src/ops/shapes.ts:502-523); out is f32 [m, n].
+ * The kernel is a pure function of (storage, shape, m, x_dtype) — never autotuned,
+ * like the reference's geometry table
+ * (packages/runtime/src/kernels/gemm-geometry.ts:243-267). */
+KQ_API int kq_linear(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
+                     uint64_t out_dptr, uint32_t m);
+
+/* Several weights applied to the SAME x in one launch (q/k/v, gate/up).  Outputs
+ * are separate [m, n_i] tensors; semantics are those of `count` kq_linear calls. */
+KQ_API int kq_linear_multi(kq_ctx* ctx, uint32_t count, const kq_weight* w, uint64_t x_dptr,
+                           int x_dtype, const uint64_t* bias_dptr, const uint64_t* out_dptr,
+                           uint32_t m);
+
+/* Host-buffer form of kq_linear: copies x in, runs, copies out, and returns after
+ * the result is in `out_host` (the round trip Session.run makes per call,
+ * executor.ts:985-1507).  bias stays a device pointer: it is a weight-lifetime
+ * initializer. */
+KQ_API int kq_linear_host(kq_ctx* ctx, kq_weight w, const void* x_host, int x_dtype,
+                          uint64_t bias_dptr, float* out_host, uint32_t m);
+
+/* ---- replayable plans -----------------------------------------------------------
+ * Records every kq_* launch between begin and end into a CUDA graph that
+ * kq_graph_launch replays.  Replaces the reference's baked plan replay
+ * (executeBakedPlan, packages/runtime/src/runtime/recipe.ts:462). */
+KQ_API int kq_graph_begin(kq_ctx* ctx);
+KQ_API int kq_graph_end(kq_ctx* ctx, kq_graph* out);
+KQ_API int kq_graph_launch(kq_ctx* ctx, kq_graph g);
+KQ_API int kq_graph_free(kq_ctx* ctx, kq_graph g);
+
+/* ---- timing ---------------------------------------------------------------------
+ * CUDA events on the context's stream.  Replaces the reference's opt-in
+ * timestamp-query diagnostics (packages/runtime/src/gpu/submit.ts:180-194). */
+KQ_API int kq_timer_start(kq_ctx* ctx);
+KQ_API int kq_timer_stop(kq_ctx* ctx, float* out_ms); /* synchronises */
+
+/* Number of kernels this library has launched on the context so far. */
+KQ_API uint64_t kq_launch_count(kq_ctx* ctx);
+
+/* Library / build identification: "kq <version> sm_100a". */
+KQ_API const char* kq_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KQ_H_ */

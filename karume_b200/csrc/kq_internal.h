@@ -1,0 +1,62 @@
+// Host-side declarations shared by the translation units of libkq.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/kq.h"
+
+namespace kq {
+
+enum Layout : int {
+  kLayoutNative = 0,  // payload and scale exactly as uploaded (row-major)
+  kLayoutTiledI4 = 1  // chunked int4 layout described in kq_common.cuh (group size 32)
+};
+
+struct Weight {
+  int storage = 0;      // kq_storage
+  int scale_dtype = 0;  // kq_dtype (KQ_F32 or KQ_F16)
+  uint32_t n = 0, k = 0, group_size = 0;
+  int layout = kLayoutNative;
+  void* data = nullptr;   // native: payload; tiled: interleaved chunks (payload + scales)
+  void* scale = nullptr;  // native: scales; tiled: nullptr
+  uint64_t payload_bytes = 0, scale_bytes = 0;
+};
+
+// One launch's worth of "several weights, same x" (kq_linear_multi).
+constexpr int kMaxMulti = 4;
+
+struct LinearTarget {
+  const Weight* w;
+  const float* bias;
+  float* out;
+};
+
+struct LaunchEnv {
+  cudaStream_t stream;
+  bool overlap;          // programmatic dependent launch
+  void* workspace;       // split-K partial sums
+  uint64_t workspace_bytes;
+  unsigned int* counters;  // split-K arrival counters (zero between launches)
+  uint32_t counter_count;
+  int* error_flag;       // device word: non-zero once a kernel saw an out-of-domain activation
+  int sm_count;
+};
+
+// Generic kernels: any shape the storage contract allows, native layout.
+cudaError_t launch_linear_generic(const LaunchEnv& env, const Weight& w, const void* x, int x_dtype,
+                                  const float* bias, float* out, uint32_t m);
+cudaError_t launch_dequant(const LaunchEnv& env, const Weight& w, float* out);
+
+// Tiled int4 layout.
+bool tiled_i4_eligible(int storage, uint32_t n, uint32_t k, uint32_t group_size);
+cudaError_t launch_repack_i4(cudaStream_t stream, const uint8_t* payload, const void* scale,
+                             int scale_dtype, uint32_t n, uint32_t k, uint8_t* tiled);
+
+// Tensor-core GEMV for the tiled int4 layout, m <= 16.  Returns cudaErrorInvalidValue
+// when the request needs more workspace than the context owns.
+bool qgemv_i4_supports(const Weight& w, uint32_t m);
+cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget* targets,
+                            const void* x, int x_dtype, uint32_t m, int* launches);
+
+}  // namespace kq

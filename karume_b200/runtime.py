@@ -1,0 +1,222 @@
+"""Host-side mirror of the reference interface for the quantized `linear` path.
+
+karume's TypeScript runtime reaches this path through three steps, and the classes
+here keep their names, argument meaning and failure behaviour so the parity tests read
+like the reference's own:
+
+* ``acquire_gpu()``             <- ``acquireGpu()`` (packages/runtime/src/gpu/device.ts:1182-1218)
+* ``Gpu.upload_weight(...)``    <- the i4 / i8 branch of ``Session.#build``
+                                   (packages/runtime/src/runtime/executor.ts:830-896)
+* ``Gpu.linear(x, w, bias)``    <- ``RecipeBuilder.#buildLinear``
+                                   (packages/runtime/src/runtime/recipe-builder.ts:1311-1392)
+
+Everything funnels into the C ABI of ``libkq.so``; torch is used only to own device
+memory and streams.  Errors are raised, never swallowed, and there is no alternative
+execution path (the reference's "fail loudly" rule, CLAUDE.md:51 of its repository).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from ._lib import (KQ_BF16, KQ_F16, KQ_F32, KQ_SHARD_COLUMN, KQ_SHARD_NONE, KQ_SHARD_ROW,
+                   KQ_STORAGE_I4, KQ_STORAGE_I8)
+
+L = _lib.lib
+
+
+class KqError(RuntimeError):
+    """A libkq call returned a non-zero status (code + the library's message)."""
+
+    def __init__(self, code: int, message: str):
+        self.code = code
+        self.status = _lib.STATUS_NAMES.get(code, str(code))
+        super().__init__(f"{self.status}: {message}")
+
+
+_NP_DTYPES = {np.dtype(np.float32): KQ_F32, np.dtype(np.float16): KQ_F16}
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _tensor_dtype_code(t) -> int:
+    torch = _torch()
+    table = {torch.float32: KQ_F32, torch.float16: KQ_F16, torch.bfloat16: KQ_BF16}
+    if t.dtype not in table:
+        raise KqError(1, f"activation dtype {t.dtype} is not f32 / f16 / bf16")
+    return table[t.dtype]
+
+
+@dataclass
+class Weight:
+    """A resident quantized weight (handle + the metadata the host planned with)."""
+    gpu: "Gpu"
+    handle: int
+    storage: str        # "i4" | "i8"  (storage.dtype of the initializer)
+    n: int
+    k: int
+    group_size: int     # 0 for i8
+
+    @property
+    def resident_bytes(self) -> int:
+        return int(L.kq_weight_resident_bytes(self.gpu._ctx, self.handle))
+
+    def dequant(self):
+        """f32 [n, k] expansion computed on the device with the kernels' dequant rule."""
+        torch = _torch()
+        out = torch.empty((self.n, self.k), dtype=torch.float32, device=self.gpu.device)
+        self.gpu._check(L.kq_weight_dequant(self.gpu._ctx, self.handle, out.data_ptr()))
+        self.gpu.sync()
+        return out
+
+    def free(self) -> None:
+        if self.handle:
+            self.gpu._check(L.kq_weight_free(self.gpu._ctx, self.handle))
+            self.handle = 0
+
+
+class Gpu:
+    """One CUDA device = one libkq context (the reference's GpuContext)."""
+
+    def __init__(self, device: int = 0, workspace_bytes: int = 0, use_torch_stream: bool = True):
+        torch = _torch()
+        if not torch.cuda.is_available():
+            raise KqError(4, "no CUDA device: libkq has no CPU path")
+        self.index = int(device)
+        self.device = torch.device("cuda", self.index)
+        ctx = ctypes.c_void_p()
+        rc = L.kq_init(self.index, int(workspace_bytes), ctypes.byref(ctx))
+        if rc != 0:
+            raise KqError(rc, (L.kq_last_error(None) or b"").decode())
+        self._ctx = ctx
+        if use_torch_stream:
+            self.use_stream(torch.cuda.current_stream(self.device))
+
+    # -- plumbing -----------------------------------------------------------
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise KqError(rc, (L.kq_last_error(self._ctx) or b"").decode())
+
+    def use_stream(self, stream) -> None:
+        self._check(L.kq_set_stream(self._ctx, int(stream.cuda_stream) if stream is not None else 0))
+
+    def set_overlap(self, enabled: bool) -> None:
+        self._check(L.kq_set_overlap(self._ctx, 1 if enabled else 0))
+
+    def sync(self) -> None:
+        self._check(L.kq_sync(self._ctx))
+
+    @property
+    def launch_count(self) -> int:
+        return int(L.kq_launch_count(self._ctx))
+
+    def destroy(self) -> None:
+        if self._ctx:
+            L.kq_destroy(self._ctx)
+            self._ctx = None
+
+    # -- weights ------------------------------------------------------------
+    def upload_weight(self, storage: str, payload, scale, shape, group_size: int = 0,
+                      shard: int = KQ_SHARD_NONE, rank: int = 0, world: int = 1) -> Weight:
+        """payload: raw safetensors bytes (uint8 for i4, int8/uint8 for i8) of a [n, k]
+        weight; scale: float32 or float16 array, [n, k/group_size] (i4) or [n] / [n,1] (i8)."""
+        code = {"i4": KQ_STORAGE_I4, "i8": KQ_STORAGE_I8}.get(storage)
+        if code is None:
+            raise KqError(1, f"storage {storage!r}: only 'i4' and 'i8' weights take this path")
+        if len(shape) != 2:
+            raise KqError(2, f"linear weight must be rank 2 [out, in], got {tuple(shape)}")
+        n, k = int(shape[0]), int(shape[1])
+        pay = np.ascontiguousarray(np.asarray(payload)).view(np.uint8).reshape(-1)
+        sc = np.ascontiguousarray(np.asarray(scale))
+        if sc.dtype not in _NP_DTYPES:
+            raise KqError(1, f"scale dtype {sc.dtype} is not float32 / float16")
+        handle = ctypes.c_uint64(0)
+        args = (self._ctx, code, pay.ctypes.data, pay.size, sc.ctypes.data, sc.size * sc.itemsize,
+                _NP_DTYPES[sc.dtype], n, k, int(group_size))
+        if shard == KQ_SHARD_NONE:
+            rc = L.kq_weight_upload(*args, ctypes.byref(handle))
+        else:
+            rc = L.kq_weight_upload_shard(*args, int(shard), int(rank), int(world), ctypes.byref(handle))
+        self._check(rc)
+        sn, sk = ctypes.c_uint32(), ctypes.c_uint32()
+        self._check(L.kq_weight_shape(self._ctx, handle.value, ctypes.byref(sn), ctypes.byref(sk)))
+        return Weight(self, handle.value, storage, sn.value, sk.value, int(group_size))
+
+    # -- the op ---------------------------------------------------------------
+    def linear(self, x, weight: Weight, bias, out=None):
+        """out[..., n] = x[..., k] @ W[n, k]^T + bias[n]; x is a CUDA tensor (f32/f16/bf16),
+        bias a CUDA f32 tensor [n] (required: the op's arity is 3).  Returns f32."""
+        torch = _torch()
+        if x.shape[-1] != weight.k:
+            raise KqError(2, f"linear: x[..., {x.shape[-1]}] does not match W[{weight.n},{weight.k}]")
+        if bias is None or tuple(bias.shape) != (weight.n,) or bias.dtype != torch.float32:
+            raise KqError(2, f"linear: bias must be f32 [{weight.n}] (arity 3 is fixed)")
+        x = x.contiguous()
+        m = x.numel() // weight.k if weight.k else int(np.prod(x.shape[:-1]))
+        if out is None:
+            out = torch.empty(tuple(x.shape[:-1]) + (weight.n,), dtype=torch.float32, device=x.device)
+        self._check(L.kq_linear(self._ctx, weight.handle, x.data_ptr(), _tensor_dtype_code(x),
+                                bias.data_ptr(), out.data_ptr(), m))
+        return out
+
+    def linear_multi(self, x, weights, biases, outs=None):
+        """Several weights on the same x in one launch (q/k/v, gate/up)."""
+        torch = _torch()
+        x = x.contiguous()
+        k = weights[0].k
+        m = x.numel() // k
+        if outs is None:
+            outs = [torch.empty(tuple(x.shape[:-1]) + (w.n,), dtype=torch.float32, device=x.device)
+                    for w in weights]
+        cnt = len(weights)
+        arr = ctypes.c_uint64 * cnt
+        self._check(L.kq_linear_multi(
+            self._ctx, cnt, arr(*[w.handle for w in weights]), x.data_ptr(), _tensor_dtype_code(x),
+            arr(*[b.data_ptr() for b in biases]), arr(*[o.data_ptr() for o in outs]), m))
+        return outs
+
+    def linear_host(self, x: np.ndarray, weight: Weight, bias) -> np.ndarray:
+        """Host-buffer round trip: numpy x in, numpy f32 out (copies inside the call)."""
+        x = np.ascontiguousarray(x)
+        if x.dtype not in _NP_DTYPES:
+            raise KqError(1, f"host activations must be float32 / float16, got {x.dtype}")
+        if x.shape[-1] != weight.k:
+            raise KqError(2, f"linear: x[..., {x.shape[-1]}] does not match W[{weight.n},{weight.k}]")
+        m = x.size // weight.k
+        out = np.empty(x.shape[:-1] + (weight.n,), np.float32)
+        self._check(L.kq_linear_host(self._ctx, weight.handle, x.ctypes.data, _NP_DTYPES[x.dtype],
+                                     bias.data_ptr(), out.ctypes.data, m))
+        return out
+
+    # -- replayable plans -------------------------------------------------------
+    def graph_begin(self) -> None:
+        self._check(L.kq_graph_begin(self._ctx))
+
+    def graph_end(self) -> int:
+        g = ctypes.c_uint64(0)
+        self._check(L.kq_graph_end(self._ctx, ctypes.byref(g)))
+        return g.value
+
+    def graph_launch(self, g: int) -> None:
+        self._check(L.kq_graph_launch(self._ctx, g))
+
+    def graph_free(self, g: int) -> None:
+        self._check(L.kq_graph_free(self._ctx, g))
+
+    def timer_start(self) -> None:
+        self._check(L.kq_timer_start(self._ctx))
+
+    def timer_stop(self) -> float:
+        ms = ctypes.c_float(0)
+        self._check(L.kq_timer_stop(self._ctx, ctypes.byref(ms)))
+        return float(ms.value)
+
+
+def acquire_gpu(device: int = 0, **kwargs) -> Gpu:
+    return Gpu(device, **kwargs)
