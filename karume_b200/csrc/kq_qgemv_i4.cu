@@ -9,14 +9,22 @@
 // weight at ~6.5 TB/s is ~11.5e12 weights/s, which leaves about three issue slots per
 // weight on 148 SMs — not enough for "unpack, convert, scale, FMA" per weight on the
 // FP32 pipe, and nothing at all for m > 1.  So:
-//   * weights stream through a per-warp cp.async ring (128-bit per lane, 8 stages,
-//     no register staging, no block-wide barrier in the steady state);
+//   * each lane streams its weights with 128-bit read-only loads straight into a
+//     register ring (kDepth chunks ahead per row block); weights never touch shared
+//     memory, whose bandwidth the activations need;
 //   * a nibble is never converted: `word & 0x000F000F` IS a pair of binary16
-//     subnormals u * 2^-24, which feed mma.sync.m16n8k16 directly as the A operand
-//     (16 output channels x 16 k);
-//   * the activations are the B operand (8 rows of x per MMA), staged once per CTA in
-//     shared memory as binary16 hi + lo parts (x = hi + lo to ~2^-25 absolute) in the
-//     k-order the nibble pairs come out in, so one 128-bit shared load feeds two MMAs;
+//     subnormals u * 2^-24 and `word & 0x00F000F0` a pair u * 2^-20; both feed
+//     mma.sync.m16n8k16 directly as the A operand (16 output channels x 16 k), the
+//     factor 16 being taken out of the matching activations when they are staged.
+//     Integer/logic instructions issue at half rate, so the unpack (5 per 8 weights)
+//     is the scarce resource of the whole kernel;
+//   * the activations are the B operand.  They are staged once per CTA in shared
+//     memory as binary16 in the k-order the nibble pairs come out in, so one 128-bit
+//     shared load feeds two MMAs and is reused by both row blocks of the warp.  f32 and
+//     bf16 activations are split as x = hi + lo (binary16 each, ~2^-25 absolute) and
+//     the two parts sit in ADJACENT columns of the same MMA tile, so the extra
+//     precision costs no extra MMA: the lane that owns column pair (2t, 2t+1) adds the
+//     two partial sums;
 //   * the "- 8" of the storage rule is folded into the accumulator's initial value
 //     (-8 * sum of the group's x, computed once per CTA), and the group scale is
 //     applied in f32 to each group's 32-term partial sum:
@@ -25,16 +33,16 @@
 //     across groups.  Dequantised weights are therefore never rounded at all in this
 //     kernel; the bit-exact f32 expansion is a separate entry point sharing
 //     kq::dequant_i4.
-//   * K can be split across CTAs; partial sums go to the context workspace and the
-//     last CTA to arrive for a row tile adds them in split order (deterministic).
+//   * K can be split across the CTAs of a thread-block cluster (up to 8); each CTA
+//     leaves its partial sums in its own shared memory and, after one cluster barrier,
+//     every CTA adds a slice of the rows over distributed shared memory in rank order
+//     (deterministic, no global scratch, no atomics).
 //   * griddepcontrol lets the next launch start streaming its weights while this one
 //     drains; nothing that depends on the previous kernel is touched before the wait.
 //
 // Activation domain: finite |x| <= 65504 (binary16 range).  Larger finite values raise
 // the context's range flag, reported by the next kq_sync as KQ_ERR_RANGE.
-#include <cmath>
-#include <map>
-#include <tuple>
+#include <algorithm>
 #include <type_traits>
 
 #include "kq_common.cuh"
@@ -43,10 +51,10 @@
 namespace kq {
 namespace {
 
-constexpr int kWarps = 8;               // row blocks (16 rows each) per CTA tile
-constexpr int kTileRowsCta = kWarps * 16;
-constexpr int kStages = 8;              // cp.async ring depth, chunks per warp
-constexpr float kUnscale = 16777216.0f; // 2^24: undoes the subnormal encoding of the nibbles
+constexpr int kWarps = 4;                // warps per CTA
+constexpr int kDepth = 4;                // chunks in flight per row block, in registers
+constexpr int kMaxCluster = 8;           // portable cluster size: K splits per row tile
+constexpr float kUnscale = 16777216.0f;  // 2^24: undoes the subnormal encoding of the nibbles
 
 struct GemvParams {
   const uint8_t* w[kMaxMulti];
@@ -60,20 +68,20 @@ struct GemvParams {
   uint32_t chunks_per_split;
   uint32_t splits;
   uint32_t slab_chunks;  // chunks of x staged in shared memory at a time
-  float* partial;        // [split][m][rows_total]
-  uint32_t rows_total;
-  unsigned int* counters;
   int* error_flag;
 };
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int kPending>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+__device__ __forceinline__ uint2 ldg_stream_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
 }
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -84,8 +92,37 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], u
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// D = A.B + C with C in its own registers (the first MMA of a chain reads the
+// pre-computed "-8 sum x" term without a copy).
+__device__ __forceinline__ void mma_f16_init(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                             float c0, float c1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%11,%10,%11};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
+}
+
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
   return static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
 }
 
 template <typename XT>
@@ -101,8 +138,8 @@ __device__ __forceinline__ void load_x8(const XT* p, float (&v)[8]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       if constexpr (std::is_same<XT, __half>::value) {
-        v[2 * i] = __half2float(__ushort_as_half(static_cast<unsigned short>(parts[i] & 0xFFFFu)));
-        v[2 * i + 1] = __half2float(__ushort_as_half(static_cast<unsigned short>(parts[i] >> 16)));
+        v[2 * i] = half_bits_to_float(parts[i] & 0xFFFFu);
+        v[2 * i + 1] = half_bits_to_float(parts[i] >> 16);
       } else {
         v[2 * i] = __uint_as_float(parts[i] << 16);
         v[2 * i + 1] = __uint_as_float(parts[i] & 0xFFFF0000u);
@@ -112,15 +149,27 @@ __device__ __forceinline__ void load_x8(const XT* p, float (&v)[8]) {
 }
 
 // Stages groups [group0, group0 + groups) of x into shared memory.
-//   xs_hi / xs_lo : [local group][kMT rows][32 halfs], the 8 values of each k-octet
-//                   stored in the order 0,4,1,5,2,6,3,7
-//   cpre          : [local group][kMT] f32 = -8 * 2^-24 * sum over the group of (hi + lo)
-// Four consecutive threads share one (group, row): each converts one octet.
-template <typename XT, int kMT, bool kHasLo>
+//   xs   : [local group][kCols columns][32 halfs]; activation row r occupies column r
+//          (binary16 input) or columns 2r (hi) and 2r+1 (lo); the 8 values of each
+//          k-octet are stored in the order 0,4,1,5,2,6,3,7
+//   cpre : [local group][kCols] f32; -8 * 2^-24 * (sum of the group's hi + lo) in the hi
+//          column, 0 in the lo column
+// Four consecutive threads share one (group, row): each converts one octet.  Columns
+// beyond the rows that exist are never read (the B loads are predicated).
+// Stages groups [group0, group0 + groups) of x into shared memory.
+//   xs   : [local group][kCols columns][32 halfs]; activation row r occupies column r
+//          (binary16 input) or columns 2r (hi) and 2r+1 (lo).  The 8 values of each
+//          k-octet are stored in the order 0,4,1,5,2,6,3,7, and the odd ones (1,3,5,7)
+//          are stored divided by 16: their nibbles reach the MMA as u * 2^-20 instead
+//          of u * 2^-24.
+//   cpre : [local group][kCols] f32; -8 * 2^-24 * (sum of the group's x as staged) in
+//          the hi column, 0 in the lo column
+// Four consecutive threads share one (group, row): each converts one octet.  Columns
+// beyond the rows that exist are never read (the B loads are predicated).
+template <typename XT, int kCols, bool kHasLo>
 __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, uint32_t k,
-                                        uint32_t group0, uint32_t groups, uint8_t* xs_hi,
-                                        uint8_t* xs_lo, float* cpre, int* error_flag) {
-  // rows that exist: one thread per (group, row, octet)
+                                        uint32_t group0, uint32_t groups, uint8_t* xs, float* cpre,
+                                        int* error_flag) {
   const uint32_t items = groups * m * 4;
   const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles below
   bool out_of_range = false;
@@ -140,13 +189,15 @@ __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, ui
       for (int e = 0; e < 8; ++e) {
         const float a = fabsf(v[e]);
         if (a > 65504.0f && a < __int_as_float(0x7f800000)) out_of_range = true;
-        h[e] = __float2half_rn(v[e]);
+        const float staged = (e & 1) ? v[e] * 0.0625f : v[e];
+        const float back = (e & 1) ? 16.0f : 1.0f;
+        h[e] = __float2half_rn(staged);
         const float hf = __half2float(h[e]);
         if constexpr (kHasLo) {
-          l[e] = __float2half_rn(v[e] - hf);
-          sum += hf + __half2float(l[e]);
+          l[e] = __float2half_rn(staged - hf);
+          sum = fmaf(hf + __half2float(l[e]), back, sum);
         } else {
-          sum += hf;
+          sum = fmaf(hf, back, sum);
         }
       }
       hi4 = make_uint4(pack_half2(h[0], h[4]), pack_half2(h[1], h[5]), pack_half2(h[2], h[6]),
@@ -158,34 +209,34 @@ __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, ui
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     if (valid) {
-      const uint32_t off = lg * (kMT * 64) + row * 64 + q * 16;
-      *reinterpret_cast<uint4*>(xs_hi + off) = hi4;
-      if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs_lo + off) = lo4;
-      if (q == 0) cpre[lg * kMT + row] = sum * (-8.0f / kUnscale);
+      const uint32_t col = kHasLo ? 2 * row : row;
+      const uint32_t off = lg * (kCols * 64) + col * 64 + q * 16;
+      *reinterpret_cast<uint4*>(xs + off) = hi4;
+      if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + 64) = lo4;
+      if (q == 0) {
+        cpre[lg * kCols + col] = sum * (-8.0f / kUnscale);
+        if constexpr (kHasLo) cpre[lg * kCols + col + 1] = 0.0f;
+      }
     }
-  }
-  // rows of the MMA tile beyond m: zeros (their output columns are never stored)
-  const uint32_t pad_rows = kMT - m;
-  for (uint32_t item = threadIdx.x; item < groups * pad_rows * 4; item += blockDim.x) {
-    const uint32_t q = item & 3u;
-    const uint32_t rest = item >> 2;
-    const uint32_t row = m + rest % pad_rows;
-    const uint32_t lg = rest / pad_rows;
-    const uint32_t off = lg * (kMT * 64) + row * 64 + q * 16;
-    *reinterpret_cast<uint4*>(xs_hi + off) = make_uint4(0, 0, 0, 0);
-    if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs_lo + off) = make_uint4(0, 0, 0, 0);
-    if (q == 0) cpre[lg * kMT + row] = 0.0f;
   }
   if (out_of_range) *reinterpret_cast<volatile int*>(error_flag) = 1;  // sticky, host-mapped word
 }
 
-template <typename XT, bool kScaleF16, int kMT>
+template <bool kScaleF16>
+struct ChunkRegs {
+  uint4 w;  // row g grp 0 | row g+8 grp 0 | row g grp 1 | row g+8 grp 1
+  typename std::conditional<kScaleF16, uint2, uint4>::type s;
+};
+
+template <typename XT, bool kScaleF16, int kCols, int kRB>
 __global__ void __launch_bounds__(kWarps * 32)
 qgemv_i4_kernel(const GemvParams p) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
   constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;  // chunk bytes
-  constexpr int kTiles = kMT / 8;
+  constexpr int kTiles = kCols / 8;
+  constexpr int kAccPerTile = kHasLo ? 2 : 4;
+  constexpr uint32_t kTileRowsCta = kWarps * kRB * 16;
 
   extern __shared__ __align__(16) uint8_t smem[];
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -208,250 +259,276 @@ qgemv_i4_kernel(const GemvParams p) {
       w_base = p.w[i]; bias = p.bias[i]; out = p.out[i]; n = p.n[i]; tile0 = p.tile_begin[i];
     }
   const uint32_t tile = blockIdx.x - tile0;
-  const uint32_t row_block = tile * kWarps + warp;
-  const bool active = row_block * 16u < n;
+  const uint32_t row_block0 = (tile * kWarps + warp) * kRB;
 
   const uint32_t chunks_per_row = p.k / kChunkK;
-  const uint32_t split = blockIdx.y;
-  const uint32_t cbeg = split * p.chunks_per_split;
+  const uint32_t split = blockIdx.y;  // == rank in the cluster when splits > 1
+  const uint32_t cbeg = min(split * p.chunks_per_split, chunks_per_row);
   const uint32_t cend = min(cbeg + p.chunks_per_split, chunks_per_row);
   const uint32_t nch = cend - cbeg;
 
-  uint8_t* ring = smem + warp * (kStages * kCB);
-  const uint32_t slab_groups = 2 * p.slab_chunks;
-  uint8_t* xs_hi = smem + kWarps * kStages * kCB;
-  uint8_t* xs_lo = xs_hi + (kHasLo ? slab_groups * kMT * 64 : 0);
-  float* cpre = reinterpret_cast<float*>(xs_lo + slab_groups * kMT * 64);
+  uint8_t* xs = smem;
+  float* cpre = reinterpret_cast<float*>(smem + 2 * p.slab_chunks * kCols * 64);
 
-  const uint8_t* stream = w_base + (static_cast<size_t>(row_block) * chunks_per_row + cbeg) * kCB;
+  bool active[kRB];
+  const uint8_t* stream[kRB];
+#pragma unroll
+  for (int r = 0; r < kRB; ++r) {
+    active[r] = (row_block0 + r) * 16u < n;
+    stream[r] = w_base + (static_cast<size_t>(row_block0 + r) * chunks_per_row + cbeg) * kCB + lane * 16;
+  }
+  const uint32_t scale_off = kChunkWeightBytes - lane * 16 + g * (4 * kScaleBytes);
 
-  auto issue = [&](uint32_t c) {
-    const uint8_t* src = stream + static_cast<size_t>(c) * kCB;
-    uint8_t* dst = ring + (c % kStages) * kCB;
-    cp_async16(dst + lane * 16, src + lane * 16);
-    if (lane < 2 * kScaleBytes) cp_async16(dst + kChunkWeightBytes + lane * 16, src + kChunkWeightBytes + lane * 16);
+  ChunkRegs<kScaleF16> ring[kDepth][kRB];
+  auto fetch = [&](ChunkRegs<kScaleF16>& dst, int r, uint32_t c) {
+    const uint8_t* src = stream[r] + static_cast<size_t>(c) * kCB;
+    dst.w = ldg_stream_v4(src);
+    if constexpr (kScaleF16) dst.s = ldg_stream_v2(src + scale_off);
+    else dst.s = ldg_stream_v4(src + scale_off);
   };
 
   // Weights do not depend on the previous kernel: start streaming before the wait.
 #pragma unroll
-  for (int s = 0; s < kStages; ++s) {
-    if (active && static_cast<uint32_t>(s) < nch) issue(s);
-    cp_async_commit();
-  }
+  for (int d = 0; d < kDepth; ++d)
+#pragma unroll
+    for (int r = 0; r < kRB; ++r) {
+      ring[d][r].w = make_uint4(0, 0, 0, 0);
+      if constexpr (kScaleF16) ring[d][r].s = make_uint2(0, 0);
+      else ring[d][r].s = make_uint4(0, 0, 0, 0);
+      if (active[r] && static_cast<uint32_t>(d) < nch) fetch(ring[d][r], r, d);
+    }
 
   pdl_wait_prior_grid();
 
-  float acc[kTiles][4];
+  float acc[kRB][kTiles][kAccPerTile];
 #pragma unroll
-  for (int i = 0; i < kTiles; ++i)
+  for (int r = 0; r < kRB; ++r)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int i = 0; i < kTiles; ++i)
+#pragma unroll
+      for (int j = 0; j < kAccPerTile; ++j) acc[r][i][j] = 0.0f;
 
   const XT* x = static_cast<const XT*>(p.x);
-  constexpr uint32_t kMask = 0x000F000Fu;
+  constexpr uint32_t kMask0 = 0x000F000Fu;  // nibbles 0 and 4 of a word: u * 2^-24 as binary16
+  constexpr uint32_t kMask1 = 0x00F000F0u;  // nibbles 1 and 5 of a word: u * 2^-20 as binary16
+  const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
+  bool load_b[kTiles], load_c[kTiles];
+#pragma unroll
+  for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+    load_b[tile_m] = tile_m * 8 + g < active_cols;
+    load_c[tile_m] = tile_m * 8 + 2 * t < active_cols;
+  }
+  const uint8_t* xs_lane = xs + lane * 16;
+  const float* cpre_lane = cpre + 2 * t;
 
   uint32_t in_slab = 0;
-  for (uint32_t c = 0; c < nch; ++c, ++in_slab) {
-    if (in_slab == p.slab_chunks) in_slab = 0;
-    if (in_slab == 0) {
-      if (c != 0) __syncthreads();  // everyone is done reading the previous slab
-      const uint32_t chunks_here = min(p.slab_chunks, nch - c);
-      stage_x<XT, kMT, kHasLo>(x, p.m, p.k, 2 * (cbeg + c), 2 * chunks_here, xs_hi, xs_lo, cpre,
-                               p.error_flag);
-      __syncthreads();
-    }
-    cp_async_wait<kStages - 1>();
-    __syncwarp();
-    if (active) {
-      const uint8_t* slot = ring + (c % kStages) * kCB;
-      const uint4 wq = *reinterpret_cast<const uint4*>(slot + lane * 16);
-      float sc[4];  // {row g, grp 0}, {row g+8, grp 0}, {row g, grp 1}, {row g+8, grp 1}
-      if constexpr (kScaleF16) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(slot + kChunkWeightBytes + g * 8);
-        sc[0] = __half2float(__ushort_as_half(static_cast<unsigned short>(raw.x & 0xFFFFu)));
-        sc[1] = __half2float(__ushort_as_half(static_cast<unsigned short>(raw.x >> 16)));
-        sc[2] = __half2float(__ushort_as_half(static_cast<unsigned short>(raw.y & 0xFFFFu)));
-        sc[3] = __half2float(__ushort_as_half(static_cast<unsigned short>(raw.y >> 16)));
-      } else {
-        const float4 raw = *reinterpret_cast<const float4*>(slot + kChunkWeightBytes + g * 16);
-        sc[0] = raw.x; sc[1] = raw.y; sc[2] = raw.z; sc[3] = raw.w;
-      }
-      __syncwarp();  // the slot is free once every lane has read it
-      if (c + kStages < nch) issue(c + kStages);
-      cp_async_commit();
-
+  for (uint32_t c0 = 0; c0 < nch; c0 += kDepth) {
 #pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        const uint32_t wa = jj ? wq.z : wq.x;  // row g
-        const uint32_t wb = jj ? wq.w : wq.y;  // row g + 8
-        // nibble pairs (e, e+4) of the lane's k-octet, as binary16 subnormals u * 2^-24
-        const uint32_t a0[4] = {wa & kMask, wb & kMask, (wa >> 4) & kMask, (wb >> 4) & kMask};
-        const uint32_t a1[4] = {(wa >> 8) & kMask, (wb >> 8) & kMask, (wa >> 12) & kMask, (wb >> 12) & kMask};
-        const uint32_t lg = 2 * in_slab + jj;
-#pragma unroll
-        for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
-          const uint32_t off = lg * (kMT * 64) + tile_m * 512 + lane * 16;
-          const uint4 bh = *reinterpret_cast<const uint4*>(xs_hi + off);
-          const float2 c0 = *reinterpret_cast<const float2*>(cpre + lg * kMT + tile_m * 8 + 2 * t);
-          float cf[4] = {c0.x, c0.y, c0.x, c0.y};
-          mma_f16(cf, a0, bh.x, bh.y);
-          mma_f16(cf, a1, bh.z, bh.w);
-          if constexpr (kHasLo) {
-            const uint4 bl = *reinterpret_cast<const uint4*>(xs_lo + off);
-            mma_f16(cf, a0, bl.x, bl.y);
-            mma_f16(cf, a1, bl.z, bl.w);
-          }
-          acc[tile_m][0] = fmaf(sc[2 * jj], cf[0], acc[tile_m][0]);
-          acc[tile_m][1] = fmaf(sc[2 * jj], cf[1], acc[tile_m][1]);
-          acc[tile_m][2] = fmaf(sc[2 * jj + 1], cf[2], acc[tile_m][2]);
-          acc[tile_m][3] = fmaf(sc[2 * jj + 1], cf[3], acc[tile_m][3]);
+    for (int d = 0; d < kDepth; ++d) {
+      const uint32_t c = c0 + d;
+      if (c < nch) {
+        if (in_slab == p.slab_chunks) in_slab = 0;
+        if (in_slab == 0) {
+          if (c != 0) __syncthreads();  // everyone is done reading the previous slab
+          const uint32_t chunks_here = min(p.slab_chunks, nch - c);
+          stage_x<XT, kCols, kHasLo>(x, p.m, p.k, 2 * (cbeg + c), 2 * chunks_here, xs, cpre, p.error_flag);
+          __syncthreads();
         }
+        // take this k-step's chunks out of the ring and refill the slots
+        uint4 wq[kRB];
+        float2 sc[kRB][2];  // [group]: .x = row g, .y = row g + 8
+#pragma unroll
+        for (int r = 0; r < kRB; ++r) {
+          wq[r] = ring[d][r].w;
+          if constexpr (kScaleF16) {
+            sc[r][0] = __half22float2(*reinterpret_cast<const __half2*>(&ring[d][r].s.x));
+            sc[r][1] = __half22float2(*reinterpret_cast<const __half2*>(&ring[d][r].s.y));
+          } else {
+            sc[r][0] = make_float2(__uint_as_float(ring[d][r].s.x), __uint_as_float(ring[d][r].s.y));
+            sc[r][1] = make_float2(__uint_as_float(ring[d][r].s.z), __uint_as_float(ring[d][r].s.w));
+          }
+          if (active[r] && c + kDepth < nch) fetch(ring[d][r], r, c + kDepth);
+        }
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const uint32_t lg = 2 * in_slab + jj;
+          // B fragments of this group: loaded once, used by every row block of the warp
+          uint4 bfrag[kTiles];
+          float2 cinit[kTiles];
+#pragma unroll
+          for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+            bfrag[tile_m] = make_uint4(0, 0, 0, 0);
+            cinit[tile_m] = make_float2(0.0f, 0.0f);
+            if (load_b[tile_m])
+              bfrag[tile_m] = *reinterpret_cast<const uint4*>(xs_lane + lg * (kCols * 64) + tile_m * 512);
+            if (load_c[tile_m])
+              cinit[tile_m] = *reinterpret_cast<const float2*>(cpre_lane + lg * kCols + tile_m * 8);
+          }
+#pragma unroll
+          for (int r = 0; r < kRB; ++r) {
+            const uint32_t wa = jj ? wq[r].z : wq[r].x;  // row g
+            const uint32_t wb = jj ? wq[r].w : wq[r].y;  // row g + 8
+            const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+            const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
+            const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
+            const float s_a = jj ? sc[r][1].x : sc[r][0].x;
+            const float s_b = jj ? sc[r][1].y : sc[r][0].y;
+#pragma unroll
+            for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+              float cf[4];
+              mma_f16_init(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y, cinit[tile_m].x, cinit[tile_m].y);
+              mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
+              if constexpr (kHasLo) {
+                acc[r][tile_m][0] = fmaf(s_a, cf[0] + cf[1], acc[r][tile_m][0]);
+                acc[r][tile_m][1] = fmaf(s_b, cf[2] + cf[3], acc[r][tile_m][1]);
+              } else {
+                acc[r][tile_m][0] = fmaf(s_a, cf[0], acc[r][tile_m][0]);
+                acc[r][tile_m][1] = fmaf(s_a, cf[1], acc[r][tile_m][1]);
+                acc[r][tile_m][2] = fmaf(s_b, cf[2], acc[r][tile_m][2]);
+                acc[r][tile_m][3] = fmaf(s_b, cf[3], acc[r][tile_m][3]);
+              }
+            }
+          }
+        }
+        ++in_slab;
       }
-    } else {
-      cp_async_commit();
     }
   }
-  cp_async_wait<0>();
 
   // ---- epilogue -----------------------------------------------------------------
-  const uint32_t row_a = row_block * 16u + g;
-  if (p.splits == 1) {
-    if (active) {
-      const float bias_a = bias[row_a], bias_b = bias[row_a + 8];
+  // lane owns, per row block and tile: rows g and g+8 of the block and activation rows
+  //   with hi/lo columns : mm = 4*tile + t             (acc[..][0] row g, [1] row g+8)
+  //   binary16 input     : mm = 8*tile + 2t, 2t+1      (acc[..][0,1] row g, [2,3] row g+8)
+  float* red = reinterpret_cast<float*>(smem);  // [m][kTileRowsCta], aliases the x slab
+  if (p.splits > 1) __syncthreads();            // the slab is dead from here on
 #pragma unroll
-      for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const uint32_t mm = tile_m * 8 + 2 * t + j;
-          if (mm < p.m) {
-            out[static_cast<size_t>(mm) * n + row_a] = fmaf(acc[tile_m][j], kUnscale, bias_a);
-            out[static_cast<size_t>(mm) * n + row_a + 8] = fmaf(acc[tile_m][2 + j], kUnscale, bias_b);
-          }
-        }
-      }
+  for (int r = 0; r < kRB; ++r) {
+    if (!active[r]) continue;
+    const uint32_t row_a = (row_block0 + r) * 16u + g;
+    const uint32_t tr_a = (warp * kRB + r) * 16u + g;  // row inside the CTA tile
+    float bias_a = 0.0f, bias_b = 0.0f;
+    if (p.splits == 1) {
+      bias_a = bias[row_a];
+      bias_b = bias[row_a + 8];
     }
-    return;
-  }
-
-  const uint32_t ws_row0 = blockIdx.x * kTileRowsCta;  // this tile's first row in the workspace
-  if (active) {
-    float* part = p.partial + static_cast<size_t>(split) * p.m * p.rows_total;
-    const uint32_t r = ws_row0 + warp * 16u + g;
 #pragma unroll
     for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const uint32_t mm = tile_m * 8 + 2 * t + j;
-        if (mm < p.m) {
-          __stcg(part + static_cast<size_t>(mm) * p.rows_total + r, acc[tile_m][j]);
-          __stcg(part + static_cast<size_t>(mm) * p.rows_total + r + 8, acc[tile_m][2 + j]);
+      for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
+        const uint32_t mm = kHasLo ? tile_m * 4 + t : tile_m * 8 + 2 * t + j;
+        if (mm >= p.m) continue;
+        const float va = acc[r][tile_m][kHasLo ? 0 : j];
+        const float vb = acc[r][tile_m][kHasLo ? 1 : 2 + j];
+        if (p.splits == 1) {
+          out[static_cast<size_t>(mm) * n + row_a] = fmaf(va, kUnscale, bias_a);
+          out[static_cast<size_t>(mm) * n + row_a + 8] = fmaf(vb, kUnscale, bias_b);
+        } else {
+          red[mm * kTileRowsCta + tr_a] = va;
+          red[mm * kTileRowsCta + tr_a + 8] = vb;
         }
       }
     }
   }
-  __shared__ unsigned int arrival;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) arrival = atomicAdd(p.counters + blockIdx.x, 1u);
-  __syncthreads();
-  if (arrival != p.splits - 1) return;
-  __threadfence();
-  // Last CTA of this row tile: add the partial sums in split order.
-  const uint32_t rows_here = min(static_cast<uint32_t>(kTileRowsCta), n - tile * kTileRowsCta);
-  for (uint32_t idx = threadIdx.x; idx < rows_here * p.m; idx += blockDim.x) {
-    const uint32_t mm = idx / rows_here, r = idx % rows_here;
-    float total = 0.0f;
-    for (uint32_t s = 0; s < p.splits; ++s)
-      total += __ldcg(p.partial + (static_cast<size_t>(s) * p.m + mm) * p.rows_total + ws_row0 + r);
+  if (p.splits == 1) return;
+
+  // K was split over the CTAs of this cluster: every CTA adds a slice of the tile's
+  // outputs over distributed shared memory, ranks in ascending order.
+  cluster_sync_all();
+  const uint32_t rows_here = min(kTileRowsCta, n - tile * kTileRowsCta);
+  const uint32_t total = rows_here * p.m;
+  const uint32_t per_rank = (total + p.splits - 1) / p.splits;
+  const uint32_t lo = min(split * per_rank, total), hi = min(lo + per_rank, total);
+  const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
+  for (uint32_t idx = lo + threadIdx.x; idx < hi; idx += blockDim.x) {
+    const uint32_t mm = idx / rows_here, r = idx - mm * rows_here;
+    const uint32_t local = red_base + (mm * kTileRowsCta + r) * 4u;
+    float sum = 0.0f;
+    for (uint32_t s = 0; s < p.splits; ++s) sum += ld_cluster_f32(cluster_map_shared(local, s));
     const uint32_t row = tile * kTileRowsCta + r;
-    out[static_cast<size_t>(mm) * n + row] = fmaf(total, kUnscale, bias[row]);
+    out[static_cast<size_t>(mm) * n + row] = fmaf(sum, kUnscale, bias[row]);
   }
-  if (threadIdx.x == 0) p.counters[blockIdx.x] = 0;  // ready for the next launch
+  cluster_sync_all();  // nobody's shared memory may go away while a peer still reads it
 }
 
-template <typename XT, bool kScaleF16, int kMT>
-size_t smem_bytes(uint32_t slab_chunks) {
-  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
-  const size_t cb = kChunkWeightBytes + 32u * (kScaleF16 ? 2u : 4u);
-  const size_t groups = 2 * slab_chunks;
-  return kWarps * kStages * cb + groups * kMT * 64 * (kHasLo ? 2 : 1) + groups * kMT * 4;
+template <int kCols, int kRB>
+size_t smem_bytes(uint32_t slab_chunks, uint32_t m, uint32_t splits) {
+  const size_t slab = static_cast<size_t>(2 * slab_chunks) * kCols * (64 + 4);
+  const size_t red = splits > 1 ? static_cast<size_t>(m) * kWarps * kRB * 16 * sizeof(float) : 0;
+  return std::max(slab, red);
 }
 
-struct Plan {
-  uint32_t splits, chunks_per_split, slab_chunks;
-};
-
-template <typename XT, bool kScaleF16, int kMT>
-cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, uint32_t tiles) {
-  auto kernel = qgemv_i4_kernel<XT, kScaleF16, kMT>;
+template <typename XT, bool kScaleF16, int kCols, int kRB>
+cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets) {
+  auto kernel = qgemv_i4_kernel<XT, kScaleF16, kCols, kRB>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const uint32_t chunks_per_row = p.k / kChunkK;
-  const uint32_t slab_cap = kMT == 8 ? 32u : 16u;
-
-  // Split K until the grid fills the machine; a pure function of the shape (never
-  // autotuned), memoised because the occupancy queries are host-side work.
-  static std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint64_t>, Plan> cache;
-  const auto key = std::make_tuple(tiles, chunks_per_row, p.m, env.workspace_bytes);
-  auto hit = cache.find(key);
-  Plan best{1, chunks_per_row, std::min(chunks_per_row, slab_cap)};
-  if (hit != cache.end()) {
-    best = hit->second;
-  } else {
-    double best_cost = 1e30;
-    const uint32_t max_splits = std::min<uint32_t>(32u, chunks_per_row);
-    for (uint32_t s = 1; s <= max_splits; ++s) {
-      const uint32_t cps = (chunks_per_row + s - 1) / s;
-      const uint32_t real = (chunks_per_row + cps - 1) / cps;
-      if (real != s) continue;
-      const uint32_t slab = std::min(cps, slab_cap);
-      if (s > 1) {
-        const uint64_t need = static_cast<uint64_t>(s) * p.m * p.rows_total * sizeof(float);
-        if (need > env.workspace_bytes || tiles > env.counter_count) continue;
-      }
-      int per_sm = 0;
-      cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-          &per_sm, kernel, kWarps * 32, smem_bytes<XT, kScaleF16, kMT>(slab));
-      if (e != cudaSuccess) return e;
-      if (per_sm < 1) continue;
-      const double slots = static_cast<double>(env.sm_count) * per_sm;
-      const double waves = std::ceil(static_cast<double>(tiles) * s / slots);
-      const double cost = waves * (cps + 6.0) + (s > 1 ? 1.0 : 0.0);
-      if (cost < best_cost - 1e-9) {
-        best_cost = cost;
-        best = Plan{s, cps, slab};
-      }
-    }
-    if (best_cost > 1e29) return cudaErrorInvalidConfiguration;
-    cache.emplace(key, best);
+  constexpr uint32_t kTileRowsCta = kWarps * kRB * 16;
+  uint32_t tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    p.tile_begin[i] = tiles;
+    tiles += (targets[i].w->n + kTileRowsCta - 1) / kTileRowsCta;
   }
-  p.splits = best.splits;
-  p.chunks_per_split = best.chunks_per_split;
-  p.slab_chunks = best.slab_chunks;
+  for (int i = count; i <= kMaxMulti; ++i) p.tile_begin[i] = tiles;
+
+  const uint32_t chunks_per_row = p.k / kChunkK;
+  const uint32_t slab_cap = 256u / kCols;  // <= 35 KB of shared memory per CTA
+
+  // Split K over a cluster until the grid fills the machine (about four CTAs per SM);
+  // a pure function of the shape, never autotuned.
+  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * 4u;
+  uint32_t splits = 1;
+  while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas &&
+         splits * 2 <= chunks_per_row)
+    splits *= 2;
+  p.splits = splits;
+  p.chunks_per_split = (chunks_per_row + splits - 1) / splits;
+  p.slab_chunks = std::max<uint32_t>(1u, std::min(p.chunks_per_split, slab_cap));
 
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles, best.splits, 1);
+  cfg.gridDim = dim3(tiles, splits, 1);
   cfg.blockDim = dim3(kWarps * 32, 1, 1);
-  cfg.dynamicSmemBytes = smem_bytes<XT, kScaleF16, kMT>(best.slab_chunks);
+  cfg.dynamicSmemBytes = smem_bytes<kCols, kRB>(p.slab_chunks, p.m, splits);
   cfg.stream = env.stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  unsigned int na = 0;
+  if (env.overlap) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (splits > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = splits;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = env.overlap ? 1 : 0;
+  cfg.numAttrs = na;
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
+// Columns of the MMA tile an activation row needs: 1 for binary16 input, 2 (hi, lo)
+// for f32 / bf16 input.  One row block per warp while a single MMA tile holds every
+// column; two (sharing the B fragments) beyond that, where shared-memory bandwidth
+// would otherwise bound the kernel.
 template <typename XT>
-cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, uint32_t tiles, bool scale_f16) {
-  if (p.m <= 8) {
-    return scale_f16 ? launch_typed<XT, true, 8>(env, p, tiles) : launch_typed<XT, false, 8>(env, p, tiles);
+cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* t, bool f16s) {
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  const uint32_t cols = kHasLo ? 2 * p.m : p.m;
+  if (cols <= 8)
+    return f16s ? launch_typed<XT, true, 8, 1>(env, p, count, t) : launch_typed<XT, false, 8, 1>(env, p, count, t);
+  if (cols <= 16)
+    return f16s ? launch_typed<XT, true, 16, 2>(env, p, count, t) : launch_typed<XT, false, 16, 2>(env, p, count, t);
+  if constexpr (kHasLo) {
+    return f16s ? launch_typed<XT, true, 32, 2>(env, p, count, t) : launch_typed<XT, false, 32, 2>(env, p, count, t);
+  } else {
+    return cudaErrorInvalidValue;
   }
-  return scale_f16 ? launch_typed<XT, true, 16>(env, p, tiles) : launch_typed<XT, false, 16>(env, p, tiles);
 }
 
 }  // namespace
@@ -462,10 +539,9 @@ bool qgemv_i4_supports(const Weight& w, uint32_t m) {
 
 cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget* targets,
                             const void* x, int x_dtype, uint32_t m, int* launches) {
-  if (count < 1 || count > kMaxMulti) return cudaErrorInvalidValue;
+  if (count < 1 || count > kMaxMulti || m < 1 || m > 16) return cudaErrorInvalidValue;
   GemvParams p = {};
   p.count = static_cast<uint32_t>(count);
-  uint32_t tiles = 0;
   const uint32_t k = targets[0].w->k;
   const int scale_dtype = targets[0].w->scale_dtype;
   for (int i = 0; i < count; ++i) {
@@ -475,23 +551,17 @@ cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget*
     p.bias[i] = targets[i].bias;
     p.out[i] = targets[i].out;
     p.n[i] = w.n;
-    p.tile_begin[i] = tiles;
-    tiles += (w.n + kTileRowsCta - 1) / kTileRowsCta;
   }
-  for (int i = count; i <= kMaxMulti; ++i) p.tile_begin[i] = tiles;
   p.x = x;
   p.m = m;
   p.k = k;
-  p.partial = static_cast<float*>(env.workspace);
-  p.rows_total = tiles * kTileRowsCta;
-  p.counters = env.counters;
   p.error_flag = env.error_flag;
   const bool f16s = scale_dtype == KQ_F16;
   cudaError_t e;
   switch (x_dtype) {
-    case KQ_F32: e = launch_x<float>(env, p, tiles, f16s); break;
-    case KQ_F16: e = launch_x<__half>(env, p, tiles, f16s); break;
-    case KQ_BF16: e = launch_x<__nv_bfloat16>(env, p, tiles, f16s); break;
+    case KQ_F32: e = launch_x<float>(env, p, count, targets, f16s); break;
+    case KQ_F16: e = launch_x<__half>(env, p, count, targets, f16s); break;
+    case KQ_BF16: e = launch_x<__nv_bfloat16>(env, p, count, targets, f16s); break;
     default: return cudaErrorInvalidValue;
   }
   if (e == cudaSuccess && launches) *launches += 1;
