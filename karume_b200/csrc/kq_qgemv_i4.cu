@@ -92,17 +92,6 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], u
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// D = A.B + C with C in its own registers (the first MMA of a chain reads the
-// pre-computed "-8 sum x" term without a copy).
-__device__ __forceinline__ void mma_f16_init(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
-                                             float c0, float c1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%10,%11,%10,%11};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
-}
-
 __device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
@@ -147,29 +136,19 @@ __device__ __forceinline__ void load_x8(const XT* p, float (&v)[8]) {
     }
   }
 }
-
 // Stages groups [group0, group0 + groups) of x into shared memory.
-//   xs   : [local group][kCols columns][32 halfs]; activation row r occupies column r
-//          (binary16 input) or columns 2r (hi) and 2r+1 (lo); the 8 values of each
-//          k-octet are stored in the order 0,4,1,5,2,6,3,7
-//   cpre : [local group][kCols] f32; -8 * 2^-24 * (sum of the group's hi + lo) in the hi
-//          column, 0 in the lo column
-// Four consecutive threads share one (group, row): each converts one octet.  Columns
-// beyond the rows that exist are never read (the B loads are predicated).
-// Stages groups [group0, group0 + groups) of x into shared memory.
-//   xs   : [local group][kCols columns][32 halfs]; activation row r occupies column r
+//   xs   : [local group][active columns][32 halfs]; activation row r occupies column r
 //          (binary16 input) or columns 2r (hi) and 2r+1 (lo).  The 8 values of each
 //          k-octet are stored in the order 0,4,1,5,2,6,3,7, and the odd ones (1,3,5,7)
 //          are stored divided by 16: their nibbles reach the MMA as u * 2^-20 instead
 //          of u * 2^-24.
-//   cpre : [local group][kCols] f32; -8 * 2^-24 * (sum of the group's x as staged) in
-//          the hi column, 0 in the lo column
-// Four consecutive threads share one (group, row): each converts one octet.  Columns
-// beyond the rows that exist are never read (the B loads are predicated).
-template <typename XT, int kCols, bool kHasLo>
+//   corr : [local group][kCorrStride] f32; entry r = -8 * 2^-24 * (sum of the group's x
+//          of activation row r, as staged): the "- 8" of the storage rule
+// Four consecutive threads share one (group, row): each converts one octet.
+template <typename XT, bool kHasLo, int kCorrStride>
 __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, uint32_t k,
-                                        uint32_t group0, uint32_t groups, uint8_t* xs, float* cpre,
-                                        int* error_flag) {
+                                        uint32_t group0, uint32_t groups, uint8_t* xs,
+                                        uint32_t xs_stride, float* corr, int* error_flag) {
   const uint32_t items = groups * m * 4;
   const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles below
   bool out_of_range = false;
@@ -210,13 +189,10 @@ __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, ui
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     if (valid) {
       const uint32_t col = kHasLo ? 2 * row : row;
-      const uint32_t off = lg * (kCols * 64) + col * 64 + q * 16;
+      const uint32_t off = lg * xs_stride + col * 64 + q * 16;
       *reinterpret_cast<uint4*>(xs + off) = hi4;
       if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + 64) = lo4;
-      if (q == 0) {
-        cpre[lg * kCols + col] = sum * (-8.0f / kUnscale);
-        if constexpr (kHasLo) cpre[lg * kCols + col + 1] = 0.0f;
-      }
+      if (q == 0) corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
     }
   }
   if (out_of_range) *reinterpret_cast<volatile int*>(error_flag) = 1;  // sticky, host-mapped word
@@ -228,6 +204,29 @@ struct ChunkRegs {
   typename std::conditional<kScaleF16, uint2, uint4>::type s;
 };
 
+// Shared loads that leave the destination untouched where the predicate is false: the
+// registers of lanes whose MMA column holds no activation row stay zero for the whole
+// kernel, at no per-iteration cost.
+__device__ __forceinline__ void lds_v4_if(uint4& v, uint32_t addr, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+               : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+               : "r"(addr), "r"(static_cast<uint32_t>(pred)));
+}
+__device__ __forceinline__ void lds_f32_if(float& v, uint32_t addr, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p ld.shared.f32 %0, [%1];\n\t}"
+               : "+f"(v)
+               : "r"(addr), "r"(static_cast<uint32_t>(pred)));
+}
+
+// D = A.B with a zero accumulator.
+__device__ __forceinline__ void mma_f16_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 template <typename XT, bool kScaleF16, int kCols, int kRB>
 __global__ void __launch_bounds__(kWarps * 32)
 qgemv_i4_kernel(const GemvParams p) {
@@ -236,6 +235,8 @@ qgemv_i4_kernel(const GemvParams p) {
   constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;  // chunk bytes
   constexpr int kTiles = kCols / 8;
   constexpr int kAccPerTile = kHasLo ? 2 : 4;
+  constexpr int kCorrPerTile = kHasLo ? 1 : 2;
+  constexpr int kCorrStride = kHasLo ? kCols / 2 : kCols;
   constexpr uint32_t kTileRowsCta = kWarps * kRB * 16;
 
   extern __shared__ __align__(16) uint8_t smem[];
@@ -267,21 +268,22 @@ qgemv_i4_kernel(const GemvParams p) {
   const uint32_t cend = min(cbeg + p.chunks_per_split, chunks_per_row);
   const uint32_t nch = cend - cbeg;
 
+  const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
+  const uint32_t xs_stride = active_cols * 64;  // bytes of staged activations per group
   uint8_t* xs = smem;
-  float* cpre = reinterpret_cast<float*>(smem + 2 * p.slab_chunks * kCols * 64);
+  float* corr = reinterpret_cast<float*>(smem + 2 * p.slab_chunks * xs_stride);
 
   bool active[kRB];
-  const uint8_t* stream[kRB];
+  const uint8_t* next[kRB];  // address this lane loads for the chunk kDepth ahead of the current block
 #pragma unroll
   for (int r = 0; r < kRB; ++r) {
     active[r] = (row_block0 + r) * 16u < n;
-    stream[r] = w_base + (static_cast<size_t>(row_block0 + r) * chunks_per_row + cbeg) * kCB + lane * 16;
+    next[r] = w_base + (static_cast<size_t>(row_block0 + r) * chunks_per_row + cbeg) * kCB + lane * 16;
   }
   const uint32_t scale_off = kChunkWeightBytes - lane * 16 + g * (4 * kScaleBytes);
 
   ChunkRegs<kScaleF16> ring[kDepth][kRB];
-  auto fetch = [&](ChunkRegs<kScaleF16>& dst, int r, uint32_t c) {
-    const uint8_t* src = stream[r] + static_cast<size_t>(c) * kCB;
+  auto fetch = [&](ChunkRegs<kScaleF16>& dst, const uint8_t* src) {
     dst.w = ldg_stream_v4(src);
     if constexpr (kScaleF16) dst.s = ldg_stream_v2(src + scale_off);
     else dst.s = ldg_stream_v4(src + scale_off);
@@ -295,8 +297,10 @@ qgemv_i4_kernel(const GemvParams p) {
       ring[d][r].w = make_uint4(0, 0, 0, 0);
       if constexpr (kScaleF16) ring[d][r].s = make_uint2(0, 0);
       else ring[d][r].s = make_uint4(0, 0, 0, 0);
-      if (active[r] && static_cast<uint32_t>(d) < nch) fetch(ring[d][r], r, d);
+      if (active[r] && static_cast<uint32_t>(d) < nch) fetch(ring[d][r], next[r] + d * kCB);
     }
+#pragma unroll
+  for (int r = 0; r < kRB; ++r) next[r] += kDepth * kCB;
 
   pdl_wait_prior_grid();
 
@@ -311,88 +315,104 @@ qgemv_i4_kernel(const GemvParams p) {
   const XT* x = static_cast<const XT*>(p.x);
   constexpr uint32_t kMask0 = 0x000F000Fu;  // nibbles 0 and 4 of a word: u * 2^-24 as binary16
   constexpr uint32_t kMask1 = 0x00F000F0u;  // nibbles 1 and 5 of a word: u * 2^-20 as binary16
-  const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
-  bool load_b[kTiles], load_c[kTiles];
+
+  // B fragments and "-8 sum x" terms live in registers that only lanes with a real
+  // column / activation row ever load into; everybody else keeps the initial zeros.
+  uint4 bfrag[kTiles];
+  float cterm[kTiles][kCorrPerTile];
+  bool load_b[kTiles], load_c[kTiles][kCorrPerTile];
 #pragma unroll
   for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+    bfrag[tile_m] = make_uint4(0, 0, 0, 0);
     load_b[tile_m] = tile_m * 8 + g < active_cols;
-    load_c[tile_m] = tile_m * 8 + 2 * t < active_cols;
+#pragma unroll
+    for (int j = 0; j < kCorrPerTile; ++j) {
+      cterm[tile_m][j] = 0.0f;
+      const uint32_t mm = kHasLo ? tile_m * 4 + t : tile_m * 8 + 2 * t + j;
+      load_c[tile_m][j] = mm < p.m;
+    }
   }
-  const uint8_t* xs_lane = xs + lane * 16;
-  const float* cpre_lane = cpre + 2 * t;
+  const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
+  const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) + (kHasLo ? t : 2 * t) * 4;
 
-  uint32_t in_slab = 0;
-  for (uint32_t c0 = 0; c0 < nch; c0 += kDepth) {
+  // One chunk (64 k = two scale groups) of every row block of the warp, out of ring
+  // slot d; then the slot is refilled with the chunk kDepth further on.
+  auto process = [&](const int d, uint32_t xs_addr, uint32_t corr_addr, bool refill) {
 #pragma unroll
-    for (int d = 0; d < kDepth; ++d) {
-      const uint32_t c = c0 + d;
-      if (c < nch) {
-        if (in_slab == p.slab_chunks) in_slab = 0;
-        if (in_slab == 0) {
-          if (c != 0) __syncthreads();  // everyone is done reading the previous slab
-          const uint32_t chunks_here = min(p.slab_chunks, nch - c);
-          stage_x<XT, kCols, kHasLo>(x, p.m, p.k, 2 * (cbeg + c), 2 * chunks_here, xs, cpre, p.error_flag);
-          __syncthreads();
+    for (int jj = 0; jj < 2; ++jj) {
+#pragma unroll
+      for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+        lds_v4_if(bfrag[tile_m], xs_addr + jj * xs_stride + tile_m * 512, load_b[tile_m]);
+#pragma unroll
+        for (int j = 0; j < kCorrPerTile; ++j)
+          lds_f32_if(cterm[tile_m][j], corr_addr + (jj * kCorrStride + tile_m * (kHasLo ? 4 : 8) + j) * 4,
+                     load_c[tile_m][j]);
+      }
+#pragma unroll
+      for (int r = 0; r < kRB; ++r) {
+        const uint32_t wa = jj ? ring[d][r].w.z : ring[d][r].w.x;  // row g
+        const uint32_t wb = jj ? ring[d][r].w.w : ring[d][r].w.y;  // row g + 8
+        const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+        const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
+        const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
+        float2 s;  // .x = row g, .y = row g + 8
+        if constexpr (kScaleF16) {
+          s = __half22float2(*reinterpret_cast<const __half2*>(jj ? &ring[d][r].s.y : &ring[d][r].s.x));
+        } else {
+          s = jj ? make_float2(__uint_as_float(ring[d][r].s.z), __uint_as_float(ring[d][r].s.w))
+                 : make_float2(__uint_as_float(ring[d][r].s.x), __uint_as_float(ring[d][r].s.y));
         }
-        // take this k-step's chunks out of the ring and refill the slots
-        uint4 wq[kRB];
-        float2 sc[kRB][2];  // [group]: .x = row g, .y = row g + 8
 #pragma unroll
-        for (int r = 0; r < kRB; ++r) {
-          wq[r] = ring[d][r].w;
-          if constexpr (kScaleF16) {
-            sc[r][0] = __half22float2(*reinterpret_cast<const __half2*>(&ring[d][r].s.x));
-            sc[r][1] = __half22float2(*reinterpret_cast<const __half2*>(&ring[d][r].s.y));
+        for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+          float cf[4];
+          mma_f16_zero(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y);
+          mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
+          if constexpr (kHasLo) {
+            acc[r][tile_m][0] = fmaf(s.x, (cf[0] + cf[1]) + cterm[tile_m][0], acc[r][tile_m][0]);
+            acc[r][tile_m][1] = fmaf(s.y, (cf[2] + cf[3]) + cterm[tile_m][0], acc[r][tile_m][1]);
           } else {
-            sc[r][0] = make_float2(__uint_as_float(ring[d][r].s.x), __uint_as_float(ring[d][r].s.y));
-            sc[r][1] = make_float2(__uint_as_float(ring[d][r].s.z), __uint_as_float(ring[d][r].s.w));
-          }
-          if (active[r] && c + kDepth < nch) fetch(ring[d][r], r, c + kDepth);
-        }
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const uint32_t lg = 2 * in_slab + jj;
-          // B fragments of this group: loaded once, used by every row block of the warp
-          uint4 bfrag[kTiles];
-          float2 cinit[kTiles];
-#pragma unroll
-          for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
-            bfrag[tile_m] = make_uint4(0, 0, 0, 0);
-            cinit[tile_m] = make_float2(0.0f, 0.0f);
-            if (load_b[tile_m])
-              bfrag[tile_m] = *reinterpret_cast<const uint4*>(xs_lane + lg * (kCols * 64) + tile_m * 512);
-            if (load_c[tile_m])
-              cinit[tile_m] = *reinterpret_cast<const float2*>(cpre_lane + lg * kCols + tile_m * 8);
-          }
-#pragma unroll
-          for (int r = 0; r < kRB; ++r) {
-            const uint32_t wa = jj ? wq[r].z : wq[r].x;  // row g
-            const uint32_t wb = jj ? wq[r].w : wq[r].y;  // row g + 8
-            const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
-            const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
-            const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
-            const float s_a = jj ? sc[r][1].x : sc[r][0].x;
-            const float s_b = jj ? sc[r][1].y : sc[r][0].y;
-#pragma unroll
-            for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
-              float cf[4];
-              mma_f16_init(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y, cinit[tile_m].x, cinit[tile_m].y);
-              mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
-              if constexpr (kHasLo) {
-                acc[r][tile_m][0] = fmaf(s_a, cf[0] + cf[1], acc[r][tile_m][0]);
-                acc[r][tile_m][1] = fmaf(s_b, cf[2] + cf[3], acc[r][tile_m][1]);
-              } else {
-                acc[r][tile_m][0] = fmaf(s_a, cf[0], acc[r][tile_m][0]);
-                acc[r][tile_m][1] = fmaf(s_a, cf[1], acc[r][tile_m][1]);
-                acc[r][tile_m][2] = fmaf(s_b, cf[2], acc[r][tile_m][2]);
-                acc[r][tile_m][3] = fmaf(s_b, cf[3], acc[r][tile_m][3]);
-              }
-            }
+            acc[r][tile_m][0] = fmaf(s.x, cf[0] + cterm[tile_m][0], acc[r][tile_m][0]);
+            acc[r][tile_m][1] = fmaf(s.x, cf[1] + cterm[tile_m][1], acc[r][tile_m][1]);
+            acc[r][tile_m][2] = fmaf(s.y, cf[2] + cterm[tile_m][0], acc[r][tile_m][2]);
+            acc[r][tile_m][3] = fmaf(s.y, cf[3] + cterm[tile_m][1], acc[r][tile_m][3]);
           }
         }
-        ++in_slab;
       }
     }
+    if (refill) {
+#pragma unroll
+      for (int r = 0; r < kRB; ++r)
+        if (active[r]) fetch(ring[d][r], next[r] + d * kCB);
+    }
+  };
+
+  for (uint32_t done = 0; done < nch;) {
+    const uint32_t slab_n = min(p.slab_chunks, nch - done);
+    if (done != 0) __syncthreads();  // everyone is done reading the previous slab
+    stage_x<XT, kHasLo, kCorrStride>(x, p.m, p.k, 2 * (cbeg + done), 2 * slab_n, xs, xs_stride, corr,
+                                     p.error_flag);
+    __syncthreads();
+    uint32_t xs_addr = xs_lane, corr_addr = corr_lane;
+    uint32_t i = 0;
+    for (; i + kDepth <= slab_n; i += kDepth) {
+#pragma unroll
+      for (int d = 0; d < kDepth; ++d) {
+        process(d, xs_addr, corr_addr, done + i + d + kDepth < nch);
+        xs_addr += 2 * xs_stride;
+        corr_addr += 2 * kCorrStride * 4;
+      }
+#pragma unroll
+      for (int r = 0; r < kRB; ++r) next[r] += kDepth * kCB;
+    }
+#pragma unroll
+    for (int d = 0; d < kDepth - 1; ++d) {  // the last, short block of the split
+      if (i + d < slab_n) {
+        process(d, xs_addr, corr_addr, false);
+        xs_addr += 2 * xs_stride;
+        corr_addr += 2 * kCorrStride * 4;
+      }
+    }
+    done += slab_n;
   }
 
   // ---- epilogue -----------------------------------------------------------------
@@ -450,11 +470,10 @@ qgemv_i4_kernel(const GemvParams p) {
   cluster_sync_all();  // nobody's shared memory may go away while a peer still reads it
 }
 
-template <int kCols, int kRB>
-size_t smem_bytes(uint32_t slab_chunks, uint32_t m, uint32_t splits) {
-  const size_t slab = static_cast<size_t>(2 * slab_chunks) * kCols * (64 + 4);
-  const size_t red = splits > 1 ? static_cast<size_t>(m) * kWarps * kRB * 16 * sizeof(float) : 0;
-  return std::max(slab, red);
+template <typename XT, int kCols>
+uint32_t group_smem_bytes(uint32_t m) {
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  return (kHasLo ? 2 * m : m) * 64 + (kHasLo ? kCols / 2 : kCols) * 4;
 }
 
 template <typename XT, bool kScaleF16, int kCols, int kRB>
@@ -475,7 +494,6 @@ cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const L
   for (int i = count; i <= kMaxMulti; ++i) p.tile_begin[i] = tiles;
 
   const uint32_t chunks_per_row = p.k / kChunkK;
-  const uint32_t slab_cap = 256u / kCols;  // <= 35 KB of shared memory per CTA
 
   // Split K over a cluster until the grid fills the machine (about four CTAs per SM);
   // a pure function of the shape, never autotuned.
@@ -486,12 +504,19 @@ cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const L
     splits *= 2;
   p.splits = splits;
   p.chunks_per_split = (chunks_per_row + splits - 1) / splits;
+  // Activations are staged at most ~32 KB at a time; a slab that is not the last one of
+  // its split must be a whole number of ring rounds.
+  const uint32_t per_chunk = 2 * group_smem_bytes<XT, kCols>(p.m);
+  uint32_t slab_cap = std::max<uint32_t>(kDepth, (32768u / per_chunk) / kDepth * kDepth);
   p.slab_chunks = std::max<uint32_t>(1u, std::min(p.chunks_per_split, slab_cap));
+
+  const size_t slab_bytes = static_cast<size_t>(p.slab_chunks) * per_chunk;
+  const size_t red_bytes = splits > 1 ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles, splits, 1);
   cfg.blockDim = dim3(kWarps * 32, 1, 1);
-  cfg.dynamicSmemBytes = smem_bytes<kCols, kRB>(p.slab_chunks, p.m, splits);
+  cfg.dynamicSmemBytes = std::max(slab_bytes, red_bytes);
   cfg.stream = env.stream;
   cudaLaunchAttribute attr[2];
   unsigned int na = 0;
