@@ -39,6 +39,7 @@ extern "C" {
 typedef struct kq_ctx kq_ctx;
 typedef uint64_t kq_weight; /* opaque handle, 0 is never valid */
 typedef uint64_t kq_graph;  /* opaque handle, 0 is never valid */
+typedef uint64_t kq_plan;   /* opaque handle, 0 is never valid */
 
 enum kq_status {
   KQ_OK = 0,
@@ -180,6 +181,24 @@ KQ_API int kq_graph_begin(kq_ctx* ctx);
 KQ_API int kq_graph_end(kq_ctx* ctx, kq_graph* out);
 KQ_API int kq_graph_launch(kq_ctx* ctx, kq_graph g);
 KQ_API int kq_graph_free(kq_ctx* ctx, kq_graph g);
+
+/* ---- fused plans ----------------------------------------------------------------
+ * Same role as kq_graph_* (the reference's baked-plan replay, recipe.ts:462), different
+ * execution: between begin and end, kq_linear / kq_linear_multi / kq_buffer_write /
+ * kq_buffer_read are RECORDED, not run; kq_plan_launch then executes all recorded linears
+ * inside one persistent kernel that keeps streaming weights across the dependencies
+ * between them, with the recorded host->device copies before it and the device->host
+ * copies after it.  Ops run in recording order and each one sees the outputs of all
+ * earlier ones.  Covered: int4 / group-32 weights in the library's tiled layout
+ * (n % 16 == 0, k % 64 == 0), one activation type, one m <= 16 and one scale type for the
+ * whole plan; anything else makes kq_plan_end return KQ_ERR_UNSUPPORTED (record such a
+ * sequence with kq_graph_begin instead).  The kernel uses the context workspace for
+ * split-K partial sums.  A bounded device-side wait that gives up is reported by the
+ * next kq_sync as KQ_ERR_TIMEOUT. */
+KQ_API int kq_plan_begin(kq_ctx* ctx);
+KQ_API int kq_plan_end(kq_ctx* ctx, kq_plan* out);
+KQ_API int kq_plan_launch(kq_ctx* ctx, kq_plan plan);
+KQ_API int kq_plan_free(kq_ctx* ctx, kq_plan plan);
 
 /* ---- timing ---------------------------------------------------------------------
  * CUDA events on the context's stream.  Replaces the reference's opt-in

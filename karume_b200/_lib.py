@@ -52,6 +52,10 @@ SYMBOLS = {
     "kq_graph_end": (_i32, [_vp, _pu64]),
     "kq_graph_launch": (_i32, [_vp, _u64]),
     "kq_graph_free": (_i32, [_vp, _u64]),
+    "kq_plan_begin": (_i32, [_vp]),
+    "kq_plan_end": (_i32, [_vp, _pu64]),
+    "kq_plan_launch": (_i32, [_vp, _u64]),
+    "kq_plan_free": (_i32, [_vp, _u64]),
     "kq_timer_start": (_i32, [_vp]),
     "kq_timer_stop": (_i32, [_vp, ctypes.POINTER(ctypes.c_float)]),
     "kq_launch_count": (_u64, [_vp]),
@@ -66,7 +70,7 @@ class KqLibraryMissing(ImportError):
 def load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise KqLibraryMissing(
-            f"{LIB_PATH} is not built. Run `python -m karume_b200.build` (needs nvcc); "
+            f"{LIB_PATH} is not built. Run `python karume_b200/build.py` (needs nvcc); "
             "karume_b200 has no implementation other than this CUDA library.")
     lib = ctypes.CDLL(LIB_PATH)
     for name, (restype, argtypes) in SYMBOLS.items():

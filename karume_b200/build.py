@@ -1,6 +1,6 @@
 """Builds libkq.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python -m karume_b200.build [--verbose] [--force]
+    python karume_b200/build.py [--verbose] [--force]
 
 The shared library lands next to this file so that it travels with the source tree;
 nothing is installed into site-packages and nothing is JIT-compiled at import time.
@@ -16,8 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libkq.so")
 
-SOURCES = ["kq_api.cu", "kq_generic.cu", "kq_qgemv_i4.cu"]
-HEADERS = ["kq_common.cuh", "kq_internal.h", os.path.join("..", "..", "include", "kq.h")]
+SOURCES = ["kq_api.cu", "kq_generic.cu", "kq_qgemv_i4.cu", "kq_plan.cu"]
+HEADERS = ["kq_common.cuh", "kq_gemv_core.cuh", "kq_internal.h", os.path.join("..", "..", "include", "kq.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

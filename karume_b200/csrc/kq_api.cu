@@ -23,6 +23,9 @@ struct kq_ctx {
   std::unordered_map<uint64_t, Weight*> weights;
   std::unordered_map<uint64_t, cudaGraphExec_t> graphs;
   std::unordered_map<uint64_t, uint64_t> graph_kernels;  // kernel nodes per recorded graph
+  std::unordered_map<uint64_t, kq::Plan*> plans;
+  kq::Plan* recording = nullptr;  // non-null between kq_plan_begin and kq_plan_end
+  std::string recording_refusal;  // first reason an op could not be fused
   uint64_t capture_mark = 0;
   uint64_t next_handle = 1;
   void* workspace = nullptr;
@@ -232,6 +235,12 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
                   find_weight(ctx, handles[0])->k);
     targets[i] = kq::LinearTarget{w, reinterpret_cast<const float*>(bias[i]), reinterpret_cast<float*>(out[i])};
   }
+  if (ctx->recording) {
+    const char* why = kq::plan_add_linear(ctx->recording, static_cast<int>(count), targets,
+                                          reinterpret_cast<const void*>(x), x_dtype, m);
+    if (why[0] != 0 && ctx->recording_refusal.empty()) ctx->recording_refusal = why;
+    return KQ_OK;
+  }
   if (m == 0) return KQ_OK;
   DeviceGuard guard(ctx->device);
   const kq::LaunchEnv env = env_of(ctx);
@@ -335,6 +344,8 @@ void kq_destroy(kq_ctx* ctx) {
   DeviceGuard guard(ctx->device);
   if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
   for (auto& kv : ctx->graphs) cudaGraphExecDestroy(kv.second);
+  for (auto& kv : ctx->plans) kq::plan_destroy(kv.second);
+  if (ctx->recording) kq::plan_destroy(ctx->recording);
   for (auto& kv : ctx->weights) {
     if (kv.second->data) cudaFree(kv.second->data);
     if (kv.second->scale) cudaFree(kv.second->scale);
@@ -369,9 +380,15 @@ int kq_set_overlap(kq_ctx* ctx, int enabled) {
 
 int kq_sync(kq_ctx* ctx) {
   if (!ctx) return KQ_ERR_BAD_ARG;
-  if (ctx->capturing) return fail(ctx, KQ_ERR_STATE, "kq_sync during graph capture");
+  if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_sync while a graph or plan is being recorded");
   DeviceGuard guard(ctx->device);
   KQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (auto& kv : ctx->plans) {
+    const int st = kq::plan_take_status(kv.second);
+    if (st != 0)
+      return fail(ctx, KQ_ERR_TIMEOUT, "a bounded wait inside the fused plan kernel gave up (%s); its outputs are not valid",
+                  st == 1 ? "grid barrier between ops" : "weight copy completion");
+  }
   if (*reinterpret_cast<volatile int*>(ctx->error_flag_host) != 0) {
     *reinterpret_cast<volatile int*>(ctx->error_flag_host) = 0;
     return fail(ctx, KQ_ERR_RANGE,
@@ -400,6 +417,10 @@ int kq_buffer_free(kq_ctx* ctx, uint64_t dptr) {
 int kq_buffer_write(kq_ctx* ctx, uint64_t dptr, uint64_t offset, const void* host, uint64_t bytes) {
   if (!ctx || !dptr || (!host && bytes)) return fail(ctx, KQ_ERR_BAD_ARG, "kq_buffer_write: null argument");
   DeviceGuard guard(ctx->device);
+  if (ctx->recording) {
+    if (bytes) kq::plan_add_copy(ctx->recording, true, reinterpret_cast<uint8_t*>(dptr) + offset, const_cast<void*>(host), bytes);
+    return KQ_OK;
+  }
   if (bytes)
     KQ_CUDA(ctx, cudaMemcpyAsync(reinterpret_cast<uint8_t*>(dptr) + offset, host, bytes,
                                  cudaMemcpyHostToDevice, ctx->stream));
@@ -409,6 +430,10 @@ int kq_buffer_write(kq_ctx* ctx, uint64_t dptr, uint64_t offset, const void* hos
 int kq_buffer_read(kq_ctx* ctx, uint64_t dptr, uint64_t offset, void* host, uint64_t bytes) {
   if (!ctx || !dptr || (!host && bytes)) return fail(ctx, KQ_ERR_BAD_ARG, "kq_buffer_read: null argument");
   DeviceGuard guard(ctx->device);
+  if (ctx->recording) {
+    if (bytes) kq::plan_add_copy(ctx->recording, false, reinterpret_cast<uint8_t*>(dptr) + offset, host, bytes);
+    return KQ_OK;
+  }
   if (bytes)
     KQ_CUDA(ctx, cudaMemcpyAsync(host, reinterpret_cast<const uint8_t*>(dptr) + offset, bytes,
                                  cudaMemcpyDeviceToHost, ctx->stream));
@@ -550,7 +575,7 @@ int kq_linear_host(kq_ctx* ctx, kq_weight h, const void* x_host, int x_dtype, ui
   if (!ctx) return KQ_ERR_BAD_ARG;
   Weight* w = find_weight(ctx, h);
   if (!w || !x_host || !out_host) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_host: bad argument");
-  if (ctx->capturing) return fail(ctx, KQ_ERR_STATE, "kq_linear_host during graph capture");
+  if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_linear_host during a recording");
   if (x_dtype != KQ_F32 && x_dtype != KQ_F16 && x_dtype != KQ_BF16)
     return fail(ctx, KQ_ERR_BAD_ARG, "x_dtype %d unknown", x_dtype);
   DeviceGuard guard(ctx->device);
@@ -582,7 +607,7 @@ int kq_linear_host(kq_ctx* ctx, kq_weight h, const void* x_host, int x_dtype, ui
 
 int kq_graph_begin(kq_ctx* ctx) {
   if (!ctx) return KQ_ERR_BAD_ARG;
-  if (ctx->capturing) return fail(ctx, KQ_ERR_STATE, "kq_graph_begin: a capture is already open");
+  if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_graph_begin: a recording is already open");
   DeviceGuard guard(ctx->device);
   KQ_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
   ctx->capturing = true;
@@ -628,6 +653,63 @@ int kq_graph_free(kq_ctx* ctx, kq_graph g) {
   cudaGraphExecDestroy(it->second);
   ctx->graphs.erase(it);
   ctx->graph_kernels.erase(g);
+  return KQ_OK;
+}
+
+int kq_plan_begin(kq_ctx* ctx) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_plan_begin: a recording is already open");
+  ctx->recording = kq::plan_create();
+  ctx->recording_refusal.clear();
+  return KQ_OK;
+}
+
+int kq_plan_end(kq_ctx* ctx, kq_plan* out) {
+  if (!ctx || !out) return fail(ctx, KQ_ERR_BAD_ARG, "kq_plan_end: null argument");
+  if (!ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_plan_end without kq_plan_begin");
+  *out = 0;
+  kq::Plan* plan = ctx->recording;
+  ctx->recording = nullptr;
+  DeviceGuard guard(ctx->device);
+  if (!ctx->recording_refusal.empty()) {
+    kq::plan_destroy(plan);
+    return fail(ctx, KQ_ERR_UNSUPPORTED, "the plan cannot be fused: %s (record it with kq_graph_begin instead)",
+                ctx->recording_refusal.c_str());
+  }
+  const char* why = "";
+  cudaError_t e = kq::plan_finalize(plan, env_of(ctx), &why);
+  if (e != cudaSuccess) {
+    kq::plan_destroy(plan);
+    if (why[0] != 0) return fail(ctx, KQ_ERR_UNSUPPORTED, "%s", why);
+    return cuda_fail(ctx, e, "kq_plan_end");
+  }
+  const uint64_t handle = ctx->next_handle++;
+  ctx->plans[handle] = plan;
+  *out = handle;
+  return KQ_OK;
+}
+
+int kq_plan_launch(kq_ctx* ctx, kq_plan plan) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  auto it = ctx->plans.find(plan);
+  if (it == ctx->plans.end()) return fail(ctx, KQ_ERR_BAD_ARG, "kq_plan_launch: unknown plan handle");
+  if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_plan_launch during a recording");
+  DeviceGuard guard(ctx->device);
+  int launched = 0;
+  cudaError_t e = kq::plan_launch(it->second, env_of(ctx), &launched);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "kq_plan_launch");
+  ctx->launches += launched;
+  return KQ_OK;
+}
+
+int kq_plan_free(kq_ctx* ctx, kq_plan plan) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  auto it = ctx->plans.find(plan);
+  if (it == ctx->plans.end()) return fail(ctx, KQ_ERR_BAD_ARG, "kq_plan_free: unknown plan handle");
+  DeviceGuard guard(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  kq::plan_destroy(it->second);
+  ctx->plans.erase(it);
   return KQ_OK;
 }
 

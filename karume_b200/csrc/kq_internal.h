@@ -60,3 +60,17 @@ cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget*
                             const void* x, int x_dtype, uint32_t m, int* launches);
 
 }  // namespace kq
+
+// ---- fused plans (kq_plan.cu) -------------------------------------------------------
+namespace kq {
+struct Plan;
+Plan* plan_create();
+void plan_destroy(Plan* plan);
+void plan_add_copy(Plan* plan, bool to_device, void* device, void* host, uint64_t bytes);
+const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, const void* x, int x_dtype,
+                            uint32_t m);
+uint32_t plan_op_count(const Plan* plan);
+cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why);
+cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches);
+int plan_take_status(Plan* plan);
+}  // namespace kq

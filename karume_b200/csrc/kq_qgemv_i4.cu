@@ -45,7 +45,7 @@
 #include <algorithm>
 #include <type_traits>
 
-#include "kq_common.cuh"
+#include "kq_gemv_core.cuh"
 #include "kq_internal.h"
 
 namespace kq {
@@ -54,7 +54,6 @@ namespace {
 constexpr int kWarps = 4;                // warps per CTA
 constexpr int kDepth = 4;                // chunks in flight per row block, in registers
 constexpr int kMaxCluster = 8;           // portable cluster size: K splits per row tile
-constexpr float kUnscale = 16777216.0f;  // 2^24: undoes the subnormal encoding of the nibbles
 
 struct GemvParams {
   const uint8_t* w[kMaxMulti];
@@ -84,14 +83,6 @@ __device__ __forceinline__ uint2 ldg_stream_v2(const void* p) {
   return v;
 }
 
-__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
 __device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
@@ -106,127 +97,11 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
-  return static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
-}
-
-__device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
-  return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
-}
-
-template <typename XT>
-__device__ __forceinline__ void load_x8(const XT* p, float (&v)[8]) {
-  if constexpr (std::is_same<XT, float>::value) {
-    const float4 a = reinterpret_cast<const float4*>(p)[0];
-    const float4 b = reinterpret_cast<const float4*>(p)[1];
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
-    const uint4 raw = *reinterpret_cast<const uint4*>(p);
-    const uint32_t parts[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if constexpr (std::is_same<XT, __half>::value) {
-        v[2 * i] = half_bits_to_float(parts[i] & 0xFFFFu);
-        v[2 * i + 1] = half_bits_to_float(parts[i] >> 16);
-      } else {
-        v[2 * i] = __uint_as_float(parts[i] << 16);
-        v[2 * i + 1] = __uint_as_float(parts[i] & 0xFFFF0000u);
-      }
-    }
-  }
-}
-// Stages groups [group0, group0 + groups) of x into shared memory.
-//   xs   : [local group][active columns][32 halfs]; activation row r occupies column r
-//          (binary16 input) or columns 2r (hi) and 2r+1 (lo).  The 8 values of each
-//          k-octet are stored in the order 0,4,1,5,2,6,3,7, and the odd ones (1,3,5,7)
-//          are stored divided by 16: their nibbles reach the MMA as u * 2^-20 instead
-//          of u * 2^-24.
-//   corr : [local group][kCorrStride] f32; entry r = -8 * 2^-24 * (sum of the group's x
-//          of activation row r, as staged): the "- 8" of the storage rule
-// Four consecutive threads share one (group, row): each converts one octet.
-template <typename XT, bool kHasLo, int kCorrStride>
-__device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, uint32_t k,
-                                        uint32_t group0, uint32_t groups, uint8_t* xs,
-                                        uint32_t xs_stride, float* corr, int* error_flag) {
-  const uint32_t items = groups * m * 4;
-  const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles below
-  bool out_of_range = false;
-  for (uint32_t item = threadIdx.x; item < items_padded; item += blockDim.x) {
-    const bool valid = item < items;
-    const uint32_t q = item & 3u;
-    const uint32_t rest = item >> 2;
-    const uint32_t row = rest % m;
-    const uint32_t lg = rest / m;
-    uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
-    float sum = 0.0f;
-    if (valid) {
-      float v[8];
-      load_x8<XT>(x + static_cast<size_t>(row) * k + (static_cast<size_t>(group0 + lg) << 5) + (q << 3), v);
-      __half h[8], l[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float a = fabsf(v[e]);
-        if (a > 65504.0f && a < __int_as_float(0x7f800000)) out_of_range = true;
-        const float staged = (e & 1) ? v[e] * 0.0625f : v[e];
-        const float back = (e & 1) ? 16.0f : 1.0f;
-        h[e] = __float2half_rn(staged);
-        const float hf = __half2float(h[e]);
-        if constexpr (kHasLo) {
-          l[e] = __float2half_rn(staged - hf);
-          sum = fmaf(hf + __half2float(l[e]), back, sum);
-        } else {
-          sum = fmaf(hf, back, sum);
-        }
-      }
-      hi4 = make_uint4(pack_half2(h[0], h[4]), pack_half2(h[1], h[5]), pack_half2(h[2], h[6]),
-                       pack_half2(h[3], h[7]));
-      if constexpr (kHasLo)
-        lo4 = make_uint4(pack_half2(l[0], l[4]), pack_half2(l[1], l[5]), pack_half2(l[2], l[6]),
-                         pack_half2(l[3], l[7]));
-    }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (valid) {
-      const uint32_t col = kHasLo ? 2 * row : row;
-      const uint32_t off = lg * xs_stride + col * 64 + q * 16;
-      *reinterpret_cast<uint4*>(xs + off) = hi4;
-      if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + 64) = lo4;
-      if (q == 0) corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
-    }
-  }
-  if (out_of_range) *reinterpret_cast<volatile int*>(error_flag) = 1;  // sticky, host-mapped word
-}
-
 template <bool kScaleF16>
 struct ChunkRegs {
   uint4 w;  // row g grp 0 | row g+8 grp 0 | row g grp 1 | row g+8 grp 1
   typename std::conditional<kScaleF16, uint2, uint4>::type s;
 };
-
-// Shared loads that leave the destination untouched where the predicate is false: the
-// registers of lanes whose MMA column holds no activation row stay zero for the whole
-// kernel, at no per-iteration cost.
-__device__ __forceinline__ void lds_v4_if(uint4& v, uint32_t addr, bool pred) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
-               : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
-               : "r"(addr), "r"(static_cast<uint32_t>(pred)));
-}
-__device__ __forceinline__ void lds_f32_if(float& v, uint32_t addr, bool pred) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p ld.shared.f32 %0, [%1];\n\t}"
-               : "+f"(v)
-               : "r"(addr), "r"(static_cast<uint32_t>(pred)));
-}
-
-// D = A.B with a zero accumulator.
-__device__ __forceinline__ void mma_f16_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%10,%10,%10,%10};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
-}
-
 template <typename XT, bool kScaleF16, int kCols, int kRB>
 __global__ void __launch_bounds__(kWarps * 32)
 qgemv_i4_kernel(const GemvParams p) {

@@ -23,9 +23,10 @@ fully chained step.
 
 karume itself is single-device (packages/runtime/src/gpu/device.ts:1182-1218); the
 sharding follows the usual column-then-row scheme so that one exchange per row-parallel
-matmul is the only communication.  With world == 1 the step is recorded through
-libkq's own plan API and replayed with one call; with world > 1 the recording goes
-through a torch CUDA graph so that the NCCL all-reduce is captured with the kernels.
+matmul is the only communication.  With world == 1 the step is recorded as a fused plan
+(kq_plan_*: one persistent kernel for all 129 linears) or, with fused=False, as a CUDA
+graph of one launch per linear (kq_graph_*); with world > 1 the recording goes through a
+torch CUDA graph so that the NCCL all-reduce is captured with the kernels.
 """
 from __future__ import annotations
 
@@ -102,7 +103,7 @@ class DecodeStep:
     """Resident sharded weights + activation buffers + a recorded plan of one step."""
 
     def __init__(self, gpu: Gpu, cfg: DecodeConfig, batch: int, rank: int = 0, world: int = 1,
-                 seed: int = 0, keep_host_weights: bool = False, process_group=None):
+                 seed: int = 0, keep_host_weights: bool = False, process_group=None, fused: bool = True):
         import torch
         if not 1 <= batch <= 16:
             raise ValueError("decode batch is 1..16 token rows")
@@ -111,6 +112,7 @@ class DecodeStep:
                 raise ValueError(f"dimension {dim} does not shard {world} ways on 16-row blocks")
         self.gpu, self.cfg, self.batch, self.rank, self.world = gpu, cfg, batch, rank, world
         self.pg = process_group
+        self.fused = fused and world == 1
         self.torch = torch
         dev = gpu.device
         self.weights = {}
@@ -188,16 +190,18 @@ class DecodeStep:
             self.gpu.use_stream(stream)
             self._stream = stream
             before = self.gpu.launch_count
-            self.gpu.graph_begin()
+            begin, end = (self.gpu.plan_begin, self.gpu.plan_end) if self.fused else (self.gpu.graph_begin, self.gpu.graph_end)
+            self._launch = self.gpu.plan_launch if self.fused else self.gpu.graph_launch
+            begin()
             self.enqueue()
-            self.plan = self.gpu.graph_end()
-            self.gpu.graph_begin()
+            self.plan = end()
+            begin()
             self.gpu._check(L.kq_buffer_write(self.gpu._ctx, self.x.data_ptr(), 0, self._px, self.x.numel() * 4))
             self.enqueue()
             self.gpu._check(L.kq_buffer_read(self.gpu._ctx, self.logits.data_ptr(), 0, self._pl, self.logits.numel() * 4))
-            self.plan_host = self.gpu.graph_end()
+            self.plan_host = end()
             assert self.gpu.launch_count == before
-            self.gpu.graph_launch(self.plan)
+            self._launch(self.plan)
             self.kernels_per_step = self.gpu.launch_count - before
             self.gpu.sync()
         else:
@@ -222,7 +226,7 @@ class DecodeStep:
     def run_device(self) -> None:
         """One step with x already resident; asynchronous."""
         if self.world == 1:
-            self.gpu.graph_launch(self.plan)
+            self._launch(self.plan)
         else:
             with self.torch.cuda.stream(self._stream):
                 self.torch_graph.replay()
@@ -230,7 +234,7 @@ class DecodeStep:
     def run_host(self) -> None:
         """One step through host buffers: host_x -> device, step, logits -> host_logits; asynchronous."""
         if self.world == 1:
-            self.gpu.graph_launch(self.plan_host)
+            self._launch(self.plan_host)
         else:
             with self.torch.cuda.stream(self._stream):
                 self.x.copy_(self._hx_t, non_blocking=True)

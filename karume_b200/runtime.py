@@ -209,6 +209,21 @@ class Gpu:
     def graph_free(self, g: int) -> None:
         self._check(L.kq_graph_free(self._ctx, g))
 
+    def plan_begin(self) -> None:
+        """Start recording linears (and host copies) into a fused plan; nothing runs until launch."""
+        self._check(L.kq_plan_begin(self._ctx))
+
+    def plan_end(self) -> int:
+        h = ctypes.c_uint64(0)
+        self._check(L.kq_plan_end(self._ctx, ctypes.byref(h)))
+        return h.value
+
+    def plan_launch(self, plan: int) -> None:
+        self._check(L.kq_plan_launch(self._ctx, plan))
+
+    def plan_free(self, plan: int) -> None:
+        self._check(L.kq_plan_free(self._ctx, plan))
+
     def timer_start(self) -> None:
         self._check(L.kq_timer_start(self._ctx))
 
