@@ -173,6 +173,28 @@ KQ_API int kq_linear_multi(kq_ctx* ctx, uint32_t count, const kq_weight* w, uint
 KQ_API int kq_linear_host(kq_ctx* ctx, kq_weight w, const void* x_host, int x_dtype,
                           uint64_t bias_dptr, float* out_host, uint32_t m);
 
+/* One linear for callers that must not allocate device memory (no counterpart in the
+ * reference, whose WebGPU layer always allocates through its arena).  Some hosts cannot
+ * afford a cudaMalloc on the inference path: a serving process that has handed all free
+ * HBM to its own cache pool (an allocation then fails or fragments that pool), or a loop
+ * with a latency budget that cudaMalloc's implicit device-wide synchronisation would
+ * break.  This call computes the same out = x . W^T + bias as kq_linear for an int4 /
+ * group-32 weight in the tiled layout and m <= 16, and takes every scratch byte it needs
+ * (split-K partial sums, arrival counters, barrier and status words, the op descriptor)
+ * from one static array inside the library, about 4.04 MiB, that each GPU holds from the
+ * moment it loads libkq until the process exits.  Neither this call nor anything it
+ * calls uses cudaMalloc, cudaFree or an allocating library routine.
+ *  - Limit: ceil(k / 512) * m * n * 4 bytes of partial sums must fit 4 MiB and n must not
+ *    exceed 131072; beyond that the call returns KQ_ERR_UNSUPPORTED and runs nothing.
+ *  - The first call on a device looks up the array's device address and zeroes its
+ *    counters; make that first call outside any stream capture.
+ *  - All calls share the one array: two calls whose kernels overlap on the GPU (different
+ *    streams or contexts of the same device) race on it.  The call therefore returns only
+ *    after its kernel has finished, and callers must not issue it concurrently.
+ *  - Weight, x, bias and out are the caller's, exactly as for kq_linear. */
+KQ_API int kq_linear_static(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
+                            uint64_t out_dptr, uint32_t m);
+
 /* ---- replayable plans -----------------------------------------------------------
  * Records every kq_* launch between begin and end into a CUDA graph that
  * kq_graph_launch replays.  Replaces the reference's baked plan replay

@@ -48,6 +48,7 @@ SYMBOLS = {
     "kq_linear": (_i32, [_vp, _u64, _u64, _i32, _u64, _u64, _u32]),
     "kq_linear_multi": (_i32, [_vp, _u32, _pu64, _u64, _i32, _pu64, _pu64, _u32]),
     "kq_linear_host": (_i32, [_vp, _u64, _vp, _i32, _u64, _vp, _u32]),
+    "kq_linear_static": (_i32, [_vp, _u64, _u64, _i32, _u64, _u64, _u32]),
     "kq_graph_begin": (_i32, [_vp]),
     "kq_graph_end": (_i32, [_vp, _pu64]),
     "kq_graph_launch": (_i32, [_vp, _u64]),

@@ -656,6 +656,33 @@ int kq_graph_free(kq_ctx* ctx, kq_graph g) {
   return KQ_OK;
 }
 
+int kq_linear_static(kq_ctx* ctx, kq_weight h, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
+                     uint64_t out_dptr, uint32_t m) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_linear_static during a recording");
+  const Weight* w = find_weight(ctx, h);
+  const int rc = check_linear_args(ctx, w, x_dptr, x_dtype, bias_dptr, out_dptr);
+  if (rc != KQ_OK) return rc;
+  DeviceGuard guard(ctx->device);
+  const kq::LinearTarget target{w, reinterpret_cast<const float*>(bias_dptr), reinterpret_cast<float*>(out_dptr)};
+  const char* why = "";
+  int device_status = 0;
+  cudaError_t e = kq::linear_static(env_of(ctx), target, reinterpret_cast<const void*>(x_dptr), x_dtype, m, &why,
+                                    &device_status);
+  if (e != cudaSuccess) {
+    if (why[0] != 0) return fail(ctx, KQ_ERR_UNSUPPORTED, "kq_linear_static: %s", why);
+    return cuda_fail(ctx, e, "kq_linear_static");
+  }
+  ctx->launches += 1;
+  if (device_status != 0)
+    return fail(ctx, KQ_ERR_TIMEOUT, "kq_linear_static: a bounded wait inside the kernel gave up; the output is not valid");
+  if (*reinterpret_cast<volatile int*>(ctx->error_flag_host) != 0) {
+    *reinterpret_cast<volatile int*>(ctx->error_flag_host) = 0;
+    return fail(ctx, KQ_ERR_RANGE, "kq_linear_static: an activation had a finite magnitude above 65504");
+  }
+  return KQ_OK;
+}
+
 int kq_plan_begin(kq_ctx* ctx) {
   if (!ctx) return KQ_ERR_BAD_ARG;
   if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_plan_begin: a recording is already open");

@@ -73,4 +73,8 @@ uint32_t plan_op_count(const Plan* plan);
 cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why);
 cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches);
 int plan_take_status(Plan* plan);
+// One linear through the fused kernel with every scratch byte in a static device array.
+cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, const void* x, int x_dtype,
+                          uint32_t m, const char** why, int* device_status);
+uint64_t linear_static_limit_bytes();
 }  // namespace kq

@@ -551,4 +551,124 @@ int plan_take_status(Plan* plan) {
   return s;
 }
 
+
+// ---- one linear, no allocation -------------------------------------------------------
+// Everything the fused kernel needs besides the caller's tensors lives in one file-scope
+// device array that every GPU loading this library carries until the process exits:
+//   [0, kStaticPartialBytes)        split-K partial sums
+//   then kStaticCounters words      per-row-block arrival counters (kept at zero between calls)
+//   then 256 B                      grid-barrier word
+//   then 256 B                      status word
+//   then 512 B                      the op descriptor
+constexpr size_t kStaticPartialBytes = size_t(4) << 20;
+constexpr uint32_t kStaticCounters = 8192;
+constexpr size_t kStaticCountersOff = kStaticPartialBytes;
+constexpr size_t kStaticBarOff = kStaticCountersOff + kStaticCounters * sizeof(unsigned int);
+constexpr size_t kStaticStatusOff = kStaticBarOff + 256;
+constexpr size_t kStaticOpOff = kStaticStatusOff + 256;
+constexpr size_t kStaticTotal = kStaticOpOff + 512;
+static_assert(sizeof(PlanOpDev) <= 512, "op descriptor outgrew its slot");
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticTotal];
+
+constexpr int kStaticMaxDevices = 64;
+static unsigned char* g_static_base[kStaticMaxDevices] = {};  // device address of the array, per device
+
+uint64_t linear_static_limit_bytes() { return kStaticPartialBytes; }
+
+// In host code `g_static_scratch` is only a handle: the address a kernel may use comes
+// from cudaGetSymbolAddress, asked once per device with that device current.
+static cudaError_t static_scratch_for_current_device(unsigned char** out) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device < 0 || device >= kStaticMaxDevices) return cudaErrorInvalidDevice;
+  if (!g_static_base[device]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    // counters must start at zero (afterwards the kernel leaves them at zero itself)
+    e = cudaMemset(static_cast<unsigned char*>(ptr) + kStaticCountersOff, 0,
+                   kStaticCounters * sizeof(unsigned int));
+    if (e != cudaSuccess) return e;
+    g_static_base[device] = static_cast<unsigned char*>(ptr);
+  }
+  *out = g_static_base[device];
+  return cudaSuccess;
+}
+
+cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, const void* x, int x_dtype,
+                          uint32_t m, const char** why, int* device_status) {
+  *why = "";
+  *device_status = 0;
+  const Weight& w = *target.w;
+  if (w.layout != kLayoutTiledI4) {
+    *why = "the weight is not in the tiled int4 / group-32 layout";
+    return cudaErrorInvalidValue;
+  }
+  if (m < 1 || m > 16) {
+    *why = "1..16 activation rows";
+    return cudaErrorInvalidValue;
+  }
+  PlanOpDev o = {};
+  o.count = 1;
+  o.w[0] = static_cast<const uint8_t*>(w.data);
+  o.bias[0] = target.bias;
+  o.out[0] = target.out;
+  o.n[0] = w.n;
+  o.rb_begin[0] = 0;
+  for (int i = 1; i <= kMaxMulti; ++i) o.rb_begin[i] = w.n / 16;
+  o.x = x;
+  o.k = w.k;
+  o.chunks_per_row = w.k / kChunkK;
+  o.slabs = (o.chunks_per_row + kSlotChunks - 1) / kSlotChunks;
+  o.row_blocks = w.n / 16;
+  o.row_blocks_padded = (o.row_blocks + kPlanWarps - 1) / kPlanWarps * kPlanWarps;
+  o.items = o.slabs * o.row_blocks_padded;
+  o.n_total = w.n;
+  if (o.slabs > 1 && static_cast<uint64_t>(o.slabs) * m * w.n * sizeof(float) > kStaticPartialBytes) {
+    *why = "slabs * m * n * 4 bytes of partial sums exceed the 4 MiB static scratch";
+    return cudaErrorInvalidValue;
+  }
+  if (o.row_blocks > kStaticCounters) {
+    *why = "more than 8192 16-row blocks (n > 131072)";
+    return cudaErrorInvalidValue;
+  }
+  unsigned char* base = nullptr;
+  cudaError_t e = static_scratch_for_current_device(&base);
+  if (e != cudaSuccess) return e;
+
+  Plan cfg;  // only carries the kernel choice; its vectors stay empty (no heap use)
+  cfg.m = m;
+  cfg.x_dtype = x_dtype;
+  cfg.scale_dtype = w.scale_dtype;
+  switch (x_dtype) {
+    case KQ_F32: e = configure_x<float>(cfg, env.sm_count); break;
+    case KQ_F16: e = configure_x<__half>(cfg, env.sm_count); break;
+    case KQ_BF16: e = configure_x<__nv_bfloat16>(cfg, env.sm_count); break;
+    default: return cudaErrorInvalidValue;
+  }
+  if (e != cudaSuccess) return e;
+
+  e = cudaMemcpyAsync(base + kStaticOpOff, &o, sizeof(o), cudaMemcpyHostToDevice, env.stream);
+  if (e != cudaSuccess) return e;
+  e = cudaMemsetAsync(base + kStaticBarOff, 0, 512, env.stream);  // barrier word and status word
+  if (e != cudaSuccess) return e;
+  PlanParams p = {};
+  p.ops = reinterpret_cast<const PlanOpDev*>(base + kStaticOpOff);
+  p.op_count = 1;
+  p.m = m;
+  p.partial = reinterpret_cast<float*>(base);
+  p.counters = reinterpret_cast<unsigned int*>(base + kStaticCountersOff);
+  p.grid_bar = reinterpret_cast<unsigned int*>(base + kStaticBarOff);
+  p.error_flag = env.error_flag;
+  p.status = reinterpret_cast<int*>(base + kStaticStatusOff);
+  void* args[] = {&p};
+  e = cudaLaunchCooperativeKernel(cfg.kernel, dim3(cfg.grid), dim3(kPlanWarps * 32), args, cfg.smem, env.stream);
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpyAsync(device_status, base + kStaticStatusOff, sizeof(int), cudaMemcpyDeviceToHost, env.stream);
+  if (e != cudaSuccess) return e;
+  return cudaStreamSynchronize(env.stream);
+}
+
 }  // namespace kq

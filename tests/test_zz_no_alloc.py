@@ -1,0 +1,56 @@
+"""kq_linear_static: the entry point for hosts that cannot allocate device memory while
+serving (all of HBM already belongs to their own pool, or a cudaMalloc's device-wide
+synchronisation does not fit their latency budget).  It must give the same answer as
+kq_linear while taking its scratch from the library's static device array.
+
+The file name sorts last on purpose: a run that stops at the first failure has already
+been through every other test when it gets here.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 1e-5, 1e-3  # the tolerance every parity test of this suite uses
+
+
+def test_static_scratch_linear_matches_the_allocating_entry_point_twice_in_a_row():
+    import torch
+    import karume_b200 as kb
+    import oracle
+    from tests import cases
+
+    gpu = kb.acquire_gpu(0)
+    L = kb.lib
+    rng = np.random.default_rng(7)
+    try:
+        for call, (n, k, m) in enumerate([(1024, 2048, 3), (4096, 4096, 1)]):
+            data, scale = cases.synth_i4(n, k, seed=50 + call)
+            w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+            x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+            bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+            want = gpu.linear(x, w, bias)  # the existing entry point (kq_linear)
+            gpu.sync()
+            for repeat in range(2):  # two calls in a row share the static array
+                got = torch.full((m, n), float("nan"), device="cuda")
+                rc = L.kq_linear_static(gpu._ctx, w.handle, x.data_ptr(), kb.KQ_F32, bias.data_ptr(),
+                                        got.data_ptr(), m)
+                assert rc == 0, (L.kq_last_error(gpu._ctx) or b"").decode()
+                rep = oracle.allclose(got.cpu().numpy(), want.cpu().numpy(), atol=ATOL, rtol=RTOL)
+                assert rep["pass"], (call, repeat, rep)
+            w.free()
+        # a request beyond the static array's size is refused, loudly, and runs nothing
+        n, k, m = 16384, 8192, 16  # 16 slabs * 16 * 16384 * 4 B = 16 MiB of partial sums
+        data, scale = cases.synth_i4(n, k, seed=60)
+        w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+        x = torch.zeros((m, k), device="cuda")
+        out = torch.zeros((m, n), device="cuda")
+        rc = L.kq_linear_static(gpu._ctx, w.handle, x.data_ptr(), kb.KQ_F32, torch.zeros(n, device="cuda").data_ptr(),
+                                out.data_ptr(), m)
+        assert rc == 5  # KQ_ERR_UNSUPPORTED
+        assert b"4 MiB" in L.kq_last_error(gpu._ctx)
+        w.free()
+    finally:
+        gpu.destroy()
