@@ -179,18 +179,21 @@ KQ_API int kq_linear_host(kq_ctx* ctx, kq_weight w, const void* x_host, int x_dt
  * HBM to its own cache pool (an allocation then fails or fragments that pool), or a loop
  * with a latency budget that cudaMalloc's implicit device-wide synchronisation would
  * break.  This call computes the same out = x . W^T + bias as kq_linear for an int4 /
- * group-32 weight in the tiled layout and m <= 16, and takes every scratch byte it needs
- * (split-K partial sums, arrival counters, barrier and status words, the op descriptor)
- * from one static array inside the library, about 4.04 MiB, that each GPU holds from the
- * moment it loads libkq until the process exits.  Neither this call nor anything it
- * calls uses cudaMalloc, cudaFree or an allocating library routine.
- *  - Limit: ceil(k / 512) * m * n * 4 bytes of partial sums must fit 4 MiB and n must not
- *    exceed 131072; beyond that the call returns KQ_ERR_UNSUPPORTED and runs nothing.
- *  - The first call on a device looks up the array's device address and zeroes its
- *    counters; make that first call outside any stream capture.
- *  - All calls share the one array: two calls whose kernels overlap on the GPU (different
- *    streams or contexts of the same device) race on it.  The call therefore returns only
- *    after its kernel has finished, and callers must not issue it concurrently.
+ * group-32 weight in the tiled layout and m <= 16 with the fused plan kernel, and takes
+ * the global scratch that kernel needs (barrier word, status word, op descriptor) from one
+ * static 4 KiB array inside the library, which each GPU holds from the moment it loads
+ * libkq until the process exits.  Neither this call nor anything it calls uses cudaMalloc,
+ * cudaFree or an allocating library routine.
+ *  - Limit: the op's activations are staged whole in shared memory, so k * c * 2 bytes
+ *    (c = m for binary16 activations, 2 m for f32 / bf16) plus the weight rings must fit
+ *    227 KiB: e.g. k <= 14336 at m = 1 in f32, k <= 4096 at m = 8.  Beyond that the call
+ *    returns KQ_ERR_UNSUPPORTED and runs nothing.
+ *  - The first call on a device looks up the array's device address and zeroes it; make
+ *    that first call outside any stream capture.
+ *  - All calls share the one array, which keeps the previous call's contents; the words
+ *    that must start at zero are cleared by every call.  Two calls whose kernels overlap
+ *    on the GPU (different streams or contexts of one device) race on it, so the call
+ *    returns only after its kernel has finished and must not be issued concurrently.
  *  - Weight, x, bias and out are the caller's, exactly as for kq_linear. */
 KQ_API int kq_linear_static(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
                             uint64_t out_dptr, uint32_t m);
@@ -213,10 +216,10 @@ KQ_API int kq_graph_free(kq_ctx* ctx, kq_graph g);
  * copies after it.  Ops run in recording order and each one sees the outputs of all
  * earlier ones.  Covered: int4 / group-32 weights in the library's tiled layout
  * (n % 16 == 0, k % 64 == 0), one activation type, one m <= 16 and one scale type for the
- * whole plan; anything else makes kq_plan_end return KQ_ERR_UNSUPPORTED (record such a
- * sequence with kq_graph_begin instead).  The kernel uses the context workspace for
- * split-K partial sums.  A bounded device-side wait that gives up is reported by the
- * next kq_sync as KQ_ERR_TIMEOUT. */
+ * whole plan, and the widest op's activations (k * columns * 2 bytes) must fit in shared
+ * memory next to the weight rings; anything else makes kq_plan_end return
+ * KQ_ERR_UNSUPPORTED (record such a sequence with kq_graph_begin instead).  A bounded
+ * device-side wait that gives up is reported by the next kq_sync as KQ_ERR_TIMEOUT. */
 KQ_API int kq_plan_begin(kq_ctx* ctx);
 KQ_API int kq_plan_end(kq_ctx* ctx, kq_plan* out);
 KQ_API int kq_plan_launch(kq_ctx* ctx, kq_plan plan);

@@ -76,5 +76,4 @@ int plan_take_status(Plan* plan);
 // One linear through the fused kernel with every scratch byte in a static device array.
 cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, const void* x, int x_dtype,
                           uint32_t m, const char** why, int* device_status);
-uint64_t linear_static_limit_bytes();
 }  // namespace kq

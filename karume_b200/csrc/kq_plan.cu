@@ -6,16 +6,17 @@
 // matmuls one by one costs more in launch and drain latency than in memory time; here one
 // CTA per SM stays resident for the whole plan and the weight stream never stops:
 //
-//   * every warp owns a static, interleaved list of work items (16 output channels x 512 k
-//     = 4.6 KB of the tiled layout) across ALL ops of the plan, and keeps two of them in
-//     flight in its private shared-memory ring with cp.async.bulk + mbarrier.  The copies
-//     for the next op are issued before the warp waits for the previous op to finish, so
-//     HBM keeps streaming through the dependency barriers;
+//   * every warp owns a static list of work items across ALL ops of the plan (an item = a
+//     16-row block x one k-slab of the tiled layout) and streams them in pieces of up to
+//     4.6 KB through its private shared-memory ring with cp.async.bulk + mbarrier.  The
+//     copies for the next op are issued before the warp waits for the previous op to
+//     finish, so HBM keeps streaming through the dependency barriers;
 //   * the math per 64-k chunk is the same as in qgemv_i4_kernel (kq_gemv_core.cuh): nibble
 //     pairs as binary16 subnormals into mma.sync, hi/lo activation columns, f32 group scale;
-//   * partial sums of the k-slabs of one 16-row block meet in the context workspace; the
-//     warp that delivers the last slab adds them in slab order (deterministic) and writes
-//     the output row block;
+//   * an op with few output rows splits K over the warps of ONE CTA (S slabs x 16/S row
+//     blocks per CTA round); the S partial sums meet in shared memory and are added in slab
+//     order (deterministic, no atomics, no global scratch).  Ops with many rows give every
+//     warp a whole row block and store straight from registers;
 //   * ops are separated by a grid-wide barrier (all CTAs are co-resident: cooperative
 //     launch).  Every wait in this file is bounded: if one gives up, the kernel records a
 //     status word, keeps going without blocking, and the host reports KQ_ERR_TIMEOUT.
@@ -30,8 +31,7 @@ namespace kq {
 namespace {
 
 constexpr int kPlanWarps = 16;
-constexpr int kSlotChunks = 8;  // chunks (64 k each) per work item = per ring slot
-constexpr int kSlots = 2;       // ring slots per warp
+constexpr int kSlots = 2;  // ring slots per warp
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct PlanOpDev {
@@ -43,20 +43,20 @@ struct PlanOpDev {
   uint32_t count;
   const void* x;
   uint32_t k;
-  uint32_t chunks_per_row;  // k / 64
-  uint32_t slabs;           // k-slabs of kSlotChunks chunks per row block
-  uint32_t row_blocks;      // total 16-row blocks of the op
-  uint32_t row_blocks_padded;  // rounded up to kPlanWarps: all items of a CTA round share a slab
-  uint32_t items;           // slabs * row_blocks_padded
-  uint32_t n_total;
+  uint32_t chunks_per_row;   // k / 64
+  uint32_t slabs;            // S: k-slabs a row block is split into across the warps of a CTA
+  uint32_t chunks_per_slab;  // ceil(chunks_per_row / S)
+  uint32_t row_blocks;       // 16-row blocks of the op
+  uint32_t cta_items;        // ceil(row_blocks / (kPlanWarps / S)): CTA-sized units of work
+  uint32_t rounds;           // ceil(cta_items / grid)
+  uint32_t rot;              // CTA b works on unit round*grid + (b + rot) % grid
 };
 
 struct PlanParams {
   const PlanOpDev* ops;
   uint32_t op_count;
   uint32_t m;
-  float* partial;          // [slab][m][n_total] of the op being executed
-  unsigned int* counters;  // per 16-row block: slabs delivered (self-resetting)
+  uint32_t xs_bytes;       // shared memory reserved for the staged activations of one op
   unsigned int* grid_bar;  // arrivals at the inter-op barrier (zeroed before every launch)
   int* error_flag;         // activation out of domain
   int* status;             // non-zero: a bounded wait gave up
@@ -84,12 +84,46 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
   return v;
 }
 
-// Position of a warp in its list of work items.
-struct ItemCursor {
-  uint32_t op, round;
+// One warp's share of one CTA round of an op.
+struct WarpItem {
+  const uint8_t* src;  // first chunk of the slab in the tiled layout
+  uint32_t nck;        // chunks in the slab (0: nothing to do)
+  uint32_t c0;         // first chunk index inside the row (for the staged activations)
+  uint32_t rb;         // row block inside the op
+  uint32_t wi;         // which weight of the op
+  bool row_block_valid;
 };
 
-template <typename XT, bool kScaleF16, int kCols>
+template <uint32_t kCB>
+__device__ __forceinline__ WarpItem item_of(const PlanOpDev& o, uint32_t round, uint32_t warp, uint32_t grid,
+                                            uint32_t cta) {
+  WarpItem it;
+  it.nck = 0;
+  it.row_block_valid = false;
+  it.src = nullptr;
+  it.c0 = 0;
+  it.rb = 0;
+  it.wi = 0;
+  uint32_t cta_eff = cta + o.rot;
+  if (cta_eff >= grid) cta_eff -= grid;
+  const uint32_t unit = round * grid + cta_eff;
+  if (unit >= o.cta_items) return it;
+  const uint32_t per_cta = kPlanWarps / o.slabs;  // row blocks per CTA round
+  const uint32_t sub = warp / o.slabs, slab = warp - sub * o.slabs;
+  it.rb = unit * per_cta + sub;
+  if (it.rb >= o.row_blocks) return it;
+  it.row_block_valid = true;
+#pragma unroll
+  for (int i = 1; i < kMaxMulti; ++i)
+    if (i < static_cast<int>(o.count) && it.rb >= o.rb_begin[i]) it.wi = i;
+  it.c0 = slab * o.chunks_per_slab;
+  if (it.c0 >= o.chunks_per_row) return it;
+  it.nck = min(o.chunks_per_slab, o.chunks_per_row - it.c0);
+  it.src = o.w[it.wi] + (static_cast<size_t>(it.rb - o.rb_begin[it.wi]) * o.chunks_per_row + it.c0) * kCB;
+  return it;
+}
+
+template <typename XT, bool kScaleF16, int kCols, int kSlotChunks>
 __global__ void __launch_bounds__(kPlanWarps * 32, 1)
 plan_kernel(const PlanParams p) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
@@ -105,17 +139,18 @@ plan_kernel(const PlanParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
-  const uint32_t gw = blockIdx.x * kPlanWarps + warp;  // this warp's index in the grid
-  const uint32_t GW = gridDim.x * kPlanWarps;
+  const uint32_t grid = gridDim.x, cta = blockIdx.x;
 
-  // shared memory: [warp rings][mbarriers][x slab][corr]
+  // shared memory: [warp rings][mbarriers][staged x][corr][reduction buffers x2]
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t ring = smem_base + warp * (kSlots * kSlotBytes);
   const uint32_t bars = smem_base + kPlanWarps * kSlots * kSlotBytes + warp * (kSlots * 8);
   uint8_t* xs = smem + kPlanWarps * kSlots * kSlotBytes + kPlanWarps * kSlots * 8;
   const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
   const uint32_t xs_stride = active_cols * 64;
-  float* corr = reinterpret_cast<float*>(xs + 2 * kSlotChunks * xs_stride);
+  const uint32_t groups_max = p.xs_bytes / xs_stride;
+  float* corr = reinterpret_cast<float*>(xs + p.xs_bytes);
+  float* red = corr + groups_max * kCorrStride;  // [2][kPlanWarps][m][16]
 
   if (lane == 0) {
 #pragma unroll
@@ -125,45 +160,37 @@ plan_kernel(const PlanParams p) {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
 
-  // Decodes work item `item` of op `o`; false for the padding items of a slab.
-  auto locate = [&](const PlanOpDev& o, uint32_t item, const uint8_t*& src, uint32_t& nck, uint32_t& rb,
-                    uint32_t& ks, uint32_t& wi) -> bool {
-    ks = item / o.row_blocks_padded;
-    rb = item - ks * o.row_blocks_padded;
-    if (rb >= o.row_blocks) return false;
-    wi = 0;
-#pragma unroll
-    for (int i = 1; i < kMaxMulti; ++i)
-      if (i < static_cast<int>(o.count) && rb >= o.rb_begin[i]) wi = i;
-    const uint32_t c0 = ks * kSlotChunks;
-    nck = min(static_cast<uint32_t>(kSlotChunks), o.chunks_per_row - c0);
-    src = o.w[wi] + (static_cast<size_t>(rb - o.rb_begin[wi]) * o.chunks_per_row + c0) * kCB;
-    return true;
-  };
-
-  // Producer side: start the copy of this warp's next work item (whatever op it belongs
-  // to) into the ring slot that sequence number prod_q maps to.
-  ItemCursor prod{0, 0};
-  uint32_t prod_q = 0;
+  // Producer side: start the copy of the next piece (<= kSlotChunks chunks) of this warp's
+  // work list, whatever op it belongs to, into the slot sequence number prod_q maps to.
+  uint32_t prod_op = 0, prod_round = 0, prod_piece = 0, prod_q = 0;
   auto produce = [&]() {
-    while (prod.op < p.op_count) {
-      const PlanOpDev& o = p.ops[prod.op];
-      const uint32_t item = prod.round * GW + gw;
-      if (item >= o.items) {
-        prod.op += 1;
-        prod.round = 0;
+    while (prod_op < p.op_count) {
+      const PlanOpDev& o = p.ops[prod_op];
+      if (prod_round >= o.rounds) {
+        prod_op += 1;
+        prod_round = 0;
+        prod_piece = 0;
         continue;
       }
-      prod.round += 1;
-      const uint8_t* src;
-      uint32_t nck, rb, ks, wi;
-      if (!locate(o, item, src, nck, rb, ks, wi)) continue;
+      const WarpItem it = item_of<kCB>(o, prod_round, warp, grid, cta);
+      if (it.nck == 0) {
+        prod_round += 1;
+        prod_piece = 0;
+        continue;
+      }
+      const uint32_t first = prod_piece * kSlotChunks;
+      const uint32_t nc = min(static_cast<uint32_t>(kSlotChunks), it.nck - first);
       const uint32_t slot = prod_q & 1u;
       if (lane == 0) {
-        mbar_expect_tx(bars + slot * 8, nck * kCB);
-        bulk_copy_g2s(ring + slot * kSlotBytes, src, nck * kCB, bars + slot * 8);
+        mbar_expect_tx(bars + slot * 8, nc * kCB);
+        bulk_copy_g2s(ring + slot * kSlotBytes, it.src + static_cast<size_t>(first) * kCB, nc * kCB, bars + slot * 8);
       }
       prod_q += 1;
+      prod_piece += 1;
+      if (prod_piece * kSlotChunks >= it.nck) {
+        prod_piece = 0;
+        prod_round += 1;
+      }
       return;
     }
   };
@@ -188,7 +215,7 @@ plan_kernel(const PlanParams p) {
   const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
   const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) + (kHasLo ? t : 2 * t) * 4;
 
-  uint32_t cons_q = 0;
+  uint32_t cons_q = 0, red_buf = 0;
   for (uint32_t op = 0; op < p.op_count; ++op) {
     const PlanOpDev& o = p.ops[op];
     if (op > 0) {
@@ -197,162 +224,152 @@ plan_kernel(const PlanParams p) {
       if (threadIdx.x == 0) {
         __threadfence();
         atomicAdd(p.grid_bar, 1u);
-        const unsigned int target = op * gridDim.x;
+        const unsigned int target = op * grid;
         uint32_t spins = 0;
         while (ld_acquire_gpu(p.grid_bar) < target) {
           if (++spins > kSpinLimit) {
             *reinterpret_cast<volatile int*>(p.status) = 1;
             break;
           }
-          __nanosleep(32);
         }
         __threadfence();
       }
       __syncthreads();
     }
-    const XT* x = static_cast<const XT*>(o.x);
-    const uint32_t rounds = (o.items + GW - 1) / GW;
-    for (uint32_t round = 0; round < rounds; ++round) {
-      const uint32_t base = round * GW + blockIdx.x * kPlanWarps;  // first item of this CTA
-      if (base >= o.items) break;
-      // the CTA's 16 items share one k-slab (row_blocks_padded is a multiple of 16)
-      const uint32_t ks_cta = base / o.row_blocks_padded;
-      const uint32_t c0 = ks_cta * kSlotChunks;
-      const uint32_t nck_cta = min(static_cast<uint32_t>(kSlotChunks), o.chunks_per_row - c0);
-      __syncthreads();  // the previous round's slab is no longer being read
-      stage_x<XT, kHasLo, kCorrStride, true>(x, p.m, o.k, 2 * c0, 2 * nck_cta, xs, xs_stride, corr, p.error_flag);
-      __syncthreads();
+    // stage the op's whole activation block (it fits: checked when the plan was built)
+    stage_x<XT, kHasLo, kCorrStride, true>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, xs_stride, corr,
+                                           p.error_flag);
+    __syncthreads();
 
-      const uint8_t* src;
-      uint32_t nck, rb, ks, wi;
-      const uint32_t item = base + warp;
-      if (item >= o.items || !locate(o, item, src, nck, rb, ks, wi)) continue;
-
-      const uint32_t slot = cons_q & 1u, parity = (cons_q >> 1) & 1u;
-      {
-        uint32_t spins = 0;
-        while (!mbar_try_wait(bars + slot * 8, parity)) {
-          if (++spins > kSpinLimit) {
-            *reinterpret_cast<volatile int*>(p.status) = 2;
-            break;
-          }
-        }
-      }
+    const uint32_t slabs = o.slabs;
+    for (uint32_t round = 0; round < o.rounds; ++round) {
+      const WarpItem it = item_of<kCB>(o, round, warp, grid, cta);
       float acc[kTiles][kAccPerTile];
 #pragma unroll
       for (int i = 0; i < kTiles; ++i)
 #pragma unroll
         for (int j = 0; j < kAccPerTile; ++j) acc[i][j] = 0.0f;
 
-      const uint32_t slot_addr = ring + slot * kSlotBytes;
-#pragma unroll 2
-      for (uint32_t c = 0; c < nck; ++c) {
-        const uint32_t chunk_addr = slot_addr + c * kCB;
-        uint4 wq;
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(wq.x), "=r"(wq.y), "=r"(wq.z), "=r"(wq.w) : "r"(chunk_addr + lane * 16));
-        float2 sc[2];  // [group]: .x = row g, .y = row g + 8
-        if constexpr (kScaleF16) {
-          uint2 raw;
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(raw.x), "=r"(raw.y)
-                       : "r"(chunk_addr + kChunkWeightBytes + g * 8));
-          sc[0] = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-          sc[1] = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-        } else {
-          uint4 raw;
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
-                       : "r"(chunk_addr + kChunkWeightBytes + g * 16));
-          sc[0] = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.y));
-          sc[1] = make_float2(__uint_as_float(raw.z), __uint_as_float(raw.w));
-        }
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const uint32_t lg = 2 * c + jj;
-#pragma unroll
-          for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
-            lds_v4_if(bfrag[tile_m], xs_lane + lg * xs_stride + tile_m * 512, load_b[tile_m]);
-#pragma unroll
-            for (int j = 0; j < kCorrPerTile; ++j)
-              lds_f32_if(cterm[tile_m][j], corr_lane + (lg * kCorrStride + tile_m * (kHasLo ? 4 : 8) + j) * 4,
-                         load_c[tile_m][j]);
-          }
-          const uint32_t wa = jj ? wq.z : wq.x;  // row g
-          const uint32_t wb = jj ? wq.w : wq.y;  // row g + 8
-          const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
-          const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
-          const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
-          const float2 s = sc[jj];
-#pragma unroll
-          for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
-            float cf[4];
-            mma_f16_zero(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y);
-            mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
-            if constexpr (kHasLo) {
-              acc[tile_m][0] = fmaf(s.x, (cf[0] + cf[1]) + cterm[tile_m][0], acc[tile_m][0]);
-              acc[tile_m][1] = fmaf(s.y, (cf[2] + cf[3]) + cterm[tile_m][0], acc[tile_m][1]);
-            } else {
-              acc[tile_m][0] = fmaf(s.x, cf[0] + cterm[tile_m][0], acc[tile_m][0]);
-              acc[tile_m][1] = fmaf(s.x, cf[1] + cterm[tile_m][1], acc[tile_m][1]);
-              acc[tile_m][2] = fmaf(s.y, cf[2] + cterm[tile_m][0], acc[tile_m][2]);
-              acc[tile_m][3] = fmaf(s.y, cf[3] + cterm[tile_m][1], acc[tile_m][3]);
+      for (uint32_t first = 0; first < it.nck; first += kSlotChunks) {
+        const uint32_t nc = min(static_cast<uint32_t>(kSlotChunks), it.nck - first);
+        const uint32_t slot = cons_q & 1u, parity = (cons_q >> 1) & 1u;
+        {
+          uint32_t spins = 0;
+          while (!mbar_try_wait(bars + slot * 8, parity)) {
+            if (++spins > kSpinLimit) {
+              *reinterpret_cast<volatile int*>(p.status) = 2;
+              break;
             }
           }
         }
+        const uint32_t slot_addr = ring + slot * kSlotBytes;
+        const uint32_t group0 = 2 * (it.c0 + first);
+#pragma unroll 2
+        for (uint32_t c = 0; c < nc; ++c) {
+          const uint32_t chunk_addr = slot_addr + c * kCB;
+          uint4 wq;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(wq.x), "=r"(wq.y), "=r"(wq.z), "=r"(wq.w) : "r"(chunk_addr + lane * 16));
+          float2 sc[2];  // [group]: .x = row g, .y = row g + 8
+          if constexpr (kScaleF16) {
+            uint2 raw;
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(raw.x), "=r"(raw.y)
+                         : "r"(chunk_addr + kChunkWeightBytes + g * 8));
+            sc[0] = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+            sc[1] = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+          } else {
+            uint4 raw;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                         : "r"(chunk_addr + kChunkWeightBytes + g * 16));
+            sc[0] = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.y));
+            sc[1] = make_float2(__uint_as_float(raw.z), __uint_as_float(raw.w));
+          }
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const uint32_t lg = group0 + 2 * c + jj;
+#pragma unroll
+            for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+              lds_v4_if(bfrag[tile_m], xs_lane + lg * xs_stride + tile_m * 512, load_b[tile_m]);
+#pragma unroll
+              for (int j = 0; j < kCorrPerTile; ++j)
+                lds_f32_if(cterm[tile_m][j], corr_lane + (lg * kCorrStride + tile_m * (kHasLo ? 4 : 8) + j) * 4,
+                           load_c[tile_m][j]);
+            }
+            const uint32_t wa = jj ? wq.z : wq.x;  // row g
+            const uint32_t wb = jj ? wq.w : wq.y;  // row g + 8
+            const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+            const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
+            const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
+            const float2 s = sc[jj];
+#pragma unroll
+            for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+              float cf[4];
+              mma_f16_zero(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y);
+              mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
+              if constexpr (kHasLo) {
+                acc[tile_m][0] = fmaf(s.x, (cf[0] + cf[1]) + cterm[tile_m][0], acc[tile_m][0]);
+                acc[tile_m][1] = fmaf(s.y, (cf[2] + cf[3]) + cterm[tile_m][0], acc[tile_m][1]);
+              } else {
+                acc[tile_m][0] = fmaf(s.x, cf[0] + cterm[tile_m][0], acc[tile_m][0]);
+                acc[tile_m][1] = fmaf(s.x, cf[1] + cterm[tile_m][1], acc[tile_m][1]);
+                acc[tile_m][2] = fmaf(s.y, cf[2] + cterm[tile_m][0], acc[tile_m][2]);
+                acc[tile_m][3] = fmaf(s.y, cf[3] + cterm[tile_m][1], acc[tile_m][3]);
+              }
+            }
+          }
+        }
+        __syncwarp();  // every lane has read the slot: it can take the next piece
+        produce();
+        cons_q += 1;
       }
-      __syncwarp();  // every lane has read the slot: it can take the next item
-      produce();
-      cons_q += 1;
 
-      // ---- this item's 16 rows x m partial sums ------------------------------------
-      const uint32_t local_row = (rb - o.rb_begin[wi]) * 16u;  // first row of the block inside its weight
-      const uint32_t n_i = o.n[wi];
-      float* out = o.out[wi];
-      const float* bias = o.bias[wi];
-      const bool direct = o.slabs == 1;
+      // ---- this round's outputs ------------------------------------------------------
+      const uint32_t local_row = (it.rb - o.rb_begin[it.wi]) * 16u;  // first row of the block inside its weight
+      const uint32_t n_i = o.n[it.wi];
+      float* out = o.out[it.wi];
+      const float* bias = o.bias[it.wi];
+      if (slabs == 1) {
+        if (it.nck != 0) {
+#pragma unroll
+          for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+#pragma unroll
+            for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
+              const uint32_t mm = kHasLo ? tile_m * 4 + t : tile_m * 8 + 2 * t + j;
+              if (mm >= p.m) continue;
+              const float va = acc[tile_m][kHasLo ? 0 : j];
+              const float vb = acc[tile_m][kHasLo ? 1 : 2 + j];
+              out[static_cast<size_t>(mm) * n_i + local_row + g] = fmaf(va, kUnscale, bias[local_row + g]);
+              out[static_cast<size_t>(mm) * n_i + local_row + g + 8] = fmaf(vb, kUnscale, bias[local_row + g + 8]);
+            }
+          }
+        }
+        continue;
+      }
+      // K was split over `slabs` warps of this CTA: meet in shared memory, add in slab order.
+      float* mine = red + (static_cast<size_t>(red_buf) * kPlanWarps + warp) * p.m * 16;
 #pragma unroll
       for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
 #pragma unroll
         for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
           const uint32_t mm = kHasLo ? tile_m * 4 + t : tile_m * 8 + 2 * t + j;
           if (mm >= p.m) continue;
-          const float va = acc[tile_m][kHasLo ? 0 : j];
-          const float vb = acc[tile_m][kHasLo ? 1 : 2 + j];
-          if (direct) {
-            out[static_cast<size_t>(mm) * n_i + local_row + g] = fmaf(va, kUnscale, bias[local_row + g]);
-            out[static_cast<size_t>(mm) * n_i + local_row + g + 8] = fmaf(vb, kUnscale, bias[local_row + g + 8]);
-          } else {
-            float* part = p.partial + (static_cast<size_t>(ks) * p.m + mm) * o.n_total + rb * 16u + g;
-            __stcg(part, va);
-            __stcg(part + 8, vb);
-          }
+          mine[mm * 16 + g] = acc[tile_m][kHasLo ? 0 : j];          // zeros when the warp had no chunks
+          mine[mm * 16 + g + 8] = acc[tile_m][kHasLo ? 1 : 2 + j];
         }
       }
-      if (direct) continue;
-      // The warp that delivers the last k-slab of this row block adds all of them, in
-      // slab order, and writes the block's outputs.
-      __threadfence();
-      __syncwarp();
-      unsigned int arrived = 0;
-      if (lane == 0) arrived = atomicAdd(p.counters + rb, 1u);
-      arrived = __shfl_sync(0xffffffffu, arrived, 0);
-      if (arrived != o.slabs - 1) continue;
-      __threadfence();
-      const size_t slab_stride = static_cast<size_t>(p.m) * o.n_total;
-      for (uint32_t idx = lane; idx < 16u * p.m; idx += 32) {
-        const uint32_t mm = idx >> 4, r = idx & 15u;
-        const float* srcp = p.partial + static_cast<size_t>(mm) * o.n_total + rb * 16u + r;
-        float total = 0.0f;
-        uint32_t s = 0;
-        for (; s + 4 <= o.slabs; s += 4) {
-          const float v0 = __ldcg(srcp + (s + 0) * slab_stride), v1 = __ldcg(srcp + (s + 1) * slab_stride);
-          const float v2 = __ldcg(srcp + (s + 2) * slab_stride), v3 = __ldcg(srcp + (s + 3) * slab_stride);
-          total = (((total + v0) + v1) + v2) + v3;
+      __syncthreads();
+      const uint32_t sub = warp / slabs;
+      if (warp - sub * slabs == 0 && it.row_block_valid) {
+        const float* first_slab = red + (static_cast<size_t>(red_buf) * kPlanWarps + warp) * p.m * 16;
+        for (uint32_t idx = lane; idx < 16u * p.m; idx += 32) {
+          float total = 0.0f;
+          for (uint32_t s = 0; s < slabs; ++s) total += first_slab[static_cast<size_t>(s) * p.m * 16 + idx];
+          const uint32_t mm = idx >> 4, r = idx & 15u;
+          out[static_cast<size_t>(mm) * n_i + local_row + r] = fmaf(total, kUnscale, bias[local_row + r]);
         }
-        for (; s < o.slabs; ++s) total += __ldcg(srcp + s * slab_stride);
-        out[static_cast<size_t>(mm) * n_i + local_row + r] = fmaf(total, kUnscale, bias[local_row + r]);
       }
-      if (lane == 0) p.counters[rb] = 0;  // ready for the next op / launch
+      red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
     }
   }
 }
@@ -378,23 +395,30 @@ struct Plan {
   uint32_t m = 0;
   int x_dtype = 0;
   int scale_dtype = 0;
+  uint32_t k_max = 0;
   int grid = 0;
   size_t smem = 0;
+  uint32_t xs_bytes = 0;
   void* kernel = nullptr;
-  uint64_t partial_bytes = 0;
-  uint32_t max_row_blocks = 0;
 };
 
 namespace {
 
-template <typename XT, bool kScaleF16, int kCols>
-cudaError_t configure(Plan& plan, int sm_count) {
-  auto kernel = plan_kernel<XT, kScaleF16, kCols>;
+constexpr size_t kSmemBudget = 227 * 1024;
+
+template <typename XT, bool kScaleF16, int kCols, int kSlotChunks>
+cudaError_t configure(Plan& plan, int sm_count, bool* fits) {
+  auto kernel = plan_kernel<XT, kScaleF16, kCols, kSlotChunks>;
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   const uint32_t cb = kChunkWeightBytes + 32u * (kScaleF16 ? 2u : 4u);
   const uint32_t active_cols = kHasLo ? 2 * plan.m : plan.m;
-  const size_t smem = static_cast<size_t>(kPlanWarps) * kSlots * kSlotChunks * cb + kPlanWarps * kSlots * 8 +
-                      static_cast<size_t>(2 * kSlotChunks) * (active_cols * 64 + (kHasLo ? kCols / 2 : kCols) * 4);
+  const uint32_t groups = plan.k_max / 32;
+  const size_t xs_bytes = static_cast<size_t>(groups) * active_cols * 64;
+  const size_t smem = static_cast<size_t>(kPlanWarps) * kSlots * kSlotChunks * cb + kPlanWarps * kSlots * 8 + xs_bytes +
+                      static_cast<size_t>(groups) * (kHasLo ? kCols / 2 : kCols) * 4 +
+                      static_cast<size_t>(2) * kPlanWarps * plan.m * 16 * sizeof(float);
+  *fits = smem <= kSmemBudget;
+  if (!*fits) return cudaSuccess;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   int per_sm = 0;
@@ -403,22 +427,87 @@ cudaError_t configure(Plan& plan, int sm_count) {
   if (per_sm < 1) return cudaErrorLaunchOutOfResources;
   plan.kernel = reinterpret_cast<void*>(kernel);
   plan.smem = smem;
+  plan.xs_bytes = static_cast<uint32_t>(xs_bytes);
   plan.grid = sm_count;  // one CTA per SM; all co-resident (cooperative launch)
   return cudaSuccess;
 }
 
+// Deep weight rings when the staged activations leave room for them, shallower ones otherwise.
+template <typename XT, bool kScaleF16, int kCols>
+cudaError_t configure_slots(Plan& plan, int sm_count, bool* fits) {
+  cudaError_t e = configure<XT, kScaleF16, kCols, 8>(plan, sm_count, fits);
+  if (e != cudaSuccess || *fits) return e;
+  return configure<XT, kScaleF16, kCols, 4>(plan, sm_count, fits);
+}
+
 template <typename XT>
-cudaError_t configure_x(Plan& plan, int sm_count) {
+cudaError_t configure_x(Plan& plan, int sm_count, bool* fits) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   const bool f16s = plan.scale_dtype == KQ_F16;
   const uint32_t cols = kHasLo ? 2 * plan.m : plan.m;
-  if (cols <= 8) return f16s ? configure<XT, true, 8>(plan, sm_count) : configure<XT, false, 8>(plan, sm_count);
-  if (cols <= 16) return f16s ? configure<XT, true, 16>(plan, sm_count) : configure<XT, false, 16>(plan, sm_count);
+  if (cols <= 8)
+    return f16s ? configure_slots<XT, true, 8>(plan, sm_count, fits) : configure_slots<XT, false, 8>(plan, sm_count, fits);
+  if (cols <= 16)
+    return f16s ? configure_slots<XT, true, 16>(plan, sm_count, fits) : configure_slots<XT, false, 16>(plan, sm_count, fits);
   if constexpr (kHasLo) {
-    return f16s ? configure<XT, true, 32>(plan, sm_count) : configure<XT, false, 32>(plan, sm_count);
+    return f16s ? configure_slots<XT, true, 32>(plan, sm_count, fits) : configure_slots<XT, false, 32>(plan, sm_count, fits);
   } else {
     return cudaErrorInvalidValue;
   }
+}
+
+cudaError_t configure_any(Plan& plan, int sm_count, bool* fits) {
+  switch (plan.x_dtype) {
+    case KQ_F32: return configure_x<float>(plan, sm_count, fits);
+    case KQ_F16: return configure_x<__half>(plan, sm_count, fits);
+    case KQ_BF16: return configure_x<__nv_bfloat16>(plan, sm_count, fits);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+// How an op is cut once the grid size is known: split K over S warps of a CTA until the
+// op offers work to most of the grid; a pure function of the shape.
+void shape_op(PlanOpDev& o, uint32_t grid, uint32_t* rot) {
+  uint32_t s = 1;
+  while (s < static_cast<uint32_t>(kPlanWarps) && s * 2 <= o.chunks_per_row &&
+         (o.row_blocks + kPlanWarps / s - 1) / (kPlanWarps / s) < (grid * 3) / 5)
+    s *= 2;
+  o.slabs = s;
+  o.chunks_per_slab = (o.chunks_per_row + s - 1) / s;
+  o.cta_items = (o.row_blocks + kPlanWarps / s - 1) / (kPlanWarps / s);
+  o.rounds = (o.cta_items + grid - 1) / grid;
+  o.rot = *rot;
+  *rot = (*rot + o.cta_items) % grid;  // the next op starts where this one left the grid idle
+}
+
+bool fill_op(PlanOpDev& o, int count, const LinearTarget* targets, const void* x, const char** why) {
+  o = PlanOpDev{};
+  o.count = static_cast<uint32_t>(count);
+  const Weight& w0 = *targets[0].w;
+  uint32_t rb = 0;
+  for (int i = 0; i < count; ++i) {
+    const Weight& w = *targets[i].w;
+    if (w.layout != kLayoutTiledI4) {
+      *why = "a weight is not in the tiled int4 / group-32 layout";
+      return false;
+    }
+    if (w.k != w0.k || w.scale_dtype != w0.scale_dtype) {
+      *why = "weights of one op differ in k or scale type";
+      return false;
+    }
+    o.w[i] = static_cast<const uint8_t*>(w.data);
+    o.bias[i] = targets[i].bias;
+    o.out[i] = targets[i].out;
+    o.n[i] = w.n;
+    o.rb_begin[i] = rb;
+    rb += w.n / 16;
+  }
+  for (int i = count; i <= kMaxMulti; ++i) o.rb_begin[i] = rb;
+  o.x = x;
+  o.k = w0.k;
+  o.chunks_per_row = w0.k / kChunkK;
+  o.row_blocks = rb;
+  return true;
 }
 
 }  // namespace
@@ -443,42 +532,19 @@ const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, 
   if (!plan->after.empty()) return "a host read was recorded before this linear; reads must come after the last op";
   if (m < 1 || m > 16) return "the fused plan kernel covers 1..16 activation rows";
   if (count < 1 || count > kMaxMulti) return "too many weights in one op";
-  PlanOpDev o = {};
-  o.count = static_cast<uint32_t>(count);
-  const Weight& w0 = *targets[0].w;
-  uint32_t rb = 0, n_total = 0;
-  for (int i = 0; i < count; ++i) {
-    const Weight& w = *targets[i].w;
-    if (w.layout != kLayoutTiledI4) return "a weight is not in the tiled int4 / group-32 layout";
-    if (w.k != w0.k || w.scale_dtype != w0.scale_dtype) return "weights of one op differ in k or scale type";
-    o.w[i] = static_cast<const uint8_t*>(w.data);
-    o.bias[i] = targets[i].bias;
-    o.out[i] = targets[i].out;
-    o.n[i] = w.n;
-    o.rb_begin[i] = rb;
-    rb += w.n / 16;
-    n_total += w.n;
-  }
-  for (int i = count; i <= kMaxMulti; ++i) o.rb_begin[i] = rb;
+  PlanOpDev o;
+  const char* why = "";
+  if (!fill_op(o, count, targets, x, &why)) return why;
+  const int scale_dtype = targets[0].w->scale_dtype;
   if (plan->ops.empty()) {
     plan->m = m;
     plan->x_dtype = x_dtype;
-    plan->scale_dtype = w0.scale_dtype;
-  } else if (plan->m != m || plan->x_dtype != x_dtype || plan->scale_dtype != w0.scale_dtype) {
+    plan->scale_dtype = scale_dtype;
+  } else if (plan->m != m || plan->x_dtype != x_dtype || plan->scale_dtype != scale_dtype) {
     return "ops of one plan must share m, the activation type and the scale type";
   }
-  o.x = x;
-  o.k = w0.k;
-  o.chunks_per_row = w0.k / kChunkK;
-  o.slabs = (o.chunks_per_row + kSlotChunks - 1) / kSlotChunks;
-  o.row_blocks = rb;
-  o.row_blocks_padded = (rb + kPlanWarps - 1) / kPlanWarps * kPlanWarps;
-  o.items = o.slabs * o.row_blocks_padded;
-  o.n_total = n_total;
+  plan->k_max = std::max(plan->k_max, o.k);
   plan->ops.push_back(o);
-  if (o.slabs > 1)
-    plan->partial_bytes = std::max<uint64_t>(plan->partial_bytes, static_cast<uint64_t>(o.slabs) * m * n_total * sizeof(float));
-  plan->max_row_blocks = std::max(plan->max_row_blocks, rb);
   return "";
 }
 
@@ -490,22 +556,15 @@ cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why) {
     *why = "the plan holds no linear op";
     return cudaErrorInvalidValue;
   }
-  if (plan->partial_bytes > env.workspace_bytes) {
-    *why = "the plan's split-K partial sums do not fit the context workspace (raise workspace_bytes in kq_init)";
-    return cudaErrorInvalidValue;
-  }
-  if (plan->max_row_blocks > env.counter_count) {
-    *why = "an op has more 16-row blocks than the context has arrival counters";
-    return cudaErrorInvalidValue;
-  }
-  cudaError_t e;
-  switch (plan->x_dtype) {
-    case KQ_F32: e = configure_x<float>(*plan, env.sm_count); break;
-    case KQ_F16: e = configure_x<__half>(*plan, env.sm_count); break;
-    case KQ_BF16: e = configure_x<__nv_bfloat16>(*plan, env.sm_count); break;
-    default: return cudaErrorInvalidValue;
-  }
+  bool fits = false;
+  cudaError_t e = configure_any(*plan, env.sm_count, &fits);
   if (e != cudaSuccess) return e;
+  if (!fits) {
+    *why = "the staged activations of the widest op (k * columns * 2 bytes) do not fit in shared memory next to the weight rings";
+    return cudaErrorInvalidValue;
+  }
+  uint32_t rot = 0;
+  for (PlanOpDev& o : plan->ops) shape_op(o, static_cast<uint32_t>(plan->grid), &rot);
   e = cudaMalloc(reinterpret_cast<void**>(&plan->ops_dev), plan->ops.size() * sizeof(PlanOpDev));
   if (e == cudaSuccess) e = cudaMemcpy(plan->ops_dev, plan->ops.data(), plan->ops.size() * sizeof(PlanOpDev), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&plan->grid_bar), sizeof(unsigned int));
@@ -529,8 +588,7 @@ cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
   p.ops = plan->ops_dev;
   p.op_count = static_cast<uint32_t>(plan->ops.size());
   p.m = plan->m;
-  p.partial = static_cast<float*>(env.workspace);
-  p.counters = env.counters;
+  p.xs_bytes = plan->xs_bytes;
   p.grid_bar = plan->grid_bar;
   p.error_flag = env.error_flag;
   p.status = plan->status_dev;
@@ -551,30 +609,23 @@ int plan_take_status(Plan* plan) {
   return s;
 }
 
-
 // ---- one linear, no allocation -------------------------------------------------------
-// Everything the fused kernel needs besides the caller's tensors lives in one file-scope
-// device array that every GPU loading this library carries until the process exits:
-//   [0, kStaticPartialBytes)        split-K partial sums
-//   then kStaticCounters words      per-row-block arrival counters (kept at zero between calls)
-//   then 256 B                      grid-barrier word
-//   then 256 B                      status word
-//   then 512 B                      the op descriptor
-constexpr size_t kStaticPartialBytes = size_t(4) << 20;
-constexpr uint32_t kStaticCounters = 8192;
-constexpr size_t kStaticCountersOff = kStaticPartialBytes;
-constexpr size_t kStaticBarOff = kStaticCountersOff + kStaticCounters * sizeof(unsigned int);
-constexpr size_t kStaticStatusOff = kStaticBarOff + 256;
-constexpr size_t kStaticOpOff = kStaticStatusOff + 256;
-constexpr size_t kStaticTotal = kStaticOpOff + 512;
+// Everything the fused kernel needs in global memory besides the caller's tensors lives
+// in one file-scope device array that every GPU loading this library carries until the
+// process exits:
+//   [0, 256)      grid-barrier word
+//   [256, 512)    status word
+//   [512, 1024)   the op descriptor
+constexpr size_t kStaticBarOff = 0;
+constexpr size_t kStaticStatusOff = 256;
+constexpr size_t kStaticOpOff = 512;
+constexpr size_t kStaticTotal = 4096;
 static_assert(sizeof(PlanOpDev) <= 512, "op descriptor outgrew its slot");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticTotal];
 
 constexpr int kStaticMaxDevices = 64;
 static unsigned char* g_static_base[kStaticMaxDevices] = {};  // device address of the array, per device
-
-uint64_t linear_static_limit_bytes() { return kStaticPartialBytes; }
 
 // In host code `g_static_scratch` is only a handle: the address a kernel may use comes
 // from cudaGetSymbolAddress, asked once per device with that device current.
@@ -587,9 +638,7 @@ static cudaError_t static_scratch_for_current_device(unsigned char** out) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess) return e;
-    // counters must start at zero (afterwards the kernel leaves them at zero itself)
-    e = cudaMemset(static_cast<unsigned char*>(ptr) + kStaticCountersOff, 0,
-                   kStaticCounters * sizeof(unsigned int));
+    e = cudaMemset(ptr, 0, kStaticTotal);
     if (e != cudaSuccess) return e;
     g_static_base[device] = static_cast<unsigned char*>(ptr);
   }
@@ -601,39 +650,12 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
                           uint32_t m, const char** why, int* device_status) {
   *why = "";
   *device_status = 0;
-  const Weight& w = *target.w;
-  if (w.layout != kLayoutTiledI4) {
-    *why = "the weight is not in the tiled int4 / group-32 layout";
-    return cudaErrorInvalidValue;
-  }
   if (m < 1 || m > 16) {
     *why = "1..16 activation rows";
     return cudaErrorInvalidValue;
   }
-  PlanOpDev o = {};
-  o.count = 1;
-  o.w[0] = static_cast<const uint8_t*>(w.data);
-  o.bias[0] = target.bias;
-  o.out[0] = target.out;
-  o.n[0] = w.n;
-  o.rb_begin[0] = 0;
-  for (int i = 1; i <= kMaxMulti; ++i) o.rb_begin[i] = w.n / 16;
-  o.x = x;
-  o.k = w.k;
-  o.chunks_per_row = w.k / kChunkK;
-  o.slabs = (o.chunks_per_row + kSlotChunks - 1) / kSlotChunks;
-  o.row_blocks = w.n / 16;
-  o.row_blocks_padded = (o.row_blocks + kPlanWarps - 1) / kPlanWarps * kPlanWarps;
-  o.items = o.slabs * o.row_blocks_padded;
-  o.n_total = w.n;
-  if (o.slabs > 1 && static_cast<uint64_t>(o.slabs) * m * w.n * sizeof(float) > kStaticPartialBytes) {
-    *why = "slabs * m * n * 4 bytes of partial sums exceed the 4 MiB static scratch";
-    return cudaErrorInvalidValue;
-  }
-  if (o.row_blocks > kStaticCounters) {
-    *why = "more than 8192 16-row blocks (n > 131072)";
-    return cudaErrorInvalidValue;
-  }
+  PlanOpDev o;
+  if (!fill_op(o, 1, &target, x, why)) return cudaErrorInvalidValue;
   unsigned char* base = nullptr;
   cudaError_t e = static_scratch_for_current_device(&base);
   if (e != cudaSuccess) return e;
@@ -641,14 +663,18 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
   Plan cfg;  // only carries the kernel choice; its vectors stay empty (no heap use)
   cfg.m = m;
   cfg.x_dtype = x_dtype;
-  cfg.scale_dtype = w.scale_dtype;
-  switch (x_dtype) {
-    case KQ_F32: e = configure_x<float>(cfg, env.sm_count); break;
-    case KQ_F16: e = configure_x<__half>(cfg, env.sm_count); break;
-    case KQ_BF16: e = configure_x<__nv_bfloat16>(cfg, env.sm_count); break;
-    default: return cudaErrorInvalidValue;
-  }
+  cfg.scale_dtype = target.w->scale_dtype;
+  cfg.k_max = o.k;
+  bool fits = false;
+  e = configure_any(cfg, env.sm_count, &fits);
   if (e != cudaSuccess) return e;
+  if (!fits) {
+    *why = "k * columns * 2 bytes of staged activations exceed the kernel's shared-memory budget "
+           "(columns = m for binary16 activations, 2 m for f32 / bf16)";
+    return cudaErrorInvalidValue;
+  }
+  uint32_t rot = 0;
+  shape_op(o, static_cast<uint32_t>(cfg.grid), &rot);
 
   e = cudaMemcpyAsync(base + kStaticOpOff, &o, sizeof(o), cudaMemcpyHostToDevice, env.stream);
   if (e != cudaSuccess) return e;
@@ -658,8 +684,7 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
   p.ops = reinterpret_cast<const PlanOpDev*>(base + kStaticOpOff);
   p.op_count = 1;
   p.m = m;
-  p.partial = reinterpret_cast<float*>(base);
-  p.counters = reinterpret_cast<unsigned int*>(base + kStaticCountersOff);
+  p.xs_bytes = cfg.xs_bytes;
   p.grid_bar = reinterpret_cast<unsigned int*>(base + kStaticBarOff);
   p.error_flag = env.error_flag;
   p.status = reinterpret_cast<int*>(base + kStaticStatusOff);

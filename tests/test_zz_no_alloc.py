@@ -41,8 +41,8 @@ def test_static_scratch_linear_matches_the_allocating_entry_point_twice_in_a_row
                 rep = oracle.allclose(got.cpu().numpy(), want.cpu().numpy(), atol=ATOL, rtol=RTOL)
                 assert rep["pass"], (call, repeat, rep)
             w.free()
-        # a request beyond the static array's size is refused, loudly, and runs nothing
-        n, k, m = 16384, 8192, 16  # 16 slabs * 16 * 16384 * 4 B = 16 MiB of partial sums
+        # a request beyond the documented limit is refused, loudly, and runs nothing
+        n, k, m = 16384, 8192, 16  # 8192 * 32 columns * 2 B = 512 KiB of staged activations
         data, scale = cases.synth_i4(n, k, seed=60)
         w = gpu.upload_weight("i4", data, scale, (n, k), 32)
         x = torch.zeros((m, k), device="cuda")
@@ -50,7 +50,7 @@ def test_static_scratch_linear_matches_the_allocating_entry_point_twice_in_a_row
         rc = L.kq_linear_static(gpu._ctx, w.handle, x.data_ptr(), kb.KQ_F32, torch.zeros(n, device="cuda").data_ptr(),
                                 out.data_ptr(), m)
         assert rc == 5  # KQ_ERR_UNSUPPORTED
-        assert b"4 MiB" in L.kq_last_error(gpu._ctx)
+        assert b"shared-memory budget" in L.kq_last_error(gpu._ctx)
         w.free()
     finally:
         gpu.destroy()
