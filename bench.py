@@ -174,7 +174,7 @@ def run_cuda(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = DecodeConfig()
     gpu = kb.acquire_gpu(local)
-    step = DecodeStep(gpu, cfg, args.batch, rank=rank, world=world, seed=0)
+    step = DecodeStep(gpu, cfg, args.batch, rank=rank, world=world, seed=0, fused=args.fused)
     step.record()
     rng = np.random.default_rng(1)
     step.host_x[...] = rng.standard_normal(step.host_x.shape).astype(np.float32)
@@ -244,13 +244,13 @@ def run_cuda(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
                 "workload": f"{cfg.name}: 32 layers x (q,k,v,o,gate,up,down) + lm_head, int4 g32, fp16 scales, batch {args.batch}",
-                "batch": args.batch, "activations": "f32", "parallelism": f"tp{world}",
+                "batch": args.batch, "activations": "f32", "parallelism": f"tp{world}", "replay": "fused plan kernel" if args.fused and world == 1 else "cuda graph, one launch per linear",
                 "weight_bytes": cfg.weight_bytes(), "l2": "inputs larger than L2 (4.2 GB of weights per step)"},
             "e2e": {"value": tok_s_e2e, "unit": "tok/s", "ms_per_step": per_step_e2e,
                     "h2d_bytes_per_step": int(step.x.numel() * 4),
                     "d2h_bytes_per_step": int(step.logits.numel() * 4)},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "qgemv_i4_kernel", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "plan_kernel" if args.fused else "qgemv_i4_kernel", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "frac_of_8tbs": achieved / 8000.0,
                          "launches_per_step": launches_per_step,
@@ -275,6 +275,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="kq", choices=["kq", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fused", action="store_true", help="replay the step as one persistent plan kernel instead of a CUDA graph of 129 launches")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
