@@ -219,6 +219,8 @@ def run_cuda(args):
     launches_before = gpu.launch_count
     ms_dev = timed(step.run_device, args.steps)
     launches = gpu.launch_count - launches_before
+    if world > 1:  # a torch CUDA graph replays the recorded launches; the library does not see the replays
+        launches = step.kernels_per_step * args.steps
     ms_e2e = timed(step.run_host, args.steps)
     t1 = time.time()
     clocks = sampler.stop(t0, t1) if rank == 0 else None
@@ -261,10 +263,16 @@ def run_cuda(args):
             "finite_outputs": logits_ok,
         }
         print(json.dumps(line))
+    if world > 1:
+        # Tearing down NCCL communicators that a CUDA graph still references can block;
+        # everything is measured and printed, so synchronise, flush and leave.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     step.close()
     gpu.destroy()
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main():
