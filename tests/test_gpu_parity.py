@@ -394,6 +394,29 @@ def test_column_and_row_shards_recompose(gpu, world, storage):
     assert_close(total.astype(np.float32), ref, "row")
 
 
+@pytest.mark.parametrize("storage", ["i4", "i8"])
+def test_library_shard_cutter_matches_the_host_mirror(gpu, storage):
+    import karume_b200 as kb
+    from karume_b200 import sharding
+    n, k, g, world = 128, 512, 32, 4
+    if storage == "i4":
+        data, scale = cases.synth_i4(n, k, seed=70)
+    else:
+        data, scale = cases.synth_i8(n, k, seed=70)
+        g = 0
+    for mode in (kb.KQ_SHARD_COLUMN, kb.KQ_SHARD_ROW):
+        for rank in range(world):
+            w = gpu.upload_weight(storage, data, scale, (n, k), g, shard=mode, rank=rank, world=world)
+            p, s, ns, ks = sharding.cut_shard(storage, data, scale, n, k, g or 32, mode, rank, world)
+            if storage == "i4":
+                want = oracle.decode_i4(p, (ns, ks), s.astype(np.float32), (ns, ks // 32), 32)
+            else:
+                want = oracle.decode_i8(p, (ns, ks), np.asarray(s, np.float32).reshape(-1), (ns, 1))
+            assert (w.n, w.k) == (ns, ks)
+            assert np.array_equal(bits(w.dequant().cpu().numpy()), bits(want))
+            w.free()
+
+
 # ---- failure behaviour: loud, typed, no alternate path -----------------------------------
 
 def test_storage_contract_violations_are_rejected(gpu):
