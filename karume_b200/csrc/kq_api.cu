@@ -32,7 +32,7 @@ struct kq_ctx {
   uint64_t workspace_bytes = 0;
   unsigned int* counters = nullptr;
   uint32_t counter_count = 0;
-  int* error_flag_host = nullptr;  // mapped, page-locked
+  int* error_flag_host = nullptr;  // mapped, page-locked: [0] activation range flag, [1] GEMM wait status
   int* error_flag_dev = nullptr;
   int sm_count = 0;
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
@@ -250,6 +250,16 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
     all_tiled = all_tiled && targets[i].w->layout == kq::kLayoutTiledI4;
     same_scale = same_scale && targets[i].w->scale_dtype == targets[0].w->scale_dtype;
   }
+  if (all_tiled && kq::qgemm_i4_supports(*targets[0].w, x_dtype, m)) {
+    // Prefill: bf16 activations, more than 16 rows -> tcgen05 GEMM, one launch per weight.
+    for (uint32_t i = 0; i < count; ++i) {
+      if (targets[i].w->n == 0) continue;
+      cudaError_t e = kq::launch_qgemm_i4(env, targets[i], reinterpret_cast<const void*>(x), m, ctx->error_flag_dev + 1);
+      if (e != cudaSuccess) return cuda_fail(ctx, e, "qgemm_i4 launch");
+      ctx->launches += 1;
+    }
+    return KQ_OK;
+  }
   if (all_tiled && same_scale) {
     // Tiled int4: row panels of at most 16 activation rows per launch.
     for (uint32_t m0 = 0; m0 < m; m0 += 16) {
@@ -322,9 +332,10 @@ int kq_init(int device, uint64_t workspace_bytes, kq_ctx** out) {
   if (e == cudaSuccess) e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ctx->counters), ctx->counter_count * sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMemset(ctx->counters, 0, ctx->counter_count * sizeof(unsigned int));
-  if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->error_flag_host), sizeof(int), cudaHostAllocMapped);
+  if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->error_flag_host), 2 * sizeof(int), cudaHostAllocMapped);
   if (e == cudaSuccess) {
-    *ctx->error_flag_host = 0;
+    ctx->error_flag_host[0] = 0;
+    ctx->error_flag_host[1] = 0;
     e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->error_flag_dev), ctx->error_flag_host, 0);
   }
   if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_start);
@@ -383,6 +394,11 @@ int kq_sync(kq_ctx* ctx) {
   if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_sync while a graph or plan is being recorded");
   DeviceGuard guard(ctx->device);
   KQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (reinterpret_cast<volatile int*>(ctx->error_flag_host)[1] != 0) {
+    const int code = reinterpret_cast<volatile int*>(ctx->error_flag_host)[1];
+    reinterpret_cast<volatile int*>(ctx->error_flag_host)[1] = 0;
+    return fail(ctx, KQ_ERR_TIMEOUT, "a bounded wait inside the tcgen05 GEMM gave up (stage %d); its outputs are not valid", code);
+  }
   for (auto& kv : ctx->plans) {
     const int st = kq::plan_take_status(kv.second);
     if (st != 0)

@@ -61,6 +61,13 @@ cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget*
 
 }  // namespace kq
 
+// ---- tcgen05 prefill GEMM (kq_qgemm_i4.cu): tiled int4 weights, bf16 activations, m > 16
+namespace kq {
+bool qgemm_i4_supports(const Weight& w, int x_dtype, uint32_t m);
+cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, const void* x, uint32_t m,
+                            int* status_word);
+}  // namespace kq
+
 // ---- fused plans (kq_plan.cu) -------------------------------------------------------
 namespace kq {
 struct Plan;

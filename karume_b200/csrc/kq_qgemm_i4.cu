@@ -1,0 +1,341 @@
+// qgemm_i4 — the prefill kernel of libkq: out[m, n] = x[m, k] . W[n, k]^T + bias for large m,
+// bf16 activations, W in the tiled int4 / group-32 layout (kq_common.cuh).
+//
+// Replaces the reference's large-M linear variants with in-kernel int4 dequant
+// (linear:v2:f32:reg64x32r4x4w8:wi4g32 and reg128x128r8x8w16 —
+// packages/runtime/src/kernels/gemm-geometry.ts:243-267, kernel text
+// packages/runtime/tests/fixtures/wgsl/linear_wi4_v4.wgsl): the same "dequantise a weight
+// tile into shared memory, then contract" structure, on Blackwell's tensor cores.
+//
+//   CTA tile 256 (m) x 256 (n), k-step 64, three shared-memory stages.
+//   warps 0-7  producers.  Per k-step they copy the 256 x 64 bf16 activation tile and
+//              dequantise the 256 x 64 weight tile (16 chunks of the tiled layout, read with
+//              128-bit loads) into the canonical K-major 128-byte-swizzled layout that
+//              tcgen05.mma reads.  A dequantised element is RNE_bf16(fround((u - 8) * s)):
+//              the reference's single-rounding f32 value (kq::dequant_i4's rule, computed
+//              here with an exact integer-to-float trick instead of a conversion), rounded
+//              once more to the tensor core's input type.  After the epilogue they also
+//              drain the accumulators.
+//   warp 8     one elected thread issues tcgen05.mma (M 128 x N 256 x K 16, bf16 in, f32
+//              accumulate) — two per k16 slice, one per 128-row half of the tile, sharing
+//              the weight operand — and commits each stage back to the producers.
+//   TMEM       512 columns: two 128 x 256 f32 accumulators.
+//
+// Parity contract (there is no bf16-compute variant in the reference): the result equals
+// the reference's math (f64-accumulate oracle) applied to the bf16 activations and to the
+// bf16-rounded dequantised weights, within atol 1e-5 + rtol 1e-3.
+//
+// Every mbarrier wait is bounded; a wait that gives up sets a status word and a CTA-wide
+// abort flag that makes all later waits return at once, so the kernel always reaches the
+// TMEM deallocation and exits.
+#include <cuda_bf16.h>
+
+#include "kq_common.cuh"
+#include "kq_internal.h"
+
+namespace kq {
+namespace {
+
+constexpr int kBM = 256, kBN = 256, kBK = 64, kStagesG = 3;
+constexpr int kProducerWarps = 8;
+constexpr int kGemmThreads = kProducerWarps * 32 + 32;
+constexpr uint32_t kATileBytes = kBM * kBK * 2;  // 32 KB
+constexpr uint32_t kBTileBytes = kBN * kBK * 2;  // 32 KB
+constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kWaitLimit = 1u << 24;
+
+struct GemmParams {
+  const uint8_t* w;  // tiled int4 weight
+  const __nv_bfloat16* x;
+  const float* bias;
+  float* out;
+  uint32_t m, n, k;
+  int* status;
+};
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+
+// Bounded wait.  Returns false (at once, if another thread already gave up) when the
+// barrier did not flip in time; the caller keeps going without blocking.
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                             int code) {
+  for (uint32_t spins = 0; spins < kWaitLimit; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  *reinterpret_cast<volatile int*>(status) = code;
+  return false;
+}
+
+// K-major, 128-byte swizzle: rows are 128 B, groups of 8 rows are 1024 B apart (SBO),
+// descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>(1) << 16) |
+         (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) |
+         (static_cast<uint64_t>(2) << 61);
+}
+
+// kind::f16 instruction descriptor: f32 accumulate, bf16 A and B, both K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t mma_m, uint32_t mma_n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((mma_n >> 3) << 17) | ((mma_m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 8 nibbles of one 32-bit word -> 8 bf16 (16 bytes, k ascending), each
+// RNE_bf16(fround((u - 8) * s)).  (word & (0xF << 4e)) | 0x4B000000 is the float
+// 2^23 + u * 16^e exactly; subtracting 2^23 + 8 * 16^e leaves (u - 8) * 16^e exactly, and
+// the power of sixteen is taken out of the scale (exact), so the one rounding of the
+// multiply is the reference's.
+__device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, float s) {
+  const float s1 = s * 0.0625f, s2 = s * 0.00390625f, s3 = s * 0.000244140625f;
+  const uint32_t hi = word >> 16;
+  float v[8];
+  v[0] = (__uint_as_float((word & 0x000Fu) | 0x4B000000u) - 8388616.0f) * s;
+  v[1] = (__uint_as_float((word & 0x00F0u) | 0x4B000000u) - 8388736.0f) * s1;
+  v[2] = (__uint_as_float((word & 0x0F00u) | 0x4B000000u) - 8390656.0f) * s2;
+  v[3] = (__uint_as_float((word & 0xF000u) | 0x4B000000u) - 8421376.0f) * s3;
+  v[4] = (__uint_as_float((hi & 0x000Fu) | 0x4B000000u) - 8388616.0f) * s;
+  v[5] = (__uint_as_float((hi & 0x00F0u) | 0x4B000000u) - 8388736.0f) * s1;
+  v[6] = (__uint_as_float((hi & 0x0F00u) | 0x4B000000u) - 8390656.0f) * s2;
+  v[7] = (__uint_as_float((hi & 0xF000u) | 0x4B000000u) - 8421376.0f) * s3;
+  uint4 out;
+  __nv_bfloat162 p;
+  p = __floats2bfloat162_rn(v[0], v[1]); out.x = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(v[2], v[3]); out.y = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(v[4], v[5]); out.z = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(v[6], v[7]); out.w = *reinterpret_cast<uint32_t*>(&p);
+  return out;
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// byte offset of 16-byte piece c (0..7) of tile row r in the swizzled K-major layout
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
+
+template <bool kScaleF16>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+qgemm_i4_kernel(const GemmParams p) {
+  constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
+  constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t raw_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
+  const uint32_t tiles = (raw_base + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  const uint32_t bars = tiles + kStagesG * kStageBytes;  // full[3], empty[3], accum
+  const uint32_t tmem_slot = bars + 64;
+  const uint32_t abort_addr = bars + 72;
+  uint8_t* generic_base = smem_raw + (tiles - raw_base);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + kStagesG * kStageBytes + 72);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + kStagesG * kStageBytes + 64);
+  (void)abort_addr;
+
+  const uint32_t n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+  const uint32_t ksteps = p.k / kBK;
+  const uint32_t chunks_per_row = p.k / kChunkK;
+
+  if (warp == kProducerWarps) {
+    if (lane == 0) {
+      for (int s = 0; s < kStagesG; ++s) {
+        mbar_init(bars + s * 8, kProducerWarps * 32);  // full: every producer thread arrives
+        mbar_init(bars + (kStagesG + s) * 8, 1);       // empty: one tcgen05.commit
+      }
+      mbar_init(bars + 2 * kStagesG * 8, 1);           // accumulators complete
+      *abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp < kProducerWarps) {
+    // ---------------- producers ----------------
+    const uint32_t tid = threadIdx.x;  // 0..255
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    for (uint32_t ks = 0; ks < ksteps; ++ks) {
+      const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
+      wait_bounded(bars + (kStagesG + s) * 8, phase ^ 1u, abort_flag, p.status, 1);
+      const uint32_t a_tile = tiles + s * kStageBytes, b_tile = a_tile + kATileBytes;
+      // activations: 256 rows x 8 pieces of 16 B; thread -> 8 pieces
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t piece = tid + i * 256u;
+        const uint32_t r = piece >> 3, c = piece & 7u;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (m0 + r < p.m)
+          v = *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m0 + r) * p.k + ks * kBK + c * 8);
+        sts128(a_tile + swz(r, c), v);
+      }
+      // weights: 16 chunks (16 rows x 64 k each); warp -> chunks 2*warp, 2*warp + 1
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const uint32_t rblock = warp * 2 + cc;           // row block inside the tile
+        const uint32_t row0 = n0 + rblock * 16u;         // first output channel of the block
+        uint4 wq = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // u = 8 -> value 0
+        float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (row0 < p.n) {
+          const uint8_t* chunk = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks) * kCB;
+          wq = *reinterpret_cast<const uint4*>(chunk + lane * 16);
+          if constexpr (kScaleF16) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(chunk + kChunkWeightBytes + g * 8);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            sc[0] = a.x; sc[1] = a.y; sc[2] = b.x; sc[3] = b.y;
+          } else {
+            const float4 raw = *reinterpret_cast<const float4*>(chunk + kChunkWeightBytes + g * 16);
+            sc[0] = raw.x; sc[1] = raw.y; sc[2] = raw.z; sc[3] = raw.w;
+          }
+        }
+        // words: row g grp 0 | row g+8 grp 0 | row g grp 1 | row g+8 grp 1; the lane's 8
+        // nibbles of a group are k = 8t .. 8t+7 of that group = 16-byte piece t (group 0)
+        // or 4 + t (group 1) of the 128-byte tile row
+        const uint32_t r_a = rblock * 16u + g, r_b = r_a + 8u;
+        sts128(b_tile + swz(r_a, t), dequant8_bf16(wq.x, sc[0]));
+        sts128(b_tile + swz(r_b, t), dequant8_bf16(wq.y, sc[1]));
+        sts128(b_tile + swz(r_a, 4u + t), dequant8_bf16(wq.z, sc[2]));
+        sts128(b_tile + swz(r_b, 4u + t), dequant8_bf16(wq.w, sc[3]));
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
+      mbar_arrive(bars + s * 8);
+    }
+    // ---------------- epilogue: accumulators -> out ----------------
+    wait_bounded(bars + 2 * kStagesG * 8, 0, abort_flag, p.status, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t half = warp >> 2, quarter = warp & 3u;  // accumulator (rows 0-127 / 128-255), lane quarter
+    const uint32_t row = m0 + half * 128u + quarter * 32u + lane;
+#pragma unroll 1
+    for (uint32_t cb = 0; cb < kBN / 32; ++cb) {
+      uint32_t v[32];
+      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + half * kBN + cb * 32u;
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+          "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+            "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+            "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+            "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const uint32_t col0 = n0 + cb * 32u;
+      if (row < p.m) {
+        float* dst = p.out + static_cast<size_t>(row) * p.n + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          if (col0 + j < p.n) {  // n is a multiple of 16, so a valid quad is wholly valid
+            const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+            float4 o;
+            o.x = __uint_as_float(v[j]) + b.x;
+            o.y = __uint_as_float(v[j + 1]) + b.y;
+            o.z = __uint_as_float(v[j + 2]) + b.z;
+            o.w = __uint_as_float(v[j + 3]) + b.w;
+            *reinterpret_cast<float4*>(dst + j) = o;
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t kIdesc = umma_idesc(128, kBN);
+    for (uint32_t ks = 0; ks < ksteps; ++ks) {
+      const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
+      const bool ok = wait_bounded(bars + s * 8, phase, abort_flag, p.status, 2);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) {
+        const uint32_t a_tile = tiles + s * kStageBytes, b_tile = a_tile + kATileBytes;
+        if (ok) {
+#pragma unroll
+          for (uint32_t kk = 0; kk < kBK / 16; ++kk) {
+            const uint64_t db = umma_desc(b_tile + kk * 32u);
+            const uint32_t acc = (ks | kk) != 0 ? 1u : 0u;
+            umma_bf16(tmem_base, umma_desc(a_tile + kk * 32u), db, kIdesc, acc);
+            umma_bf16(tmem_base + kBN, umma_desc(a_tile + 128u * 128u + kk * 32u), db, kIdesc, acc);
+          }
+        }
+        umma_commit(bars + (kStagesG + s) * 8);  // the stage is free once these MMAs have read it
+      }
+      __syncwarp();
+    }
+    if (lane == 0) umma_commit(bars + 2 * kStagesG * 8);  // all MMAs done: accumulators are final
+    __syncwarp();
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kProducerWarps) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+}  // namespace
+
+bool qgemm_i4_supports(const Weight& w, int x_dtype, uint32_t m) {
+  return w.layout == kLayoutTiledI4 && x_dtype == KQ_BF16 && m > 16;
+}
+
+cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, const void* x, uint32_t m,
+                            int* status_word) {
+  const Weight& w = *target.w;
+  if (w.layout != kLayoutTiledI4) return cudaErrorInvalidValue;
+  GemmParams p = {};
+  p.w = static_cast<const uint8_t*>(w.data);
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.bias = target.bias;
+  p.out = target.out;
+  p.m = m;
+  p.n = w.n;
+  p.k = w.k;
+  p.status = status_word;
+  const size_t smem = kStagesG * kStageBytes + 1024 + 256;
+  const dim3 grid((w.n + kBN - 1) / kBN, (m + kBM - 1) / kBM);
+  cudaError_t e;
+  if (w.scale_dtype == KQ_F16) {
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(qgemm_i4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return e;
+      configured = true;
+    }
+    qgemm_i4_kernel<true><<<grid, kGemmThreads, smem, env.stream>>>(p);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(qgemm_i4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return e;
+      configured = true;
+    }
+    qgemm_i4_kernel<false><<<grid, kGemmThreads, smem, env.stream>>>(p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace kq

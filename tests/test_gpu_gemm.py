@@ -1,0 +1,88 @@
+"""The tcgen05 prefill GEMM (bf16 activations, m > 16) against the oracle.
+
+There is no bf16-compute variant in the reference; parity is "reference math on
+pre-rounded inputs" (the construction the reference uses for its f16-compute variant,
+packages/runtime/src/kernels/gemm.ts:177-197): activations are bf16 values, weights are
+RNE_bf16 of the reference's dequantised value, accumulation is checked against the f64
+oracle at atol 1e-5 + rtol 1e-3.  The dequantised tile itself is checked bit for bit by
+multiplying with one-hot activations.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    import karume_b200 as kb
+    g = kb.acquire_gpu(0)
+    yield g
+    g.destroy()
+
+
+def dev(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("scale_dtype", ["f16", "f32"])
+def test_dequantised_tile_is_bit_exact_through_one_hot_activations(gpu, scale_dtype):
+    import torch
+    n, k = 272, 256  # two n tiles (the second ragged), four k steps
+    data, scale = cases.synth_i4(n, k, seed=3, scale_dtype=scale_dtype)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    x = torch.eye(k, dtype=torch.bfloat16, device="cuda")  # m = k = 256: row i picks column i of W
+    out = torch.full((k, n), float("nan"), device="cuda")
+    gpu.linear(x, w, torch.zeros(n, device="cuda"), out=out)
+    gpu.sync()
+    want = oracle.round_to_bf16(oracle.decode_i4(data, (n, k), np.asarray(scale, np.float32), (n, k // 32), 32))
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want.T))
+    w.free()
+
+
+@pytest.mark.parametrize("m,n,k", [(17, 272, 512), (65, 512, 256), (256, 256, 64), (300, 784, 1024), (513, 256, 2048)])
+def test_gemm_matches_oracle_on_prerounded_inputs(gpu, m, n, k):
+    import torch
+    data, scale = cases.synth_i4(n, k, seed=m + n)
+    rng = np.random.default_rng(m)
+    x = oracle.round_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    bias = rng.standard_normal(n).astype(np.float32)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    out = torch.full((m, n), float("nan"), device="cuda")
+    gpu.linear(dev(x).to(torch.bfloat16), w, dev(bias), out=out)
+    gpu.sync()
+    wq = oracle.round_to_bf16(oracle.decode_i4(data, (n, k), scale.astype(np.float32), (n, k // 32), 32))
+    ref = oracle.linear_f64(x, wq, bias)
+    rep = oracle.allclose(out.cpu().numpy(), ref, atol=1e-5, rtol=1e-3)
+    assert rep["pass"], rep
+    w.free()
+
+
+@pytest.mark.parametrize("m,k,n", [(512, 4096, 14336), (2048, 14336, 4096)])
+def test_prefill_benchmark_shapes_on_sampled_rows_and_columns(gpu, m, k, n):
+    import torch
+    data, scale = cases.synth_i4(n, k, seed=k)
+    rng = np.random.default_rng(7)
+    x = oracle.round_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    bias = rng.standard_normal(n).astype(np.float32)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    out = gpu.linear(dev(x).to(torch.bfloat16), w, dev(bias))
+    gpu.sync()
+    got = out.cpu().numpy()
+    assert np.all(np.isfinite(got))
+    rows = rng.choice(m, 48, replace=False)
+    cols = np.sort(rng.choice(n, 384, replace=False))
+    sub = data.reshape(n, k // 2)[cols]
+    wq = oracle.round_to_bf16(oracle.decode_i4(sub, (len(cols), k), scale.astype(np.float32)[cols], (len(cols), k // 32), 32))
+    ref = oracle.linear_f64(x[rows], wq, bias[cols])
+    rep = oracle.allclose(got[np.ix_(rows, cols)], ref, atol=1e-5, rtol=1e-3)
+    assert rep["pass"], rep
+    w.free()
