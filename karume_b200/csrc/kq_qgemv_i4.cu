@@ -52,7 +52,16 @@ namespace kq {
 namespace {
 
 constexpr int kWarps = 4;                // warps per CTA
-constexpr int kDepth = 4;                // chunks in flight per row block, in registers
+#ifndef KQ_TUNE_DEPTH
+#define KQ_TUNE_DEPTH 4
+#endif
+#ifndef KQ_TUNE_WANT
+#define KQ_TUNE_WANT 4
+#endif
+#ifndef KQ_TUNE_LATE_TRIGGER
+#define KQ_TUNE_LATE_TRIGGER 0
+#endif
+constexpr int kDepth = KQ_TUNE_DEPTH;    // chunks in flight per row block, in registers
 constexpr int kMaxCluster = 8;           // portable cluster size: K splits per row tile
 
 struct GemvParams {
@@ -118,7 +127,7 @@ qgemv_i4_kernel(const GemvParams p) {
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
 
-  pdl_launch_dependents();
+  if (!KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
 
   // which weight of the launch this CTA's row tile belongs to
   uint32_t wi = 0;
@@ -290,6 +299,8 @@ qgemv_i4_kernel(const GemvParams p) {
     done += slab_n;
   }
 
+  if (KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
+
   // ---- epilogue -----------------------------------------------------------------
   // lane owns, per row block and tile: rows g and g+8 of the block and activation rows
   //   with hi/lo columns : mm = 4*tile + t             (acc[..][0] row g, [1] row g+8)
@@ -372,7 +383,7 @@ cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const L
 
   // Split K over a cluster until the grid fills the machine (about four CTAs per SM);
   // a pure function of the shape, never autotuned.
-  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * 4u;
+  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * KQ_TUNE_WANT;
   uint32_t splits = 1;
   while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas &&
          splits * 2 <= chunks_per_row)
