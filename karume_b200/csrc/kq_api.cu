@@ -194,6 +194,22 @@ int upload_checked(kq_ctx* ctx, int storage, const void* payload, uint64_t paylo
     w->layout = kq::kLayoutTiledI4;
     w->data = tiled;
     w->scale = nullptr;
+  } else if (kq::tiled_i8_eligible(storage, n, k)) {
+    void* tiled = nullptr;
+    e = cudaMalloc(&tiled, payload_bytes);
+    if (e == cudaSuccess)
+      e = kq::launch_repack_i8(ctx->stream, static_cast<const uint8_t*>(d_payload), n, k, static_cast<uint8_t*>(tiled));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+      if (tiled) cudaFree(tiled);
+      cleanup();
+      return cuda_fail(ctx, e, "weight repack");
+    }
+    ctx->launches += 1;
+    cudaFree(d_payload);
+    w->layout = kq::kLayoutTiledI8;
+    w->data = tiled;
+    w->scale = d_scale;
   } else {
     e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
@@ -293,6 +309,18 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
       continue;
     }
     if (w.n == 0) continue;
+    if (w.layout == kq::kLayoutTiledI8) {
+      // Tiled int8: row panels of at most 16 activation rows per launch.
+      for (uint32_t m0 = 0; m0 < m; m0 += 16) {
+        const uint32_t mm = std::min<uint32_t>(16u, m - m0);
+        kq::LinearTarget panel{targets[i].w, targets[i].bias, targets[i].out + static_cast<size_t>(m0) * w.n};
+        const void* xp = reinterpret_cast<const uint8_t*>(x) + static_cast<size_t>(m0) * w.k * xb;
+        cudaError_t e8 = kq::launch_qgemv_i8(env, panel, xp, x_dtype, mm);
+        if (e8 != cudaSuccess) return cuda_fail(ctx, e8, "qgemv_i8 launch");
+        ctx->launches += 1;
+      }
+      continue;
+    }
     cudaError_t e = kq::launch_linear_generic(env, w, reinterpret_cast<const void*>(x), x_dtype,
                                               targets[i].bias, targets[i].out, m);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "generic linear launch");

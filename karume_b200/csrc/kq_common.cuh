@@ -90,6 +90,23 @@ __host__ __device__ __forceinline__ TiledPos tiled_i4_locate(uint32_t row, uint3
   return pos;
 }
 
+// ---- tiled int8 layout -------------------------------------------------------------
+// A weight [n, k] with n % 16 == 0 and k % 32 == 0 is stored as 512-byte chunks; chunk
+// (R, J) holds rows 16R..16R+15 and k 32J..32J+31.  Lane L = 4*g + t owns 16 B = four
+// 32-bit words, each four consecutive weights of one row with the sign bit flipped
+// (byte = q + 128, an unsigned value 0..255):
+//   word 0 = row 16R+g  , k 32J    + 4t .. +3        word 1 = row 16R+g+8, same k
+//   word 2 = row 16R+g  , k 32J+16 + 4t .. +3        word 3 = row 16R+g+8, same k
+// The per-output-channel scales stay a plain [n] array next to it.
+constexpr uint32_t kChunkK8 = 32;
+
+__host__ __device__ __forceinline__ size_t tiled_i8_locate(uint32_t row, uint32_t kk, uint32_t k) {
+  const uint32_t R = row / kTileRows, rr = row % kTileRows;
+  const uint32_t g = rr & 7u, upper = rr >> 3;
+  const uint32_t J = kk >> 5, in = kk & 31u, half = in >> 4, q = in & 15u, t = q >> 2, b = q & 3u;
+  return (static_cast<size_t>(R) * (k / kChunkK8) + J) * 512u + (4u * g + t) * 16u + (half * 2u + upper) * 4u + b;
+}
+
 // ---- misc ----------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -155,6 +155,36 @@ __global__ void dequant_native_i8(const int8_t* __restrict__ w, const void* __re
   }
 }
 
+template <bool kScaleF16>
+__global__ void dequant_tiled_i8(const uint8_t* __restrict__ tiled, const void* __restrict__ scale,
+                                 float* __restrict__ out, uint32_t n, uint32_t k) {
+  const size_t total = static_cast<size_t>(n) * k;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const uint32_t row = static_cast<uint32_t>(i / k), kk = static_cast<uint32_t>(i % k);
+    const int q = static_cast<int>(tiled[tiled_i8_locate(row, kk, k)]) - 128;  // stored with the sign bit flipped
+    out[i] = dequant_i8(q, load_scale<kScaleF16>(scale, row));
+  }
+}
+
+// One thread per 32-bit word of the destination.
+__global__ void repack_i8_tiled(const uint8_t* __restrict__ payload, uint32_t n, uint32_t k,
+                                uint8_t* __restrict__ tiled) {
+  const uint32_t chunks_per_block = k / kChunkK8;
+  const size_t total = static_cast<size_t>(n / kTileRows) * chunks_per_block * 128;
+  for (size_t it = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; it < total;
+       it += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t chunk = it >> 7;
+    const uint32_t item = static_cast<uint32_t>(it & 127u);
+    const uint32_t R = static_cast<uint32_t>(chunk / chunks_per_block), J = static_cast<uint32_t>(chunk % chunks_per_block);
+    const uint32_t lane = item >> 2, word = item & 3u, g = lane >> 2, t = lane & 3u;
+    const uint32_t row = R * kTileRows + g + ((word & 1u) ? 8u : 0u);
+    const uint32_t kk = J * kChunkK8 + (word >> 1) * 16u + t * 4u;
+    const uint32_t v = *reinterpret_cast<const uint32_t*>(payload + static_cast<size_t>(row) * k + kk);
+    *reinterpret_cast<uint32_t*>(tiled + chunk * 512u + lane * 16u + word * 4u) = v ^ 0x80808080u;
+  }
+}
+
 // ---- repack into the tiled layout ----------------------------------------------------
 // One thread per 32-bit word of the destination (weights first, then scales).
 __global__ void repack_i4_tiled(const uint8_t* __restrict__ payload, const uint8_t* __restrict__ scale,
@@ -251,6 +281,9 @@ cudaError_t launch_dequant(const LaunchEnv& env, const Weight& w, float* out) {
   if (w.storage == KQ_STORAGE_I4 && w.layout == kLayoutTiledI4) {
     if (f16s) dequant_tiled_i4<true><<<grid, block, 0, env.stream>>>(static_cast<const uint8_t*>(w.data), out, w.n, w.k);
     else dequant_tiled_i4<false><<<grid, block, 0, env.stream>>>(static_cast<const uint8_t*>(w.data), out, w.n, w.k);
+  } else if (w.storage == KQ_STORAGE_I8 && w.layout == kLayoutTiledI8) {
+    if (f16s) dequant_tiled_i8<true><<<grid, block, 0, env.stream>>>(static_cast<const uint8_t*>(w.data), w.scale, out, w.n, w.k);
+    else dequant_tiled_i8<false><<<grid, block, 0, env.stream>>>(static_cast<const uint8_t*>(w.data), w.scale, out, w.n, w.k);
   } else if (w.storage == KQ_STORAGE_I4) {
     const uint32_t gshift = log2_exact(w.group_size);
     if (f16s) dequant_native_i4<true><<<grid, block, 0, env.stream>>>(static_cast<const uint8_t*>(w.data), w.scale, out, w.n, w.k, gshift);
@@ -265,6 +298,18 @@ cudaError_t launch_dequant(const LaunchEnv& env, const Weight& w, float* out) {
 bool tiled_i4_eligible(int storage, uint32_t n, uint32_t k, uint32_t group_size) {
   return storage == KQ_STORAGE_I4 && group_size == 32 && n > 0 && k > 0 && n % kTileRows == 0 &&
          k % kChunkK == 0;
+}
+
+bool tiled_i8_eligible(int storage, uint32_t n, uint32_t k) {
+  return storage == KQ_STORAGE_I8 && n > 0 && k > 0 && n % kTileRows == 0 && k % kChunkK8 == 0;
+}
+
+cudaError_t launch_repack_i8(cudaStream_t stream, const uint8_t* payload, uint32_t n, uint32_t k, uint8_t* tiled) {
+  const size_t total = static_cast<size_t>(n / kTileRows) * (k / kChunkK8) * 128;
+  const int block = 256;
+  const int grid = static_cast<int>(std::min<size_t>((total + block - 1) / block, 148u * 32u));
+  repack_i8_tiled<<<grid, block, 0, stream>>>(payload, n, k, tiled);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_repack_i4(cudaStream_t stream, const uint8_t* payload, const void* scale,

@@ -10,7 +10,8 @@ namespace kq {
 
 enum Layout : int {
   kLayoutNative = 0,  // payload and scale exactly as uploaded (row-major)
-  kLayoutTiledI4 = 1  // chunked int4 layout described in kq_common.cuh (group size 32)
+  kLayoutTiledI4 = 1,  // chunked int4 layout described in kq_common.cuh (group size 32)
+  kLayoutTiledI8 = 2   // chunked int8 layout described in kq_common.cuh (scales stay [n])
 };
 
 struct Weight {
@@ -52,6 +53,12 @@ cudaError_t launch_dequant(const LaunchEnv& env, const Weight& w, float* out);
 bool tiled_i4_eligible(int storage, uint32_t n, uint32_t k, uint32_t group_size);
 cudaError_t launch_repack_i4(cudaStream_t stream, const uint8_t* payload, const void* scale,
                              int scale_dtype, uint32_t n, uint32_t k, uint8_t* tiled);
+
+// Tiled int8 layout.
+bool tiled_i8_eligible(int storage, uint32_t n, uint32_t k);
+cudaError_t launch_repack_i8(cudaStream_t stream, const uint8_t* payload, uint32_t n, uint32_t k, uint8_t* tiled);
+cudaError_t launch_qgemv_i8(const LaunchEnv& env, const LinearTarget& target, const void* x, int x_dtype,
+                            uint32_t m);
 
 // Tensor-core GEMV for the tiled int4 layout, m <= 16.  Returns cudaErrorInvalidValue
 // when the request needs more workspace than the context owns.

@@ -137,6 +137,41 @@ def test_i8_dequant_all_256_values_in_all_4_lanes(gpu):
     w.free()
 
 
+def test_i8_tiled_layout_dequant_bit_exact(gpu):
+    """n % 16 == 0, k % 32 == 0 -> the tiled int8 layout; every byte value in every lane position."""
+    n, k = 64, 128
+    q = ((np.arange(n)[:, None] * 37 + np.arange(k)[None, :] * 3) % 256 - 128).astype(np.int8)
+    for pos in range(16):
+        assert len(set(q.reshape(-1)[pos::16].tolist())) == 256
+    scale = (0.1 + np.arange(n) * 0.003).astype(np.float32)
+    for sc in (scale, (scale * 0.01).astype(np.float16)):
+        w = gpu.upload_weight("i8", q, sc, (n, k))
+        assert w.resident_bytes == q.nbytes + sc.nbytes
+        want = oracle.decode_i8(q, (n, k), np.asarray(sc, np.float32), (n, 1))
+        assert np.array_equal(bits(w.dequant().cpu().numpy()), bits(want))
+        w.free()
+
+
+@pytest.mark.parametrize("xdt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 33])
+def test_tiled_int8_gemv_dtypes_and_ragged_m(gpu, xdt, m):
+    import torch
+    n, k = 272, 608  # ragged last CTA tile; 19 chunks of 32 k
+    q, scale = cases.synth_i8(n, k, seed=m)
+    rng = np.random.default_rng(m + 5)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    if xdt == "f16":
+        x = oracle.round_to_f16(x)
+    elif xdt == "bf16":
+        x = oracle.round_to_bf16(x)
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[xdt]
+    w = gpu.upload_weight("i8", q, scale, (n, k))
+    ref = oracle.linear_i8(x, q, scale.astype(np.float32), bias, n, k)
+    assert_close(run_linear(gpu, w, x, bias, dtype=tdt), ref, f"i8 {xdt} m={m}")
+    w.free()
+
+
 def test_exporter_vectors_dequant_bit_exact_on_gpu(gpu, golden_dir):
     import os
     z = np.load(os.path.join(golden_dir, "exporter_vectors.npz"))
