@@ -174,7 +174,7 @@ def run_cuda(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = DecodeConfig()
     gpu = kb.acquire_gpu(local)
-    step = DecodeStep(gpu, cfg, args.batch, rank=rank, world=world, seed=0, fused=args.fused)
+    step = DecodeStep(gpu, cfg, args.batch, rank=rank, world=world, seed=0, fused=args.fused, exchange=args.exchange)
     step.record()
     rng = np.random.default_rng(1)
     step.host_x[...] = rng.standard_normal(step.host_x.shape).astype(np.float32)
@@ -219,7 +219,7 @@ def run_cuda(args):
     launches_before = gpu.launch_count
     ms_dev = timed(step.run_device, args.steps)
     launches = gpu.launch_count - launches_before
-    if world > 1:  # a torch CUDA graph replays the recorded launches; the library does not see the replays
+    if world > 1 and args.exchange == "nccl":  # a torch CUDA graph replays the launches; the library does not see them
         launches = step.kernels_per_step * args.steps
     ms_e2e = timed(step.run_host, args.steps)
     t1 = time.time()
@@ -246,7 +246,7 @@ def run_cuda(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
                 "workload": f"{cfg.name}: 32 layers x (q,k,v,o,gate,up,down) + lm_head, int4 g32, fp16 scales, batch {args.batch}",
-                "batch": args.batch, "activations": "f32", "parallelism": f"tp{world}", "replay": "fused plan kernel" if args.fused and world == 1 else "cuda graph, one launch per linear",
+                "batch": args.batch, "activations": "f32", "parallelism": f"tp{world}", "exchange": (args.exchange if world > 1 else None), "replay": "fused plan kernel" if args.fused and world == 1 else "cuda graph, one launch per linear",
                 "weight_bytes": cfg.weight_bytes(), "l2": "inputs larger than L2 (4.2 GB of weights per step)"},
             "e2e": {"value": tok_s_e2e, "unit": "tok/s", "ms_per_step": per_step_e2e,
                     "h2d_bytes_per_step": int(step.x.numel() * 4),
@@ -283,6 +283,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="kq", choices=["kq", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="kq", choices=["kq", "nccl"], help="all-reduce used when --gpus > 1")
     ap.add_argument("--fused", action="store_true", help="replay the step as one persistent plan kernel instead of a CUDA graph of 129 launches")
     args = ap.parse_args()
     if args.impl == "reference":

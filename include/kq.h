@@ -225,6 +225,20 @@ KQ_API int kq_plan_end(kq_ctx* ctx, kq_plan* out);
 KQ_API int kq_plan_launch(kq_ctx* ctx, kq_plan plan);
 KQ_API int kq_plan_free(kq_ctx* ctx, kq_plan plan);
 
+/* ---- tensor-parallel exchange --------------------------------------------------------
+ * No reference counterpart (karume is single-device).  One process per GPU: every rank
+ * calls kq_comm_create (allocates its exchange buffer and returns a 64-byte IPC handle),
+ * the host gathers the handles of all ranks in rank order by any means, and every rank
+ * passes the concatenation (world * 64 bytes) to kq_comm_connect.  kq_all_reduce then sums
+ * an f32 vector of up to max_bytes (<= 512 KiB) over the ranks in place, with one kernel
+ * that reads the peers' buffers over NVLink; the sum is taken in rank order, so all ranks
+ * hold the same bits.  Every rank must issue the same sequence of kq_all_reduce calls.
+ * The kernel can be captured in a CUDA graph.  A peer that does not arrive within the
+ * kernel's bounded wait is reported by the next kq_sync as KQ_ERR_TIMEOUT. */
+KQ_API int kq_comm_create(kq_ctx* ctx, uint32_t rank, uint32_t world, uint64_t max_bytes, uint8_t* out_handle);
+KQ_API int kq_comm_connect(kq_ctx* ctx, const uint8_t* all_handles);
+KQ_API int kq_all_reduce(kq_ctx* ctx, uint64_t f32_dptr, uint64_t count);
+
 /* ---- timing ---------------------------------------------------------------------
  * CUDA events on the context's stream.  Replaces the reference's opt-in
  * timestamp-query diagnostics (packages/runtime/src/gpu/submit.ts:180-194). */

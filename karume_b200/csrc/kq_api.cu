@@ -25,6 +25,7 @@ struct kq_ctx {
   std::unordered_map<uint64_t, uint64_t> graph_kernels;  // kernel nodes per recorded graph
   std::unordered_map<uint64_t, kq::Plan*> plans;
   kq::Plan* recording = nullptr;  // non-null between kq_plan_begin and kq_plan_end
+  kq::Comm* comm = nullptr;       // tensor-parallel exchange, if created
   std::string recording_refusal;  // first reason an op could not be fused
   uint64_t capture_mark = 0;
   uint64_t next_handle = 1;
@@ -384,6 +385,7 @@ void kq_destroy(kq_ctx* ctx) {
   if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
   for (auto& kv : ctx->graphs) cudaGraphExecDestroy(kv.second);
   for (auto& kv : ctx->plans) kq::plan_destroy(kv.second);
+  if (ctx->comm) kq::comm_destroy(ctx->comm);
   if (ctx->recording) kq::plan_destroy(ctx->recording);
   for (auto& kv : ctx->weights) {
     if (kv.second->data) cudaFree(kv.second->data);
@@ -427,6 +429,8 @@ int kq_sync(kq_ctx* ctx) {
     reinterpret_cast<volatile int*>(ctx->error_flag_host)[1] = 0;
     return fail(ctx, KQ_ERR_TIMEOUT, "a bounded wait inside the tcgen05 GEMM gave up (stage %d); its outputs are not valid", code);
   }
+  if (ctx->comm && kq::comm_take_status(ctx->comm) != 0)
+    return fail(ctx, KQ_ERR_TIMEOUT, "kq_all_reduce: a peer did not arrive within the bounded wait; the outputs are not valid");
   for (auto& kv : ctx->plans) {
     const int st = kq::plan_take_status(kv.second);
     if (st != 0)
@@ -724,6 +728,44 @@ int kq_linear_static(kq_ctx* ctx, kq_weight h, uint64_t x_dptr, int x_dtype, uin
     *reinterpret_cast<volatile int*>(ctx->error_flag_host) = 0;
     return fail(ctx, KQ_ERR_RANGE, "kq_linear_static: an activation had a finite magnitude above 65504");
   }
+  return KQ_OK;
+}
+
+int kq_comm_create(kq_ctx* ctx, uint32_t rank, uint32_t world, uint64_t max_bytes, uint8_t* out_handle) {
+  if (!ctx || !out_handle) return fail(ctx, KQ_ERR_BAD_ARG, "kq_comm_create: null argument");
+  if (ctx->comm) return fail(ctx, KQ_ERR_STATE, "kq_comm_create: this context already has an exchange");
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = cudaSuccess;
+  const char* why = "";
+  ctx->comm = kq::comm_create(rank, world, max_bytes, out_handle, &e, &why);
+  if (!ctx->comm) {
+    if (why[0] != 0) return fail(ctx, KQ_ERR_BAD_ARG, "kq_comm_create: %s", why);
+    return cuda_fail(ctx, e, "kq_comm_create");
+  }
+  return KQ_OK;
+}
+
+int kq_comm_connect(kq_ctx* ctx, const uint8_t* all_handles) {
+  if (!ctx || !all_handles) return fail(ctx, KQ_ERR_BAD_ARG, "kq_comm_connect: null argument");
+  if (!ctx->comm) return fail(ctx, KQ_ERR_STATE, "kq_comm_connect before kq_comm_create");
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = kq::comm_connect(ctx->comm, all_handles);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "kq_comm_connect (cudaIpcOpenMemHandle)");
+  return KQ_OK;
+}
+
+int kq_all_reduce(kq_ctx* ctx, uint64_t dptr, uint64_t count) {
+  if (!ctx || !dptr) return fail(ctx, KQ_ERR_BAD_ARG, "kq_all_reduce: null argument");
+  if (!kq::comm_connected(ctx->comm)) return fail(ctx, KQ_ERR_STATE, "kq_all_reduce before kq_comm_connect");
+  if (dptr & 15u) return fail(ctx, KQ_ERR_BAD_ARG, "kq_all_reduce: the vector must be 16-byte aligned");
+  if (count * sizeof(float) > kq::comm_max_bytes(ctx->comm))
+    return fail(ctx, KQ_ERR_SHAPE, "kq_all_reduce: %llu bytes exceed the %llu the exchange was created for",
+                (unsigned long long)(count * sizeof(float)), (unsigned long long)kq::comm_max_bytes(ctx->comm));
+  if (count == 0) return KQ_OK;
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = kq::comm_all_reduce(ctx->comm, ctx->stream, reinterpret_cast<float*>(dptr), count);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "kq_all_reduce launch");
+  ctx->launches += 1;
   return KQ_OK;
 }
 

@@ -91,3 +91,16 @@ int plan_take_status(Plan* plan);
 cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, const void* x, int x_dtype,
                           uint32_t m, const char** why, int* device_status);
 }  // namespace kq
+
+// ---- peer-memory all-reduce (kq_comm.cu) ----------------------------------------------
+namespace kq {
+struct Comm;
+Comm* comm_create(uint32_t rank, uint32_t world, uint64_t max_bytes, uint8_t* handle_out, cudaError_t* err,
+                  const char** why);
+cudaError_t comm_connect(Comm* c, const uint8_t* all_handles);
+void comm_destroy(Comm* c);
+bool comm_connected(const Comm* c);
+uint64_t comm_max_bytes(const Comm* c);
+cudaError_t comm_all_reduce(Comm* c, cudaStream_t stream, float* data, uint64_t count);
+int comm_take_status(Comm* c);
+}  // namespace kq

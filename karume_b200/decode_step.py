@@ -25,8 +25,9 @@ karume itself is single-device (packages/runtime/src/gpu/device.ts:1182-1218); t
 sharding follows the usual column-then-row scheme so that one exchange per row-parallel
 matmul is the only communication.  With world == 1 the step is recorded as a fused plan
 (kq_plan_*: one persistent kernel for all 129 linears) or, with fused=False, as a CUDA
-graph of one launch per linear (kq_graph_*); with world > 1 the recording goes through a
-torch CUDA graph so that the NCCL all-reduce is captured with the kernels.
+graph of one launch per linear (kq_graph_*).  With world > 1 the exchange is libkq's own
+one-shot all-reduce over NVLink peer memory (kq_all_reduce, recorded in the same CUDA graph)
+or, with exchange="nccl", torch.distributed.all_reduce captured in a torch CUDA graph.
 """
 from __future__ import annotations
 
@@ -103,7 +104,8 @@ class DecodeStep:
     """Resident sharded weights + activation buffers + a recorded plan of one step."""
 
     def __init__(self, gpu: Gpu, cfg: DecodeConfig, batch: int, rank: int = 0, world: int = 1,
-                 seed: int = 0, keep_host_weights: bool = False, process_group=None, fused: bool = True):
+                 seed: int = 0, keep_host_weights: bool = False, process_group=None, fused: bool = True,
+                 exchange: str = "kq"):
         import torch
         if not 1 <= batch <= 16:
             raise ValueError("decode batch is 1..16 token rows")
@@ -113,6 +115,10 @@ class DecodeStep:
         self.gpu, self.cfg, self.batch, self.rank, self.world = gpu, cfg, batch, rank, world
         self.pg = process_group
         self.fused = fused and world == 1
+        # "kq": libkq's one-shot peer-memory all-reduce; "nccl": torch.distributed.all_reduce
+        self.exchange = exchange if world > 1 else "none"
+        if self.exchange == "kq":
+            gpu.connect_ranks(rank, world, batch * cfg.hidden * 4, process_group)
         self.torch = torch
         dev = gpu.device
         self.weights = {}
@@ -149,7 +155,9 @@ class DecodeStep:
         return self.zero_bias[:n]
 
     def _all_reduce(self, t):
-        if self.world > 1:
+        if self.exchange == "kq":
+            self.gpu.all_reduce(t)
+        elif self.world > 1:
             self.torch.distributed.all_reduce(t, group=self.pg)
 
     def enqueue(self) -> None:
@@ -185,7 +193,7 @@ class DecodeStep:
         self._pl, hl = self._pinned(self.logits.numel() * 4)
         self.host_x = hx.view(np.float32).reshape(tuple(self.x.shape))
         self.host_logits = hl.view(np.float32).reshape(tuple(self.logits.shape))
-        if self.world == 1:
+        if self.exchange != "nccl":
             stream = torch.cuda.Stream(self.gpu.device)
             self.gpu.use_stream(stream)
             self._stream = stream
@@ -225,7 +233,7 @@ class DecodeStep:
 
     def run_device(self) -> None:
         """One step with x already resident; asynchronous."""
-        if self.world == 1:
+        if self.exchange != "nccl":
             self._launch(self.plan)
         else:
             with self.torch.cuda.stream(self._stream):
@@ -233,7 +241,7 @@ class DecodeStep:
 
     def run_host(self) -> None:
         """One step through host buffers: host_x -> device, step, logits -> host_logits; asynchronous."""
-        if self.world == 1:
+        if self.exchange != "nccl":
             self._launch(self.plan_host)
         else:
             with self.torch.cuda.stream(self._stream):

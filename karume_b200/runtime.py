@@ -224,6 +224,29 @@ class Gpu:
     def plan_free(self, plan: int) -> None:
         self._check(L.kq_plan_free(self._ctx, plan))
 
+    # -- tensor-parallel exchange ---------------------------------------------------------
+    def connect_ranks(self, rank: int, world: int, max_bytes: int, process_group=None) -> None:
+        """Creates this rank's exchange buffer and connects it to every peer's; the 64-byte
+        IPC handles travel through torch.distributed (plumbing only)."""
+        torch = _torch()
+        import torch.distributed as dist
+        handle = (ctypes.c_uint8 * 64)()
+        self._check(L.kq_comm_create(self._ctx, rank, world, int(max_bytes), handle))
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine, group=process_group)
+        blob = bytes(torch.cat(gathered).cpu().numpy().tobytes())
+        buf = (ctypes.c_uint8 * len(blob)).from_buffer_copy(blob)
+        self._check(L.kq_comm_connect(self._ctx, buf))
+        dist.barrier(group=process_group)
+
+    def all_reduce(self, t) -> None:
+        """In-place f32 sum over the connected ranks (one peer-memory kernel, rank-ordered)."""
+        torch = _torch()
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise KqError(1, "all_reduce takes a contiguous f32 tensor")
+        self._check(L.kq_all_reduce(self._ctx, t.data_ptr(), t.numel()))
+
     def timer_start(self) -> None:
         self._check(L.kq_timer_start(self._ctx))
 
