@@ -30,6 +30,8 @@
 // TMEM deallocation and exits.
 #include <cuda_bf16.h>
 
+#include <type_traits>
+
 #include "kq_common.cuh"
 #include "kq_internal.h"
 
@@ -181,49 +183,74 @@ qgemm_i4_kernel(const GemmParams p) {
     // ---------------- producers ----------------
     const uint32_t tid = threadIdx.x;  // 0..255
     const uint32_t g = lane >> 2, t = lane & 3u;
+    // The lane's two weight chunks (and their scales) of a k-step, fetched one k-step ahead.
+    uint4 wq_next[2];
+    typename std::conditional<kScaleF16, uint2, uint4>::type sc_next[2];
+    auto fetch_weights = [&](uint32_t ks) {
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const uint32_t row0 = n0 + (warp * 2 + cc) * 16u;  // first output channel of the row block
+        wq_next[cc] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // u = 8 -> value 0
+        if constexpr (kScaleF16) sc_next[cc] = make_uint2(0, 0);
+        else sc_next[cc] = make_uint4(0, 0, 0, 0);
+        if (row0 < p.n && ks < ksteps) {
+          const uint8_t* chunk = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks) * kCB;
+          wq_next[cc] = *reinterpret_cast<const uint4*>(chunk + lane * 16);
+          if constexpr (kScaleF16) sc_next[cc] = *reinterpret_cast<const uint2*>(chunk + kChunkWeightBytes + g * 8);
+          else sc_next[cc] = *reinterpret_cast<const uint4*>(chunk + kChunkWeightBytes + g * 16);
+        }
+      }
+    };
+    fetch_weights(0);
     for (uint32_t ks = 0; ks < ksteps; ++ks) {
       const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
       wait_bounded(bars + (kStagesG + s) * 8, phase ^ 1u, abort_flag, p.status, 1);
       const uint32_t a_tile = tiles + s * kStageBytes, b_tile = a_tile + kATileBytes;
-      // activations: 256 rows x 8 pieces of 16 B; thread -> 8 pieces
+      // activations: 256 rows x 8 pieces of 16 B, copied asynchronously straight into the
+      // swizzled tile (rows past m are zero-filled); the copy flies while we dequantise
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const uint32_t piece = tid + i * 256u;
         const uint32_t r = piece >> 3, c = piece & 7u;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (m0 + r < p.m)
-          v = *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m0 + r) * p.k + ks * kBK + c * 8);
-        sts128(a_tile + swz(r, c), v);
+        const bool in_range = m0 + r < p.m;
+        const __nv_bfloat16* src = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + ks * kBK + c * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_tile + swz(r, c)), "l"(src),
+                     "r"(in_range ? 16u : 0u) : "memory");
       }
-      // weights: 16 chunks (16 rows x 64 k each); warp -> chunks 2*warp, 2*warp + 1
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      // weights: this k-step's chunks are already in registers; fetch the next k-step's
+      uint4 wq[2];
+      float sc[2][4];
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        const uint32_t rblock = warp * 2 + cc;           // row block inside the tile
-        const uint32_t row0 = n0 + rblock * 16u;         // first output channel of the block
-        uint4 wq = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // u = 8 -> value 0
-        float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (row0 < p.n) {
-          const uint8_t* chunk = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks) * kCB;
-          wq = *reinterpret_cast<const uint4*>(chunk + lane * 16);
-          if constexpr (kScaleF16) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(chunk + kChunkWeightBytes + g * 8);
-            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-            sc[0] = a.x; sc[1] = a.y; sc[2] = b.x; sc[3] = b.y;
-          } else {
-            const float4 raw = *reinterpret_cast<const float4*>(chunk + kChunkWeightBytes + g * 16);
-            sc[0] = raw.x; sc[1] = raw.y; sc[2] = raw.z; sc[3] = raw.w;
-          }
+        wq[cc] = wq_next[cc];
+        if constexpr (kScaleF16) {
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&sc_next[cc].x));
+          const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&sc_next[cc].y));
+          sc[cc][0] = a.x; sc[cc][1] = a.y; sc[cc][2] = b.x; sc[cc][3] = b.y;
+        } else {
+          sc[cc][0] = __uint_as_float(sc_next[cc].x); sc[cc][1] = __uint_as_float(sc_next[cc].y);
+          sc[cc][2] = __uint_as_float(sc_next[cc].z); sc[cc][3] = __uint_as_float(sc_next[cc].w);
         }
+      }
+      fetch_weights(ks + 1);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
         // words: row g grp 0 | row g+8 grp 0 | row g grp 1 | row g+8 grp 1; the lane's 8
         // nibbles of a group are k = 8t .. 8t+7 of that group = 16-byte piece t (group 0)
-        // or 4 + t (group 1) of the 128-byte tile row
-        const uint32_t r_a = rblock * 16u + g, r_b = r_a + 8u;
-        sts128(b_tile + swz(r_a, t), dequant8_bf16(wq.x, sc[0]));
-        sts128(b_tile + swz(r_b, t), dequant8_bf16(wq.y, sc[1]));
-        sts128(b_tile + swz(r_a, 4u + t), dequant8_bf16(wq.z, sc[2]));
-        sts128(b_tile + swz(r_b, 4u + t), dequant8_bf16(wq.w, sc[3]));
+        // or 4 + t (group 1) of the 128-byte tile row.  Odd g stores group 1 first: the 8
+        // lanes of a shared-memory phase (two values of g, four of t) then hit 8 different
+        // 16-byte columns of the swizzled rows.
+        const uint32_t r_a = (warp * 2 + cc) * 16u + g, r_b = r_a + 8u;
+        const uint4 a0 = dequant8_bf16(wq[cc].x, sc[cc][0]), a1 = dequant8_bf16(wq[cc].z, sc[cc][2]);
+        const uint4 b0 = dequant8_bf16(wq[cc].y, sc[cc][1]), b1 = dequant8_bf16(wq[cc].w, sc[cc][3]);
+        const bool odd = (g & 1u) != 0;
+        sts128(b_tile + swz(r_a, odd ? 4u + t : t), odd ? a1 : a0);
+        sts128(b_tile + swz(r_a, odd ? t : 4u + t), odd ? a0 : a1);
+        sts128(b_tile + swz(r_b, odd ? 4u + t : t), odd ? b1 : b0);
+        sts128(b_tile + swz(r_b, odd ? t : 4u + t), odd ? b0 : b1);
       }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
       mbar_arrive(bars + s * 8);
     }
