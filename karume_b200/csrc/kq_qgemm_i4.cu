@@ -39,7 +39,12 @@ namespace kq {
 namespace {
 
 constexpr int kBM = 256, kBN = 256, kBK = 64, kStagesG = 3;
-constexpr int kProducerWarps = 8;
+#ifndef KQ_GEMM_PRODUCER_WARPS
+#define KQ_GEMM_PRODUCER_WARPS 16
+#endif
+constexpr int kProducerWarps = KQ_GEMM_PRODUCER_WARPS;  // 8 or 16
+constexpr int kChunksPerWarp = 16 / kProducerWarps;      // 16-row weight chunks per warp and k-step
+constexpr int kAPiecesPerThread = 2048 / (kProducerWarps * 32);
 constexpr int kGemmThreads = kProducerWarps * 32 + 32;
 constexpr uint32_t kATileBytes = kBM * kBK * 2;  // 32 KB
 constexpr uint32_t kBTileBytes = kBN * kBK * 2;  // 32 KB
@@ -181,15 +186,15 @@ qgemm_i4_kernel(const GemmParams p) {
 
   if (warp < kProducerWarps) {
     // ---------------- producers ----------------
-    const uint32_t tid = threadIdx.x;  // 0..255
+    const uint32_t tid = threadIdx.x;  // producer thread index
     const uint32_t g = lane >> 2, t = lane & 3u;
     // The lane's two weight chunks (and their scales) of a k-step, fetched one k-step ahead.
-    uint4 wq_next[2];
-    typename std::conditional<kScaleF16, uint2, uint4>::type sc_next[2];
+    uint4 wq_next[kChunksPerWarp];
+    typename std::conditional<kScaleF16, uint2, uint4>::type sc_next[kChunksPerWarp];
     auto fetch_weights = [&](uint32_t ks) {
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const uint32_t row0 = n0 + (warp * 2 + cc) * 16u;  // first output channel of the row block
+      for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+        const uint32_t row0 = n0 + (warp * kChunksPerWarp + cc) * 16u;  // first output channel of the row block
         wq_next[cc] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // u = 8 -> value 0
         if constexpr (kScaleF16) sc_next[cc] = make_uint2(0, 0);
         else sc_next[cc] = make_uint4(0, 0, 0, 0);
@@ -209,8 +214,8 @@ qgemm_i4_kernel(const GemmParams p) {
       // activations: 256 rows x 8 pieces of 16 B, copied asynchronously straight into the
       // swizzled tile (rows past m are zero-filled); the copy flies while we dequantise
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t piece = tid + i * 256u;
+      for (int i = 0; i < kAPiecesPerThread; ++i) {
+        const uint32_t piece = tid + i * (kProducerWarps * 32u);
         const uint32_t r = piece >> 3, c = piece & 7u;
         const bool in_range = m0 + r < p.m;
         const __nv_bfloat16* src = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + ks * kBK + c * 8;
@@ -219,10 +224,10 @@ qgemm_i4_kernel(const GemmParams p) {
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
       // weights: this k-step's chunks are already in registers; fetch the next k-step's
-      uint4 wq[2];
-      float sc[2][4];
+      uint4 wq[kChunksPerWarp];
+      float sc[kChunksPerWarp][4];
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < kChunksPerWarp; ++cc) {
         wq[cc] = wq_next[cc];
         if constexpr (kScaleF16) {
           const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&sc_next[cc].x));
@@ -235,13 +240,13 @@ qgemm_i4_kernel(const GemmParams p) {
       }
       fetch_weights(ks + 1);
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < kChunksPerWarp; ++cc) {
         // words: row g grp 0 | row g+8 grp 0 | row g grp 1 | row g+8 grp 1; the lane's 8
         // nibbles of a group are k = 8t .. 8t+7 of that group = 16-byte piece t (group 0)
         // or 4 + t (group 1) of the 128-byte tile row.  Odd g stores group 1 first: the 8
         // lanes of a shared-memory phase (two values of g, four of t) then hit 8 different
         // 16-byte columns of the swizzled rows.
-        const uint32_t r_a = (warp * 2 + cc) * 16u + g, r_b = r_a + 8u;
+        const uint32_t r_a = (warp * kChunksPerWarp + cc) * 16u + g, r_b = r_a + 8u;
         const uint4 a0 = dequant8_bf16(wq[cc].x, sc[cc][0]), a1 = dequant8_bf16(wq[cc].z, sc[cc][2]);
         const uint4 b0 = dequant8_bf16(wq[cc].y, sc[cc][1]), b1 = dequant8_bf16(wq[cc].w, sc[cc][3]);
         const bool odd = (g & 1u) != 0;
@@ -257,10 +262,15 @@ qgemm_i4_kernel(const GemmParams p) {
     // ---------------- epilogue: accumulators -> out ----------------
     wait_bounded(bars + 2 * kStagesG * 8, 0, abort_flag, p.status, 3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t half = warp >> 2, quarter = warp & 3u;  // accumulator (rows 0-127 / 128-255), lane quarter
+    // a warp may only touch the TMEM lane quarter warp % 4; the warps sharing a quarter split
+    // the two accumulators (rows 0-127 / 128-255) and, with 16 producers, the column halves
+    const uint32_t quarter = warp & 3u, group = warp >> 2;
+    const uint32_t half = group & 1u;
+    constexpr uint32_t kColBatches = (kBN / 32) / (kProducerWarps / 8);
+    const uint32_t cb0 = (group >> 1) * kColBatches;
     const uint32_t row = m0 + half * 128u + quarter * 32u + lane;
 #pragma unroll 1
-    for (uint32_t cb = 0; cb < kBN / 32; ++cb) {
+    for (uint32_t cb = cb0; cb < cb0 + kColBatches; ++cb) {
       uint32_t v[32];
       const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + half * kBN + cb * 32u;
       asm volatile(
