@@ -156,6 +156,72 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def kernel_sweep(gpu):
+    """Kernel-only numbers for the other halves of the metric, measured after the timed region
+    (N = 1 only): the int4 / int8 GEMV on single matrices (graph replay over distinct weight
+    copies totalling more than L2, so every launch streams from HBM) and the prefill GEMM."""
+    import torch
+    from tests import cases
+    out = {}
+
+    def gemv(storage, k, n, m, dtype):
+        if storage == "i4":
+            data, scale = cases.synth_i4(n, k, seed=1)
+        else:
+            data, scale = cases.synth_i8(n, k, seed=1)
+        wbytes = data.nbytes + scale.nbytes
+        copies = max(2, min(48, int(400e6 // wbytes) + 1))
+        ws = [gpu.upload_weight(storage, data, scale, (n, k), 32 if storage == "i4" else 0) for _ in range(copies)]
+        x = torch.randn(m, k, device="cuda").to(dtype)
+        bias = torch.zeros(n, device="cuda")
+        y = torch.empty(m, n, device="cuda")
+        gpu.graph_begin()
+        for w in ws:
+            gpu.linear(x, w, bias, out=y)
+        g = gpu.graph_end()
+        for _ in range(3):
+            gpu.graph_launch(g)
+        gpu.sync()
+        best = 1e9
+        for _ in range(5):
+            gpu.timer_start()
+            gpu.graph_launch(g)
+            best = min(best, gpu.timer_stop())
+        gpu.graph_free(g)
+        for w in ws:
+            w.free()
+        alg = wbytes + m * k * x.element_size() + m * n * 4
+        us = best * 1e3 / copies
+        return {"us": round(us, 3), "GB/s": round(alg / us / 1e3, 1), "frac_of_8TB/s": round(alg / us / 1e3 / 8000, 3)}
+
+    out["gemv_i4_m1_4096x4096_f32 (config 0)"] = gemv("i4", 4096, 4096, 1, torch.float32)
+    out["gemv_i4_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i4", 1536, 151936, 1, torch.float32)
+    out["gemv_i8_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i8", 1536, 151936, 1, torch.float32)
+    out["gemv_i4_m8_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 8, torch.float16)
+    out["gemv_i4_m1_4096x128256_f32 (config 4 lm head)"] = gemv("i4", 4096, 128256, 1, torch.float32)
+
+    def gemm(m, k, n):
+        data, scale = cases.synth_i4(n, k, seed=1)
+        w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+        x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        bias = torch.zeros(n, device="cuda")
+        y = torch.empty(m, n, device="cuda")
+        for _ in range(3):
+            gpu.linear(x, w, bias, out=y)
+        gpu.sync()
+        best = 1e9
+        for _ in range(8):
+            gpu.timer_start()
+            gpu.linear(x, w, bias, out=y)
+            best = min(best, gpu.timer_stop())
+        w.free()
+        return {"ms": round(best, 4), "TFLOP/s": round(2.0 * m * n * k / best / 1e9, 1)}
+
+    out["gemm_i4_bf16_m2048_4096x14336 (config 3)"] = gemm(2048, 4096, 14336)
+    out["gemm_i4_bf16_m2048_14336x4096 (config 3)"] = gemm(2048, 14336, 4096)
+    return out
+
+
 def run_cuda(args):
     import torch
     import torch.distributed as dist
@@ -236,6 +302,10 @@ def run_cuda(args):
         bytes_rank = cfg.algorithmic_bytes(args.batch, world)
         launches_per_step = step.kernels_per_step
         achieved = bytes_rank / (per_step_ms * 1e-3) / 1e9
+        sweep = None
+        if world == 1 and not args.no_sweep:
+            gpu.use_stream(torch.cuda.current_stream())
+            sweep = kernel_sweep(gpu)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             tok_cpu, _, desc, cores = cpu_sample(args.batch, 0, 5)
@@ -259,6 +329,7 @@ def run_cuda(args):
                          "algorithmic_bytes_per_launch": bytes_rank / max(1, launches_per_step),
                          "traffic": None},
             "cpu_baseline": cpu,
+            "kernel_sweep": sweep,
             "clocks": clocks,
             "finite_outputs": logits_ok,
         }
@@ -283,6 +354,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="kq", choices=["kq", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the single-kernel GEMV / GEMM numbers")
     ap.add_argument("--exchange", default="kq", choices=["kq", "nccl"], help="all-reduce used when --gpus > 1")
     ap.add_argument("--fused", action="store_true", help="replay the step as one persistent plan kernel instead of a CUDA graph of 129 launches")
     args = ap.parse_args()
