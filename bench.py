@@ -302,6 +302,22 @@ def run_cuda(args):
         bytes_rank = cfg.algorithmic_bytes(args.batch, world)
         launches_per_step = step.kernels_per_step
         achieved = bytes_rank / (per_step_ms * 1e-3) / 1e9
+        other_batch = None
+        if world == 1 and not args.no_sweep and args.batch != 16:
+            # the same resident weights at the other end of the batch range (device-timed, 5 steps)
+            step16 = DecodeStep(gpu, cfg, 16, seed=0, fused=args.fused, share_weights_with=step)
+            step16.record()
+            step16.x.normal_()
+            for _ in range(3):
+                step16.run_device()
+            step16.sync()
+            gpu.timer_start()
+            for _ in range(5):
+                step16.run_device()
+            ms16 = gpu.timer_stop() / 5
+            other_batch = {"batch": 16, "ms_per_step": ms16, "tok_per_s": 16 / (ms16 * 1e-3),
+                           "GB/s": cfg.algorithmic_bytes(16, 1) / (ms16 * 1e-3) / 1e9}
+            step16.close()
         sweep = None
         if world == 1 and not args.no_sweep:
             gpu.use_stream(torch.cuda.current_stream())
@@ -330,6 +346,7 @@ def run_cuda(args):
                          "traffic": None},
             "cpu_baseline": cpu,
             "kernel_sweep": sweep,
+            "other_batch": other_batch,
             "clocks": clocks,
             "finite_outputs": logits_ok,
         }

@@ -58,6 +58,12 @@ constexpr int kWarps = 4;                // warps per CTA
 #ifndef KQ_TUNE_WANT
 #define KQ_TUNE_WANT 4
 #endif
+#ifndef KQ_TUNE_RB16
+#define KQ_TUNE_RB16 2
+#endif
+#ifndef KQ_TUNE_RB32
+#define KQ_TUNE_RB32 2
+#endif
 #ifndef KQ_TUNE_LATE_TRIGGER
 #define KQ_TUNE_LATE_TRIGGER 0
 #endif
@@ -434,9 +440,9 @@ cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const Linea
   if (cols <= 8)
     return f16s ? launch_typed<XT, true, 8, 1>(env, p, count, t) : launch_typed<XT, false, 8, 1>(env, p, count, t);
   if (cols <= 16)
-    return f16s ? launch_typed<XT, true, 16, 2>(env, p, count, t) : launch_typed<XT, false, 16, 2>(env, p, count, t);
+    return f16s ? launch_typed<XT, true, 16, KQ_TUNE_RB16>(env, p, count, t) : launch_typed<XT, false, 16, KQ_TUNE_RB16>(env, p, count, t);
   if constexpr (kHasLo) {
-    return f16s ? launch_typed<XT, true, 32, 2>(env, p, count, t) : launch_typed<XT, false, 32, 2>(env, p, count, t);
+    return f16s ? launch_typed<XT, true, 32, KQ_TUNE_RB32>(env, p, count, t) : launch_typed<XT, false, 32, KQ_TUNE_RB32>(env, p, count, t);
   } else {
     return cudaErrorInvalidValue;
   }

@@ -105,7 +105,7 @@ class DecodeStep:
 
     def __init__(self, gpu: Gpu, cfg: DecodeConfig, batch: int, rank: int = 0, world: int = 1,
                  seed: int = 0, keep_host_weights: bool = False, process_group=None, fused: bool = True,
-                 exchange: str = "kq"):
+                 exchange: str = "kq", share_weights_with: "DecodeStep | None" = None):
         import torch
         if not 1 <= batch <= 16:
             raise ValueError("decode batch is 1..16 token rows")
@@ -124,7 +124,11 @@ class DecodeStep:
         self.weights = {}
         self.host_weights = {} if keep_host_weights else None
         rng = np.random.default_rng(seed)  # every rank draws the same full matrices, then keeps its shard
-        for name, k, n, par in cfg.all_matmuls():
+        self._shared = share_weights_with is not None
+        if share_weights_with is not None:  # same resident weights, another batch size
+            self.weights = share_weights_with.weights
+            self.host_weights = share_weights_with.host_weights
+        for name, k, n, par in (cfg.all_matmuls() if share_weights_with is None else []):
             payload, scale = synth_weight(rng, n, k, cfg.group_size)
             shard = KQ_SHARD_NONE if world == 1 else (KQ_SHARD_COLUMN if par == "col" else KQ_SHARD_ROW)
             self.weights[name] = gpu.upload_weight("i4", payload, scale, (n, k), cfg.group_size,
@@ -254,6 +258,12 @@ class DecodeStep:
         self.gpu.sync()
 
     def close(self) -> None:
-        for w in self.weights.values():
-            w.free()
+        if self.plan is not None and self.exchange != "nccl":
+            free = self.gpu.plan_free if self.fused else self.gpu.graph_free
+            free(self.plan)
+            free(self.plan_host)
+            self.plan = self.plan_host = None
+        if not getattr(self, "_shared", False):
+            for w in self.weights.values():
+                w.free()
         self.weights = {}
