@@ -30,7 +30,10 @@
 namespace kq {
 namespace {
 
-constexpr int kPlanWarps = 16;
+#ifndef KQ_PLAN_WARPS
+#define KQ_PLAN_WARPS 16
+#endif
+constexpr int kPlanWarps = KQ_PLAN_WARPS;
 constexpr int kSlots = 2;  // ring slots per warp
 constexpr uint32_t kSpinLimit = 1u << 22;
 

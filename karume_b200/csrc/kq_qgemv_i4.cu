@@ -64,6 +64,9 @@ constexpr int kWarps = 4;                // warps per CTA
 #ifndef KQ_TUNE_RB32
 #define KQ_TUNE_RB32 2
 #endif
+#ifndef KQ_TUNE_GP
+#define KQ_TUNE_GP 1
+#endif
 #ifndef KQ_TUNE_LATE_TRIGGER
 #define KQ_TUNE_LATE_TRIGGER 0
 #endif
@@ -98,6 +101,12 @@ __device__ __forceinline__ uint2 ldg_stream_v2(const void* p) {
   return v;
 }
 
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
 __device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
@@ -110,6 +119,29 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// K was split over the CTAs of a cluster: every CTA holds its partial sums in `red`
+// ([m][tile_rows] f32 in its own shared memory); after one cluster barrier each CTA adds a
+// slice of the tile's outputs over distributed shared memory, ranks in ascending order.
+__device__ __forceinline__ void cluster_reduce_store(const GemvParams& p, float* red, uint32_t tile_rows,
+                                                     uint32_t tile, uint32_t split, uint32_t n, float* out,
+                                                     const float* bias) {
+  cluster_sync_all();
+  const uint32_t rows_here = min(tile_rows, n - tile * tile_rows);
+  const uint32_t total = rows_here * p.m;
+  const uint32_t per_rank = (total + p.splits - 1) / p.splits;
+  const uint32_t lo = min(split * per_rank, total), hi = min(lo + per_rank, total);
+  const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
+  for (uint32_t idx = lo + threadIdx.x; idx < hi; idx += blockDim.x) {
+    const uint32_t mm = idx / rows_here, r = idx - mm * rows_here;
+    const uint32_t local = red_base + (mm * tile_rows + r) * 4u;
+    float sum = 0.0f;
+    for (uint32_t s = 0; s < p.splits; ++s) sum += ld_cluster_f32(cluster_map_shared(local, s));
+    const uint32_t row = tile * tile_rows + r;
+    out[static_cast<size_t>(mm) * n + row] = fmaf(sum, kUnscale, bias[row]);
+  }
+  cluster_sync_all();  // nobody's shared memory may go away while a peer still reads it
 }
 
 template <bool kScaleF16>
@@ -343,23 +375,222 @@ qgemv_i4_kernel(const GemvParams p) {
   }
   if (p.splits == 1) return;
 
-  // K was split over the CTAs of this cluster: every CTA adds a slice of the tile's
-  // outputs over distributed shared memory, ranks in ascending order.
-  cluster_sync_all();
-  const uint32_t rows_here = min(kTileRowsCta, n - tile * kTileRowsCta);
-  const uint32_t total = rows_here * p.m;
-  const uint32_t per_rank = (total + p.splits - 1) / p.splits;
-  const uint32_t lo = min(split * per_rank, total), hi = min(lo + per_rank, total);
-  const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
-  for (uint32_t idx = lo + threadIdx.x; idx < hi; idx += blockDim.x) {
-    const uint32_t mm = idx / rows_here, r = idx - mm * rows_here;
-    const uint32_t local = red_base + (mm * kTileRowsCta + r) * 4u;
-    float sum = 0.0f;
-    for (uint32_t s = 0; s < p.splits; ++s) sum += ld_cluster_f32(cluster_map_shared(local, s));
-    const uint32_t row = tile * kTileRowsCta + r;
-    out[static_cast<size_t>(mm) * n + row] = fmaf(sum, kUnscale, bias[row]);
+  cluster_reduce_store(p, red, kTileRowsCta, tile, split, n, out, bias);
+}
+
+// ---- group-packed variant: at most 4 of the 8 MMA columns are needed -----------------
+// With one or two activation rows the block above would leave most of each MMA tile empty
+// and, worse, make every lane apply every group's scale.  Here the spare columns carry
+// OTHER scale groups: a unit is kG consecutive groups, group j of the unit owns columns
+// [j * kCpg, (j + 1) * kCpg) of the tile (its activations are zero in every other column),
+// and the 2 * kG MMAs of the unit accumulate into ONE C tile.  Column block j of C then
+// holds group j's partial sums only, so a lane scales just the group its two C columns
+// belong to: one scale pair, one "-8 sum x" term and three FP instructions per row half and
+// unit instead of per group.  The staged activations of a unit are 512 dense bytes, read
+// with one 128-bit load per lane into the register set of the lane's own group; the sets of
+// the other groups stay zero for the whole kernel.  Lanes that share an output row add their
+// partial sums with two shuffles in the epilogue.
+template <bool kScaleF16>
+struct UnitScale {
+  typename std::conditional<kScaleF16, uint32_t, uint2>::type v;  // rows g, g+8 of the lane's own group
+};
+
+template <typename XT, bool kScaleF16, int kG>
+__global__ void __launch_bounds__(kWarps * 32)
+qgemv_i4_gp_kernel(const GemvParams p) {
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
+  constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;  // chunk bytes
+  constexpr int kCpg = 8 / kG;                 // MMA columns per group
+  constexpr int kCU = kG / 2;                  // chunks per unit
+  constexpr int kUnits = kDepth / kCU;         // ring entries
+  constexpr int kCorrStride = kHasLo ? kCpg / 2 : kCpg;  // activation rows a group's columns hold
+  constexpr int kAcc = kHasLo ? 2 : 4;
+  constexpr int kCorr = kHasLo ? 1 : 2;
+  constexpr uint32_t kTileRowsCta = kWarps * 16;
+  constexpr uint32_t kXsStride = kCpg * 64;    // staged bytes per group
+  static_assert(kG == 2 || kG == 4, "units of two or four groups");
+  static_assert(kDepth % kCU == 0, "the ring holds whole units");
+
+  extern __shared__ __align__(16) uint8_t smem[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+
+  if (!KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
+
+  uint32_t wi = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxMulti; ++i)
+    if (i < static_cast<int>(p.count) && blockIdx.x >= p.tile_begin[i]) wi = i;
+  const uint8_t* w_base = p.w[0];
+  const float* bias = p.bias[0];
+  float* out = p.out[0];
+  uint32_t n = p.n[0], tile0 = p.tile_begin[0];
+#pragma unroll
+  for (int i = 1; i < kMaxMulti; ++i)
+    if (wi == static_cast<uint32_t>(i)) {
+      w_base = p.w[i]; bias = p.bias[i]; out = p.out[i]; n = p.n[i]; tile0 = p.tile_begin[i];
+    }
+  const uint32_t tile = blockIdx.x - tile0;
+  const uint32_t row_block = tile * kWarps + warp;
+  const bool active = row_block * 16u < n;
+
+  const uint32_t chunks_per_row = p.k / kChunkK;
+  const uint32_t split = blockIdx.y;
+  const uint32_t cbeg = min(split * p.chunks_per_split, chunks_per_row);
+  const uint32_t cend = min(cbeg + p.chunks_per_split, chunks_per_row);
+  const uint32_t nch = cend - cbeg;  // a whole number of units (the host guarantees it)
+
+  const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
+  uint8_t* xs = smem;
+  float* corr = reinterpret_cast<float*>(smem + 2 * p.slab_chunks * kXsStride);
+
+  // the group (inside a unit) and the activation row(s) this lane's two C columns belong to
+  const uint32_t jl = (2u * t) / kCpg;
+  const uint32_t tl = t % (kCpg / 2);
+  // the group whose activations this lane feeds the MMAs with (B operand: column g)
+  const uint32_t jb = g / kCpg;
+  const bool col_live = (g % kCpg) < active_cols;
+
+  const uint8_t* next = w_base + (static_cast<size_t>(row_block) * chunks_per_row + cbeg) * kCB + lane * 16;
+  const uint32_t scale_off = (jl >> 1) * kCB + kChunkWeightBytes - lane * 16 + g * (4 * kScaleBytes) +
+                             (jl & 1u) * (2 * kScaleBytes);
+
+  uint4 ring_w[kUnits][kCU];
+  UnitScale<kScaleF16> ring_s[kUnits];
+  auto fetch = [&](const int u, const uint8_t* src) {
+#pragma unroll
+    for (int c = 0; c < kCU; ++c) ring_w[u][c] = ldg_stream_v4(src + c * kCB);
+    if constexpr (kScaleF16) ring_s[u].v = ldg_stream_u32(src + scale_off);
+    else ring_s[u].v = ldg_stream_v2(src + scale_off);
+  };
+#pragma unroll
+  for (int u = 0; u < kUnits; ++u) {
+#pragma unroll
+    for (int c = 0; c < kCU; ++c) ring_w[u][c] = make_uint4(0, 0, 0, 0);
+    if constexpr (kScaleF16) ring_s[u].v = 0u;
+    else ring_s[u].v = make_uint2(0, 0);
+    if (active && static_cast<uint32_t>(u * kCU) < nch) fetch(u, next + u * (kCU * kCB));
   }
-  cluster_sync_all();  // nobody's shared memory may go away while a peer still reads it
+  next += kDepth * kCB;
+
+  pdl_wait_prior_grid();
+
+  float acc[kAcc];
+#pragma unroll
+  for (int j = 0; j < kAcc; ++j) acc[j] = 0.0f;
+  constexpr uint32_t kMask0 = 0x000F000Fu, kMask1 = 0x00F000F0u;
+
+  uint4 bset[kG];
+  bool load_b[kG];
+#pragma unroll
+  for (int j = 0; j < kG; ++j) {
+    bset[j] = make_uint4(0, 0, 0, 0);
+    load_b[j] = col_live && jb == static_cast<uint32_t>(j);
+  }
+  float cterm[kCorr];
+  bool load_c[kCorr];
+#pragma unroll
+  for (int j = 0; j < kCorr; ++j) {
+    cterm[j] = 0.0f;
+    load_c[j] = (kHasLo ? tl : 2 * tl + j) < p.m;
+  }
+  const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
+  const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) +
+                             (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 4;
+
+  auto process = [&](const int u, uint32_t xs_addr, uint32_t corr_addr, bool refill) {
+#pragma unroll
+    for (int j = 0; j < kG; ++j) lds_v4_if(bset[j], xs_addr, load_b[j]);
+#pragma unroll
+    for (int j = 0; j < kCorr; ++j) lds_f32_if(cterm[j], corr_addr + j * 4, load_c[j]);
+    float cf[4];
+#pragma unroll
+    for (int j = 0; j < kG; ++j) {
+      const uint4 wq = ring_w[u][j >> 1];
+      const uint32_t wa = (j & 1) ? wq.z : wq.x;  // row g
+      const uint32_t wb = (j & 1) ? wq.w : wq.y;  // row g + 8
+      const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+      const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
+      const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
+      if (j == 0) mma_f16_zero(cf, a0, bset[j].x, bset[j].y);
+      else mma_f16(cf, a0, bset[j].x, bset[j].y);
+      mma_f16(cf, a1, bset[j].z, bset[j].w);
+    }
+    float2 s;  // .x = row g, .y = row g + 8, the lane's own group
+    if constexpr (kScaleF16) s = __half22float2(*reinterpret_cast<const __half2*>(&ring_s[u].v));
+    else s = make_float2(__uint_as_float(ring_s[u].v.x), __uint_as_float(ring_s[u].v.y));
+    if constexpr (kHasLo) {
+      acc[0] = fmaf(s.x, (cf[0] + cf[1]) + cterm[0], acc[0]);
+      acc[1] = fmaf(s.y, (cf[2] + cf[3]) + cterm[0], acc[1]);
+    } else {
+      acc[0] = fmaf(s.x, cf[0] + cterm[0], acc[0]);
+      acc[1] = fmaf(s.x, cf[1] + cterm[1], acc[1]);
+      acc[2] = fmaf(s.y, cf[2] + cterm[0], acc[2]);
+      acc[3] = fmaf(s.y, cf[3] + cterm[1], acc[3]);
+    }
+    if (refill && active) fetch(u, next + u * (kCU * kCB));
+  };
+
+  const XT* x = static_cast<const XT*>(p.x);
+  for (uint32_t done = 0; done < nch;) {
+    const uint32_t slab_n = min(p.slab_chunks, nch - done);
+    if (done != 0) __syncthreads();
+    stage_x<XT, kHasLo, kCorrStride>(x, p.m, p.k, 2 * (cbeg + done), 2 * slab_n, xs, kXsStride, corr, p.error_flag);
+    __syncthreads();
+    uint32_t xs_addr = xs_lane, corr_addr = corr_lane;
+    uint32_t i = 0;
+    for (; i + kDepth <= slab_n; i += kDepth) {
+#pragma unroll
+      for (int u = 0; u < kUnits; ++u) {
+        process(u, xs_addr, corr_addr, done + i + u * kCU + kDepth < nch);
+        xs_addr += 512;
+        corr_addr += kG * kCorrStride * 4;
+      }
+      next += kDepth * kCB;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnits - 1; ++u) {  // the last, short round of the split
+      if (i + u * kCU < slab_n) {
+        process(u, xs_addr, corr_addr, false);
+        xs_addr += 512;
+        corr_addr += kG * kCorrStride * 4;
+      }
+    }
+    done += slab_n;
+  }
+
+  if (KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
+
+  // ---- epilogue: lanes whose C columns belong to different groups hold partial sums of the
+  // same outputs; add them (fixed order), then the lanes of group 0 own the result.
+#pragma unroll
+  for (int j = 0; j < kAcc; ++j) {
+    if constexpr (kG == 4) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 1);
+    acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 2);
+  }
+  float* red = reinterpret_cast<float*>(smem);  // [m][kTileRowsCta], aliases the x slab
+  if (p.splits > 1) __syncthreads();
+  if (active && jl == 0) {
+    const uint32_t row_a = row_block * 16u + g;
+    const uint32_t tr_a = warp * 16u + g;
+#pragma unroll
+    for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
+      const uint32_t mm = kHasLo ? tl : 2 * tl + j;
+      if (mm >= p.m) continue;
+      const float va = acc[kHasLo ? 0 : j];
+      const float vb = acc[kHasLo ? 1 : 2 + j];
+      if (p.splits == 1) {
+        out[static_cast<size_t>(mm) * n + row_a] = fmaf(va, kUnscale, bias[row_a]);
+        out[static_cast<size_t>(mm) * n + row_a + 8] = fmaf(vb, kUnscale, bias[row_a + 8]);
+      } else {
+        red[mm * kTileRowsCta + tr_a] = va;
+        red[mm * kTileRowsCta + tr_a + 8] = vb;
+      }
+    }
+  }
+  if (p.splits == 1) return;
+  cluster_reduce_store(p, red, kTileRowsCta, tile, split, n, out, bias);
 }
 
 template <typename XT, int kCols>
@@ -429,6 +660,64 @@ cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const L
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
+template <typename XT, bool kScaleF16, int kG>
+cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets) {
+  auto kernel = qgemv_i4_gp_kernel<XT, kScaleF16, kG>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  constexpr uint32_t kCpg = 8 / kG, kCU = kG / 2;
+  constexpr uint32_t kCorrStride = kHasLo ? kCpg / 2 : kCpg;
+  constexpr uint32_t kTileRowsCta = kWarps * 16;
+  uint32_t tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    p.tile_begin[i] = tiles;
+    tiles += (targets[i].w->n + kTileRowsCta - 1) / kTileRowsCta;
+  }
+  for (int i = count; i <= kMaxMulti; ++i) p.tile_begin[i] = tiles;
+
+  const uint32_t units_per_row = p.k / kChunkK / kCU;  // the caller checked divisibility
+  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * KQ_TUNE_WANT;
+  uint32_t splits = 1;
+  while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas && splits * 2 <= units_per_row)
+    splits *= 2;
+  p.splits = splits;
+  p.chunks_per_split = (units_per_row + splits - 1) / splits * kCU;
+  const uint32_t per_chunk = 2 * (kCpg * 64 + kCorrStride * 4);
+  const uint32_t slab_cap = std::max<uint32_t>(kDepth, (32768u / per_chunk) / kDepth * kDepth);
+  p.slab_chunks = std::max<uint32_t>(kCU, std::min(p.chunks_per_split, slab_cap));
+
+  const size_t slab_bytes = static_cast<size_t>(p.slab_chunks) * per_chunk;
+  const size_t red_bytes = splits > 1 ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles, splits, 1);
+  cfg.blockDim = dim3(kWarps * 32, 1, 1);
+  cfg.dynamicSmemBytes = std::max(slab_bytes, red_bytes);
+  cfg.stream = env.stream;
+  cudaLaunchAttribute attr[2];
+  unsigned int na = 0;
+  if (env.overlap) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (splits > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = splits;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // Columns of the MMA tile an activation row needs: 1 for binary16 input, 2 (hi, lo)
 // for f32 / bf16 input.  One row block per warp while a single MMA tile holds every
 // column; two (sharing the B fragments) beyond that, where shared-memory bandwidth
@@ -437,6 +726,12 @@ template <typename XT>
 cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* t, bool f16s) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   const uint32_t cols = kHasLo ? 2 * p.m : p.m;
+  // Few columns: pack several scale groups into one MMA tile (four groups need an even
+  // number of 64-k chunks per row).
+  if (KQ_TUNE_GP && cols <= 2 && (p.k / kChunkK) % 2 == 0)
+    return f16s ? launch_typed_gp<XT, true, 4>(env, p, count, t) : launch_typed_gp<XT, false, 4>(env, p, count, t);
+  if (KQ_TUNE_GP && cols <= 4)
+    return f16s ? launch_typed_gp<XT, true, 2>(env, p, count, t) : launch_typed_gp<XT, false, 2>(env, p, count, t);
   if (cols <= 8)
     return f16s ? launch_typed<XT, true, 8, 1>(env, p, count, t) : launch_typed<XT, false, 8, 1>(env, p, count, t);
   if (cols <= 16)
