@@ -64,50 +64,65 @@ template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2 = false>
 __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, uint32_t k,
                                         uint32_t group0, uint32_t groups, uint8_t* xs,
                                         uint32_t xs_stride, float* corr, int* error_flag) {
+  constexpr int kBatch = 4;  // octets a thread loads before it converts any: one memory round trip per batch
   const uint32_t items = groups * m * 4;
   const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles below
   bool out_of_range = false;
-  for (uint32_t item = threadIdx.x; item < items_padded; item += blockDim.x) {
-    const bool valid = item < items;
-    const uint32_t q = item & 3u;
-    const uint32_t rest = item >> 2;
-    const uint32_t row = rest % m;
-    const uint32_t lg = rest / m;
-    uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
-    float sum = 0.0f;
-    if (valid) {
-      float v[8];
-      load_x8<XT, kFromL2>(x + static_cast<size_t>(row) * k + (static_cast<size_t>(group0 + lg) << 5) + (q << 3), v);
-      __half h[8], l[8];
+  for (uint32_t base = threadIdx.x; base < items_padded; base += blockDim.x * kBatch) {
+    float v[kBatch][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float a = fabsf(v[e]);
-        if (a > 65504.0f && a < __int_as_float(0x7f800000)) out_of_range = true;
-        const float staged = (e & 1) ? v[e] * 0.0625f : v[e];
-        const float back = (e & 1) ? 16.0f : 1.0f;
-        h[e] = __float2half_rn(staged);
-        const float hf = __half2float(h[e]);
-        if constexpr (kHasLo) {
-          l[e] = __float2half_rn(staged - hf);
-          sum = fmaf(hf + __half2float(l[e]), back, sum);
-        } else {
-          sum = fmaf(hf, back, sum);
-        }
+    for (int b = 0; b < kBatch; ++b) {
+      const uint32_t item = base + b * blockDim.x;
+      if (item < items) {
+        const uint32_t rest = item >> 2;
+        const uint32_t row = rest % m, lg = rest / m;
+        load_x8<XT, kFromL2>(x + static_cast<size_t>(row) * k + (static_cast<size_t>(group0 + lg) << 5) + ((item & 3u) << 3),
+                             v[b]);
       }
-      hi4 = make_uint4(pack_half2(h[0], h[4]), pack_half2(h[1], h[5]), pack_half2(h[2], h[6]),
-                       pack_half2(h[3], h[7]));
-      if constexpr (kHasLo)
-        lo4 = make_uint4(pack_half2(l[0], l[4]), pack_half2(l[1], l[5]), pack_half2(l[2], l[6]),
-                         pack_half2(l[3], l[7]));
     }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (valid) {
-      const uint32_t col = kHasLo ? 2 * row : row;
-      const uint32_t off = lg * xs_stride + col * 64 + q * 16;
-      *reinterpret_cast<uint4*>(xs + off) = hi4;
-      if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + 64) = lo4;
-      if (q == 0) corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const uint32_t item = base + b * blockDim.x;
+      if (item >= items_padded) break;  // warp-uniform
+      const bool valid = item < items;
+      const uint32_t q = item & 3u;
+      const uint32_t rest = item >> 2;
+      const uint32_t row = rest % m;
+      const uint32_t lg = rest / m;
+      uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
+      float sum = 0.0f;
+      if (valid) {
+        __half h[8], l[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float a = fabsf(v[b][e]);
+          if (a > 65504.0f && a < __int_as_float(0x7f800000)) out_of_range = true;
+          const float staged = (e & 1) ? v[b][e] * 0.0625f : v[b][e];
+          const float back = (e & 1) ? 16.0f : 1.0f;
+          h[e] = __float2half_rn(staged);
+          const float hf = __half2float(h[e]);
+          if constexpr (kHasLo) {
+            l[e] = __float2half_rn(staged - hf);
+            sum = fmaf(hf + __half2float(l[e]), back, sum);
+          } else {
+            sum = fmaf(hf, back, sum);
+          }
+        }
+        hi4 = make_uint4(pack_half2(h[0], h[4]), pack_half2(h[1], h[5]), pack_half2(h[2], h[6]),
+                         pack_half2(h[3], h[7]));
+        if constexpr (kHasLo)
+          lo4 = make_uint4(pack_half2(l[0], l[4]), pack_half2(l[1], l[5]), pack_half2(l[2], l[6]),
+                           pack_half2(l[3], l[7]));
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (valid) {
+        const uint32_t col = kHasLo ? 2 * row : row;
+        const uint32_t off = lg * xs_stride + col * 64 + q * 16;
+        *reinterpret_cast<uint4*>(xs + off) = hi4;
+        if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + 64) = lo4;
+        if (q == 0) corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
+      }
     }
   }
   if (out_of_range) *reinterpret_cast<volatile int*>(error_flag) = 1;  // sticky, host-mapped word

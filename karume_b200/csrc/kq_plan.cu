@@ -22,6 +22,7 @@
 //     status word, keeps going without blocking, and the host reports KQ_ERR_TIMEOUT.
 #include <algorithm>
 #include <type_traits>
+#include <utility>
 #include <vector>
 
 #include "kq_gemv_core.cuh"
@@ -30,11 +31,15 @@
 namespace kq {
 namespace {
 
+#ifndef KQ_PLAN_PAIRED
+#define KQ_PLAN_PAIRED 1
+#endif
 #ifndef KQ_PLAN_WARPS
 #define KQ_PLAN_WARPS 16
 #endif
 constexpr int kPlanWarps = KQ_PLAN_WARPS;
 constexpr int kSlots = 2;  // ring slots per warp
+constexpr uint32_t kOpWindow = 16;  // op descriptors the paired kernel keeps in shared memory
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct PlanOpDev {
@@ -48,6 +53,7 @@ struct PlanOpDev {
   uint32_t k;
   uint32_t chunks_per_row;   // k / 64
   uint32_t slabs;            // S: k-slabs a row block is split into across the warps of a CTA
+  uint32_t slabs_log2;
   uint32_t chunks_per_slab;  // ceil(chunks_per_row / S)
   uint32_t row_blocks;       // 16-row blocks of the op
   uint32_t cta_items;        // ceil(row_blocks / (kPlanWarps / S)): CTA-sized units of work
@@ -63,7 +69,20 @@ struct PlanParams {
   unsigned int* grid_bar;  // arrivals at the inter-op barrier (zeroed before every launch)
   int* error_flag;         // activation out of domain
   int* status;             // non-zero: a bounded wait gave up
+#ifdef KQ_PLAN_TRACE
+  unsigned long long* trace;  // [cta][op][4] globaltimer stamps
+#endif
 };
+#ifdef KQ_PLAN_TRACE
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define KQ_TRACE(slot) do { if (threadIdx.x == 0) p.trace[(static_cast<size_t>(cta) * p.op_count + op) * 4 + (slot)] = gtime(); } while (0)
+#else
+#define KQ_TRACE(slot) do {} while (0)
+#endif
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -126,9 +145,15 @@ __device__ __forceinline__ WarpItem item_of(const PlanOpDev& o, uint32_t round, 
   return it;
 }
 
-template <typename XT, bool kScaleF16, int kCols, int kSlotChunks>
+template <typename XT, bool kScaleF16, int kCols, int kSlotChunks, int kG>
 __global__ void __launch_bounds__(kPlanWarps * 32, 1)
 plan_kernel(const PlanParams p) {
+  // kG > 1: kG consecutive scale groups share one 8-column MMA tile (see
+  // qgemv_i4_gp_kernel); kG == 1: one group per tile, kCols / 8 tiles.
+  static_assert(kG == 1 || kCols == 8, "group packing uses a single tile");
+  constexpr int kCpg = 8 / kG;   // MMA columns per group when packing
+  constexpr int kCU = kG > 1 ? kG / 2 : 1;  // chunks per unit
+  static_assert(kSlotChunks % kCU == 0, "ring pieces hold whole units");
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
   constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;  // chunk bytes
@@ -136,7 +161,7 @@ plan_kernel(const PlanParams p) {
   constexpr int kTiles = kCols / 8;
   constexpr int kAccPerTile = kHasLo ? 2 : 4;
   constexpr int kCorrPerTile = kHasLo ? 1 : 2;
-  constexpr int kCorrStride = kHasLo ? kCols / 2 : kCols;
+  constexpr int kCorrStride = kG > 1 ? (kHasLo ? kCpg / 2 : kCpg) : (kHasLo ? kCols / 2 : kCols);
   constexpr uint32_t kMask0 = 0x000F000Fu, kMask1 = 0x00F000F0u;
 
   extern __shared__ __align__(128) uint8_t smem[];
@@ -150,7 +175,7 @@ plan_kernel(const PlanParams p) {
   const uint32_t bars = smem_base + kPlanWarps * kSlots * kSlotBytes + warp * (kSlots * 8);
   uint8_t* xs = smem + kPlanWarps * kSlots * kSlotBytes + kPlanWarps * kSlots * 8;
   const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
-  const uint32_t xs_stride = active_cols * 64;
+  const uint32_t xs_stride = kG > 1 ? kCpg * 64u : active_cols * 64;
   const uint32_t groups_max = p.xs_bytes / xs_stride;
   float* corr = reinterpret_cast<float*>(xs + p.xs_bytes);
   float* red = corr + groups_max * kCorrStride;  // [2][kPlanWarps][m][16]
@@ -218,9 +243,32 @@ plan_kernel(const PlanParams p) {
   const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
   const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) + (kHasLo ? t : 2 * t) * 4;
 
+  // Group packing: the group (inside a unit) and activation row(s) of this lane's two C
+  // columns, the group whose activations it feeds the MMAs with, one register set per group.
+  const uint32_t jl = kG > 1 ? (2u * t) / kCpg : 0u;
+  const uint32_t tl = kG > 1 ? t % (kCpg / 2) : t;
+  uint4 bset[kG];
+  bool load_bset[kG];
+  float gterm[kCorrPerTile];
+  bool load_g[kCorrPerTile];
+#pragma unroll
+  for (int j = 0; j < kG; ++j) {
+    bset[j] = make_uint4(0, 0, 0, 0);
+    load_bset[j] = kG > 1 && (g % kCpg) < active_cols && g / kCpg == static_cast<uint32_t>(j);
+  }
+#pragma unroll
+  for (int j = 0; j < kCorrPerTile; ++j) {
+    gterm[j] = 0.0f;
+    load_g[j] = (kHasLo ? tl : 2 * tl + j) < p.m;
+  }
+  const uint32_t gcorr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) +
+                              (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 4;
+  const uint32_t gscale_off = (jl >> 1) * kCB + kChunkWeightBytes + g * (4 * kScaleBytes) + (jl & 1u) * (2 * kScaleBytes);
+
   uint32_t cons_q = 0, red_buf = 0;
   for (uint32_t op = 0; op < p.op_count; ++op) {
     const PlanOpDev& o = p.ops[op];
+    KQ_TRACE(0);
     if (op > 0) {
       // every output of the previous op must be complete and visible before x is read
       __syncthreads();
@@ -239,10 +287,12 @@ plan_kernel(const PlanParams p) {
       }
       __syncthreads();
     }
+    KQ_TRACE(1);
     // stage the op's whole activation block (it fits: checked when the plan was built)
     stage_x<XT, kHasLo, kCorrStride, true>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, xs_stride, corr,
                                            p.error_flag);
     __syncthreads();
+    KQ_TRACE(2);
 
     const uint32_t slabs = o.slabs;
     for (uint32_t round = 0; round < o.rounds; ++round) {
@@ -267,6 +317,54 @@ plan_kernel(const PlanParams p) {
         }
         const uint32_t slot_addr = ring + slot * kSlotBytes;
         const uint32_t group0 = 2 * (it.c0 + first);
+        if constexpr (kG > 1) {
+          const uint32_t unit0 = (it.c0 + first) / kCU;
+#pragma unroll 2
+          for (uint32_t c = 0; c < nc; c += kCU) {
+            const uint32_t chunk_addr = slot_addr + c * kCB;
+            const uint32_t unit = unit0 + c / kCU;
+            uint4 wq[kCU];
+#pragma unroll
+            for (int cc = 0; cc < kCU; ++cc)
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(wq[cc].x), "=r"(wq[cc].y), "=r"(wq[cc].z), "=r"(wq[cc].w)
+                           : "r"(chunk_addr + cc * kCB + lane * 16));
+            float2 s;  // rows g, g + 8 of the lane's own group
+            if constexpr (kScaleF16) {
+              uint32_t raw;
+              asm volatile("ld.shared.u32 %0, [%1];" : "=r"(raw) : "r"(chunk_addr + gscale_off));
+              s = __half22float2(*reinterpret_cast<const __half2*>(&raw));
+            } else {
+              asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(s.x), "=f"(s.y) : "r"(chunk_addr + gscale_off));
+            }
+#pragma unroll
+            for (int j = 0; j < kG; ++j) lds_v4_if(bset[j], xs_lane + unit * 512, load_bset[j]);
+#pragma unroll
+            for (int j = 0; j < kCorrPerTile; ++j)
+              lds_f32_if(gterm[j], gcorr_lane + (unit * (kG * kCorrStride) + j) * 4, load_g[j]);
+            float cf[4];
+#pragma unroll
+            for (int j = 0; j < kG; ++j) {
+              const uint32_t wa = (j & 1) ? wq[j >> 1].z : wq[j >> 1].x;  // row g
+              const uint32_t wb = (j & 1) ? wq[j >> 1].w : wq[j >> 1].y;  // row g + 8
+              const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+              const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
+              const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
+              if (j == 0) mma_f16_zero(cf, a0, bset[j].x, bset[j].y);
+              else mma_f16(cf, a0, bset[j].x, bset[j].y);
+              mma_f16(cf, a1, bset[j].z, bset[j].w);
+            }
+            if constexpr (kHasLo) {
+              acc[0][0] = fmaf(s.x, (cf[0] + cf[1]) + gterm[0], acc[0][0]);
+              acc[0][1] = fmaf(s.y, (cf[2] + cf[3]) + gterm[0], acc[0][1]);
+            } else {
+              acc[0][0] = fmaf(s.x, cf[0] + gterm[0], acc[0][0]);
+              acc[0][1] = fmaf(s.x, cf[1] + gterm[1], acc[0][1]);
+              acc[0][2] = fmaf(s.y, cf[2] + gterm[0], acc[0][2]);
+              acc[0][3] = fmaf(s.y, cf[3] + gterm[1], acc[0][3]);
+            }
+          }
+        } else {
 #pragma unroll 2
         for (uint32_t c = 0; c < nc; ++c) {
           const uint32_t chunk_addr = slot_addr + c * kCB;
@@ -322,23 +420,33 @@ plan_kernel(const PlanParams p) {
             }
           }
         }
+        }
         __syncwarp();  // every lane has read the slot: it can take the next piece
         produce();
         cons_q += 1;
       }
 
       // ---- this round's outputs ------------------------------------------------------
+      if constexpr (kG > 1) {
+        // lanes whose C columns belong to different groups hold partial sums of the same outputs
+#pragma unroll
+        for (int j = 0; j < kAccPerTile; ++j) {
+          if constexpr (kG == 4) acc[0][j] += __shfl_xor_sync(0xffffffffu, acc[0][j], 1);
+          acc[0][j] += __shfl_xor_sync(0xffffffffu, acc[0][j], 2);
+        }
+      }
+      const bool owner = jl == 0;  // always true without group packing
       const uint32_t local_row = (it.rb - o.rb_begin[it.wi]) * 16u;  // first row of the block inside its weight
       const uint32_t n_i = o.n[it.wi];
       float* out = o.out[it.wi];
       const float* bias = o.bias[it.wi];
       if (slabs == 1) {
-        if (it.nck != 0) {
+        if (it.nck != 0 && owner) {
 #pragma unroll
           for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
 #pragma unroll
             for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
-              const uint32_t mm = kHasLo ? tile_m * 4 + t : tile_m * 8 + 2 * t + j;
+              const uint32_t mm = kHasLo ? tile_m * 4 + tl : tile_m * 8 + 2 * tl + j;
               if (mm >= p.m) continue;
               const float va = acc[tile_m][kHasLo ? 0 : j];
               const float vb = acc[tile_m][kHasLo ? 1 : 2 + j];
@@ -355,8 +463,8 @@ plan_kernel(const PlanParams p) {
       for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
 #pragma unroll
         for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
-          const uint32_t mm = kHasLo ? tile_m * 4 + t : tile_m * 8 + 2 * t + j;
-          if (mm >= p.m) continue;
+          const uint32_t mm = kHasLo ? tile_m * 4 + tl : tile_m * 8 + 2 * tl + j;
+          if (mm >= p.m || !owner) continue;
           mine[mm * 16 + g] = acc[tile_m][kHasLo ? 0 : j];          // zeros when the warp had no chunks
           mine[mm * 16 + g + 8] = acc[tile_m][kHasLo ? 1 : 2 + j];
         }
@@ -374,6 +482,394 @@ plan_kernel(const PlanParams p) {
       }
       red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
     }
+    KQ_TRACE(3);
+  }
+}
+
+// ---- paired kernel: two row blocks per warp, group-packed MMA tiles ---------------------
+// The fast path for one or two activation rows (at most 4 MMA columns).  Differences from
+// plan_kernel above:
+//   * a warp's work item is a PAIR of adjacent 16-row blocks over one k-slab; both blocks use
+//     the same staged activations, so one set of shared loads (and their predicates and
+//     addresses) feeds two independent MMA chains;
+//   * kG scale groups share one C tile (see qgemv_i4_gp_kernel), so a lane scales only the
+//     group its two C columns belong to;
+//   * a ring slot holds the same kPiece chunks of k for both blocks ([block 0][block 1]);
+//     full pieces are consumed by straight-line code with immediate address offsets;
+//   * the producer keeps its position inside the current item in registers and touches the
+//     op descriptor only when it moves to the next item.
+template <int... kIs, typename F>
+__device__ __forceinline__ void static_for_impl(std::integer_sequence<int, kIs...>, F&& f) {
+  (f(std::integral_constant<int, kIs>{}), ...);
+}
+template <int kN, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  static_for_impl(std::make_integer_sequence<int, kN>{}, static_cast<F&&>(f));
+}
+
+template <int kOff>
+__device__ __forceinline__ uint4 lds_v4_at(uint32_t base) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(base), "n"(kOff));
+  return v;
+}
+template <int kOff>
+__device__ __forceinline__ uint32_t lds_u32_at(uint32_t base) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(kOff));
+  return v;
+}
+template <int kOff>
+__device__ __forceinline__ uint2 lds_v2_at(uint32_t base) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(base), "n"(kOff));
+  return v;
+}
+template <int kOff>
+__device__ __forceinline__ void lds_v4_if_at(uint4& v, uint32_t base, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6];\n\t}"
+               : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+               : "r"(base), "r"(static_cast<uint32_t>(pred)), "n"(kOff));
+}
+template <int kOff>
+__device__ __forceinline__ void lds_f32_if_at(float& v, uint32_t base, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p ld.shared.f32 %0, [%1+%3];\n\t}"
+               : "+f"(v) : "r"(base), "r"(static_cast<uint32_t>(pred)), "n"(kOff));
+}
+
+struct PairItem {
+  const uint8_t* src;  // first chunk of the slab of the pair's first row block
+  uint32_t row_stride; // bytes from a chunk of the first block to the same chunk of the second
+  uint32_t nck;        // chunks in the slab (0: nothing to do)
+  uint32_t c0;         // first chunk index inside the row
+  uint32_t rb;         // first row block of the pair, inside the op
+  uint32_t wi;         // which weight of the op
+  bool valid;          // the pair exists (its outputs are stored)
+};
+
+template <uint32_t kCB>
+__device__ __forceinline__ PairItem pair_item_of(const PlanOpDev& o, uint32_t round, uint32_t warp, uint32_t grid,
+                                                 uint32_t cta) {
+  PairItem it;
+  it.src = nullptr;
+  it.row_stride = 0;
+  it.nck = 0;
+  it.c0 = 0;
+  it.rb = 0;
+  it.wi = 0;
+  it.valid = false;
+  uint32_t cta_eff = cta + o.rot;
+  if (cta_eff >= grid) cta_eff -= grid;
+  const uint32_t unit = round * grid + cta_eff;
+  if (unit >= o.cta_items) return it;
+  const uint32_t sub = warp >> o.slabs_log2, slab = warp & (o.slabs - 1u);
+  const uint32_t pair = unit * (static_cast<uint32_t>(kPlanWarps) >> o.slabs_log2) + sub;
+  it.rb = 2u * pair;
+  if (it.rb >= o.row_blocks) return it;
+  it.valid = true;
+#pragma unroll
+  for (int i = 1; i < kMaxMulti; ++i)
+    if (i < static_cast<int>(o.count) && it.rb >= o.rb_begin[i]) it.wi = i;
+  it.c0 = slab * o.chunks_per_slab;
+  if (it.c0 >= o.chunks_per_row) return it;
+  it.nck = min(o.chunks_per_slab, o.chunks_per_row - it.c0);
+  it.row_stride = o.chunks_per_row * kCB;
+  it.src = o.w[it.wi] + (static_cast<size_t>(it.rb - o.rb_begin[it.wi]) * o.chunks_per_row + it.c0) * kCB;
+  return it;
+}
+
+template <typename XT, bool kScaleF16, int kG, int kPiece>
+__global__ void __launch_bounds__(kPlanWarps * 32, 1)
+plan_pair_kernel(const PlanParams p) {
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
+  constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;
+  constexpr int kCpg = 8 / kG;          // MMA columns per group
+  constexpr int kCU = kG / 2;           // chunks per unit
+  constexpr int kPieceUnits = kPiece / kCU;
+  constexpr uint32_t kSlotBytes = 2u * kPiece * kCB;  // both row blocks
+  constexpr int kAcc = kHasLo ? 2 : 4;
+  constexpr int kCorr = kHasLo ? 1 : 2;
+  constexpr int kCorrStride = kHasLo ? kCpg / 2 : kCpg;
+  constexpr uint32_t kMask0 = 0x000F000Fu, kMask1 = 0x00F000F0u;
+  static_assert(kG == 2 || kG == 4, "units of two or four groups");
+  static_assert(kPiece % kCU == 0, "pieces hold whole units");
+
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+  const uint32_t grid = gridDim.x, cta = blockIdx.x;
+
+  // shared memory: [warp rings][mbarriers][staged x][corr][reduction buffers x2]
+  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const uint32_t ring = smem_base + warp * (kSlots * kSlotBytes);
+  const uint32_t bars = smem_base + kPlanWarps * kSlots * kSlotBytes + warp * (kSlots * 8);
+  uint8_t* xs = smem + kPlanWarps * kSlots * kSlotBytes + kPlanWarps * kSlots * 8;
+  const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
+  constexpr uint32_t kXsStride = kCpg * 64u;
+  const uint32_t groups_max = p.xs_bytes / kXsStride;
+  float* corr = reinterpret_cast<float*>(xs + p.xs_bytes);
+  float* red = corr + groups_max * kCorrStride;  // [2][kPlanWarps][2][m][16]
+  // A window of op descriptors in shared memory (entry i lives in slot i % kOpWindow): the
+  // producer and the consumer read them every item, and a chain of dependent global loads
+  // there would sit on every warp's critical path.
+  PlanOpDev* win = reinterpret_cast<PlanOpDev*>(
+      (reinterpret_cast<uintptr_t>(red + 2 * kPlanWarps * 2 * p.m * 16) + 15) & ~static_cast<uintptr_t>(15));
+  auto fill_window = [&](uint32_t idx) {
+    if (idx >= p.op_count) return;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(p.ops + idx);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(win + idx % kOpWindow);
+    for (uint32_t i = threadIdx.x; i < sizeof(PlanOpDev) / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+  };
+  for (uint32_t i = 0; i + 2 <= kOpWindow; ++i) fill_window(i);  // entries 0 .. kOpWindow - 2
+  uint32_t cur_op = 0;  // the op this warp is working on; entries up to cur_op + kOpWindow - 2 are valid
+  auto desc = [&](uint32_t idx) -> const PlanOpDev& {
+    return idx + 2 <= cur_op + kOpWindow ? win[idx % kOpWindow] : p.ops[idx];
+  };
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) mbar_init(bars + s * 8, 1);
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+
+  // ---- producer -------------------------------------------------------------------------
+  uint32_t prod_op = 0, prod_round = 0, prod_q = 0, prod_left = 0, prod_stride = 0;
+  const uint8_t* prod_src = nullptr;
+  auto produce = [&]() {
+    while (prod_left == 0) {  // move to this warp's next item, whatever op it belongs to
+      if (prod_op >= p.op_count) return;
+      const PlanOpDev& o = desc(prod_op);
+      if (prod_round >= o.rounds) {
+        prod_op += 1;
+        prod_round = 0;
+        continue;
+      }
+      const PairItem it = pair_item_of<kCB>(o, prod_round, warp, grid, cta);
+      prod_round += 1;
+      prod_left = it.nck;
+      prod_src = it.src;
+      prod_stride = it.row_stride;
+    }
+    const uint32_t nc = min(static_cast<uint32_t>(kPiece), prod_left);
+    const uint32_t slot = prod_q & 1u;
+    if (lane == 0) {
+      mbar_expect_tx(bars + slot * 8, 2u * nc * kCB);
+      bulk_copy_g2s(ring + slot * kSlotBytes, prod_src, nc * kCB, bars + slot * 8);
+      bulk_copy_g2s(ring + slot * kSlotBytes + kPiece * kCB, prod_src + prod_stride, nc * kCB, bars + slot * 8);
+    }
+    prod_src += nc * kCB;
+    prod_left -= nc;
+    prod_q += 1;
+  };
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) produce();
+
+  // ---- per-lane constants of the packed MMA tile -----------------------------------------
+  const uint32_t jl = (2u * t) / kCpg;      // group (inside a unit) of this lane's two C columns
+  const uint32_t tl = t % (kCpg / 2);       // which activation row(s) inside that group
+  uint4 bset[kG];
+  bool load_bset[kG];
+  float gterm[kCorr];
+  bool load_g[kCorr];
+#pragma unroll
+  for (int j = 0; j < kG; ++j) {
+    bset[j] = make_uint4(0, 0, 0, 0);
+    load_bset[j] = (g % kCpg) < active_cols && g / kCpg == static_cast<uint32_t>(j);
+  }
+#pragma unroll
+  for (int j = 0; j < kCorr; ++j) {
+    gterm[j] = 0.0f;
+    load_g[j] = (kHasLo ? tl : 2 * tl + j) < p.m;
+  }
+  const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
+  const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) +
+                             (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 4;
+  const uint32_t scale_lane = (jl >> 1) * kCB + kChunkWeightBytes + g * (4 * kScaleBytes) + (jl & 1u) * (2 * kScaleBytes);
+
+  float acc[2][kAcc];
+
+  // One unit (kG groups) of both row blocks.  kU selects immediate offsets; callers that
+  // cannot unroll pass kU = 0 and pre-advanced base addresses.
+  auto unit_step = [&](auto ku, uint32_t w_base, uint32_t s_base, uint32_t xs_base, uint32_t corr_base) {
+    constexpr int kU = decltype(ku)::value;
+    uint4 wq[2][kCU];
+    float2 sc[2];
+    static_for<2>([&](auto kr) {
+      constexpr int kR = decltype(kr)::value;
+      constexpr int kChunk0 = kR * kPiece + kU * kCU;  // first chunk of the unit inside the slot
+      wq[kR][0] = lds_v4_at<kChunk0 * kCB>(w_base);
+      if constexpr (kCU == 2) wq[kR][1] = lds_v4_at<(kChunk0 + 1) * kCB>(w_base);
+      if constexpr (kScaleF16) {
+        const uint32_t raw = lds_u32_at<kChunk0 * kCB>(s_base);
+        sc[kR] = __half22float2(*reinterpret_cast<const __half2*>(&raw));
+      } else {
+        const uint2 raw = lds_v2_at<kChunk0 * kCB>(s_base);
+        sc[kR] = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.y));
+      }
+    });
+#pragma unroll
+    for (int j = 0; j < kG; ++j) lds_v4_if_at<kU * 512>(bset[j], xs_base, load_bset[j]);
+    static_for<kCorr>([&](auto kj) {
+      constexpr int kJ = decltype(kj)::value;
+      lds_f32_if_at<(kU * kG * kCorrStride + kJ) * 4>(gterm[kJ], corr_base, load_g[kJ]);
+    });
+    float cf[2][4];
+#pragma unroll
+    for (int j = 0; j < kG; ++j) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const uint4 wv = wq[r][j >> 1];
+        const uint32_t wa = (j & 1) ? wv.z : wv.x;  // row g
+        const uint32_t wb = (j & 1) ? wv.w : wv.y;  // row g + 8
+        const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+        const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
+        const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
+        if (j == 0) mma_f16_zero(cf[r], a0, bset[j].x, bset[j].y);
+        else mma_f16(cf[r], a0, bset[j].x, bset[j].y);
+        mma_f16(cf[r], a1, bset[j].z, bset[j].w);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if constexpr (kHasLo) {
+        acc[r][0] = fmaf(sc[r].x, (cf[r][0] + cf[r][1]) + gterm[0], acc[r][0]);
+        acc[r][1] = fmaf(sc[r].y, (cf[r][2] + cf[r][3]) + gterm[0], acc[r][1]);
+      } else {
+        acc[r][0] = fmaf(sc[r].x, cf[r][0] + gterm[0], acc[r][0]);
+        acc[r][1] = fmaf(sc[r].x, cf[r][1] + gterm[1], acc[r][1]);
+        acc[r][2] = fmaf(sc[r].y, cf[r][2] + gterm[0], acc[r][2]);
+        acc[r][3] = fmaf(sc[r].y, cf[r][3] + gterm[1], acc[r][3]);
+      }
+    }
+  };
+
+  uint32_t cons_q = 0, red_buf = 0;
+  for (uint32_t op = 0; op < p.op_count; ++op) {
+    KQ_TRACE(0);
+    if (op > 0) {
+      // Slot (op - 2) % kOpWindow is dead: every warp passed the barrier of op - 1.
+      fill_window(op + kOpWindow - 2);
+      // every output of the previous op must be complete and visible before x is read
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(p.grid_bar, 1u);
+        const unsigned int target = op * grid;
+        uint32_t spins = 0;
+        while (ld_acquire_gpu(p.grid_bar) < target) {
+          if (++spins > kSpinLimit) {
+            *reinterpret_cast<volatile int*>(p.status) = 1;
+            break;
+          }
+        }
+        __threadfence();
+      }
+      __syncthreads();
+    }
+    cur_op = op;
+    const PlanOpDev& o = win[op % kOpWindow];
+    KQ_TRACE(1);
+    stage_x<XT, kHasLo, kCorrStride, true>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr,
+                                           p.error_flag);
+    __syncthreads();
+    KQ_TRACE(2);
+
+    const uint32_t slabs = o.slabs, rounds = o.rounds;
+    for (uint32_t round = 0; round < rounds; ++round) {
+      const PairItem it = pair_item_of<kCB>(o, round, warp, grid, cta);
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) acc[r][j] = 0.0f;
+
+      for (uint32_t first = 0; first < it.nck; first += kPiece) {
+        const uint32_t nc = min(static_cast<uint32_t>(kPiece), it.nck - first);
+        const uint32_t slot = cons_q & 1u, parity = (cons_q >> 1) & 1u;
+        {
+          uint32_t spins = 0;
+          while (!mbar_try_wait(bars + slot * 8, parity)) {
+            if (++spins > kSpinLimit) {
+              *reinterpret_cast<volatile int*>(p.status) = 2;
+              break;
+            }
+          }
+        }
+        const uint32_t slot_addr = ring + slot * kSlotBytes;
+        const uint32_t unit0 = (it.c0 + first) / kCU;
+        const uint32_t w_base = slot_addr + lane * 16, s_base = slot_addr + scale_lane;
+        const uint32_t xs_base = xs_lane + unit0 * 512, corr_base = corr_lane + unit0 * (kG * kCorrStride * 4);
+        if (nc == kPiece) {
+          static_for<kPieceUnits>([&](auto ku) { unit_step(ku, w_base, s_base, xs_base, corr_base); });
+        } else {
+          for (uint32_t u = 0; u * kCU < nc; ++u)
+            unit_step(std::integral_constant<int, 0>{}, w_base + u * (kCU * kCB), s_base + u * (kCU * kCB),
+                      xs_base + u * 512, corr_base + u * (kG * kCorrStride * 4));
+        }
+        __syncwarp();  // every lane has read the slot: it can take the next piece
+        produce();
+        cons_q += 1;
+      }
+
+      // ---- this round's outputs ------------------------------------------------------
+      // lanes whose C columns belong to different groups hold partial sums of the same outputs
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int j = 0; j < kAcc; ++j) {
+          if constexpr (kG == 4) acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 1);
+          acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 2);
+        }
+      const bool owner = jl == 0;
+      const uint32_t local_row = (it.rb - o.rb_begin[it.wi]) * 16u;  // first row of the pair inside its weight
+      const uint32_t n_i = o.n[it.wi];
+      float* out = o.out[it.wi];
+      const float* bias = o.bias[it.wi];
+      if (slabs == 1) {
+        if (it.nck != 0 && owner) {
+#pragma unroll
+          for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
+              const uint32_t mm = kHasLo ? tl : 2 * tl + j;
+              if (mm >= p.m) continue;
+              const uint32_t row = local_row + r * 16 + g;
+              out[static_cast<size_t>(mm) * n_i + row] = fmaf(acc[r][kHasLo ? 0 : j], kUnscale, bias[row]);
+              out[static_cast<size_t>(mm) * n_i + row + 8] = fmaf(acc[r][kHasLo ? 1 : 2 + j], kUnscale, bias[row + 8]);
+            }
+        }
+        continue;
+      }
+      // K was split over `slabs` warps of this CTA: meet in shared memory, add in slab order.
+      float* mine = red + (static_cast<size_t>(red_buf) * kPlanWarps + warp) * (2 * p.m * 16);
+      if (owner) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
+            const uint32_t mm = kHasLo ? tl : 2 * tl + j;
+            if (mm >= p.m) continue;
+            mine[(r * p.m + mm) * 16 + g] = acc[r][kHasLo ? 0 : j];  // zeros when the warp had no chunks
+            mine[(r * p.m + mm) * 16 + g + 8] = acc[r][kHasLo ? 1 : 2 + j];
+          }
+      }
+      __syncthreads();
+      if ((warp & (slabs - 1u)) == 0 && it.valid) {
+        const float* first_slab = mine;
+        for (uint32_t idx = lane; idx < 32u * p.m; idx += 32) {
+          float total = 0.0f;
+          for (uint32_t s = 0; s < slabs; ++s) total += first_slab[static_cast<size_t>(s) * (2 * p.m * 16) + idx];
+          const uint32_t r = idx / (p.m * 16), rem = idx - r * (p.m * 16);
+          const uint32_t mm = rem >> 4, row = local_row + r * 16 + (rem & 15u);
+          out[static_cast<size_t>(mm) * n_i + row] = fmaf(total, kUnscale, bias[row]);
+        }
+      }
+      red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
+    }
+    KQ_TRACE(3);
   }
 }
 
@@ -399,6 +895,10 @@ struct Plan {
   int x_dtype = 0;
   int scale_dtype = 0;
   uint32_t k_max = 0;
+  bool all_even_chunks = true;  // every op's k is a multiple of 128
+  bool all_even_blocks = true;  // every weight has a whole number of 32-row pairs
+  bool paired = false;          // plan_pair_kernel: work items are pairs of row blocks
+  uint32_t unit_chunks = 1;     // chunks the kernel consumes at a time (slabs are whole units)
   int grid = 0;
   size_t smem = 0;
   uint32_t xs_bytes = 0;
@@ -409,17 +909,20 @@ namespace {
 
 constexpr size_t kSmemBudget = 227 * 1024;
 
-template <typename XT, bool kScaleF16, int kCols, int kSlotChunks>
+template <typename XT, bool kScaleF16, int kCols, int kSlotChunks, int kG>
 cudaError_t configure(Plan& plan, int sm_count, bool* fits) {
-  auto kernel = plan_kernel<XT, kScaleF16, kCols, kSlotChunks>;
+  auto kernel = plan_kernel<XT, kScaleF16, kCols, kSlotChunks, kG>;
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  constexpr uint32_t kCpg = 8 / kG;
   const uint32_t cb = kChunkWeightBytes + 32u * (kScaleF16 ? 2u : 4u);
   const uint32_t active_cols = kHasLo ? 2 * plan.m : plan.m;
   const uint32_t groups = plan.k_max / 32;
-  const size_t xs_bytes = static_cast<size_t>(groups) * active_cols * 64;
+  const size_t xs_bytes = static_cast<size_t>(groups) * (kG > 1 ? kCpg : active_cols) * 64;
+  const uint32_t corr_stride = kG > 1 ? (kHasLo ? kCpg / 2 : kCpg) : (kHasLo ? kCols / 2 : kCols);
   const size_t smem = static_cast<size_t>(kPlanWarps) * kSlots * kSlotChunks * cb + kPlanWarps * kSlots * 8 + xs_bytes +
-                      static_cast<size_t>(groups) * (kHasLo ? kCols / 2 : kCols) * 4 +
+                      static_cast<size_t>(groups) * corr_stride * 4 +
                       static_cast<size_t>(2) * kPlanWarps * plan.m * 16 * sizeof(float);
+  plan.unit_chunks = kG > 1 ? kG / 2 : 1;
   *fits = smem <= kSmemBudget;
   if (!*fits) return cudaSuccess;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -435,12 +938,48 @@ cudaError_t configure(Plan& plan, int sm_count, bool* fits) {
   return cudaSuccess;
 }
 
-// Deep weight rings when the staged activations leave room for them, shallower ones otherwise.
-template <typename XT, bool kScaleF16, int kCols>
-cudaError_t configure_slots(Plan& plan, int sm_count, bool* fits) {
-  cudaError_t e = configure<XT, kScaleF16, kCols, 8>(plan, sm_count, fits);
+template <typename XT, bool kScaleF16, int kG, int kPiece>
+cudaError_t configure_pair(Plan& plan, int sm_count, bool* fits) {
+  auto kernel = plan_pair_kernel<XT, kScaleF16, kG, kPiece>;
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  constexpr uint32_t kCpg = 8 / kG;
+  const uint32_t cb = kChunkWeightBytes + 32u * (kScaleF16 ? 2u : 4u);
+  const uint32_t groups = plan.k_max / 32;
+  const size_t xs_bytes = static_cast<size_t>(groups) * kCpg * 64;
+  const size_t smem = static_cast<size_t>(kPlanWarps) * kSlots * 2 * kPiece * cb + kPlanWarps * kSlots * 8 + xs_bytes +
+                      static_cast<size_t>(groups) * (kHasLo ? kCpg / 2 : kCpg) * 4 +
+                      static_cast<size_t>(2) * kPlanWarps * 2 * plan.m * 16 * sizeof(float) + 16 +
+                      kOpWindow * sizeof(PlanOpDev);
+  *fits = smem <= kSmemBudget;
+  if (!*fits) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  int per_sm = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPlanWarps * 32, smem);
+  if (e != cudaSuccess) return e;
+  if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+  plan.kernel = reinterpret_cast<void*>(kernel);
+  plan.smem = smem;
+  plan.xs_bytes = static_cast<uint32_t>(xs_bytes);
+  plan.grid = sm_count;
+  plan.unit_chunks = kG / 2;
+  plan.paired = true;
+  return cudaSuccess;
+}
+
+template <typename XT, bool kScaleF16, int kG>
+cudaError_t configure_pair_slots(Plan& plan, int sm_count, bool* fits) {
+  cudaError_t e = configure_pair<XT, kScaleF16, kG, 4>(plan, sm_count, fits);
   if (e != cudaSuccess || *fits) return e;
-  return configure<XT, kScaleF16, kCols, 4>(plan, sm_count, fits);
+  return configure_pair<XT, kScaleF16, kG, 2>(plan, sm_count, fits);
+}
+
+// Deep weight rings when the staged activations leave room for them, shallower ones otherwise.
+template <typename XT, bool kScaleF16, int kCols, int kG>
+cudaError_t configure_slots(Plan& plan, int sm_count, bool* fits) {
+  cudaError_t e = configure<XT, kScaleF16, kCols, 8, kG>(plan, sm_count, fits);
+  if (e != cudaSuccess || *fits) return e;
+  return configure<XT, kScaleF16, kCols, 4, kG>(plan, sm_count, fits);
 }
 
 template <typename XT>
@@ -448,12 +987,26 @@ cudaError_t configure_x(Plan& plan, int sm_count, bool* fits) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   const bool f16s = plan.scale_dtype == KQ_F16;
   const uint32_t cols = kHasLo ? 2 * plan.m : plan.m;
+  // Few columns: several scale groups share one MMA tile (four need whole pairs of chunks);
+  // with whole 32-row pairs everywhere, the paired kernel.
+  if (KQ_PLAN_PAIRED && plan.all_even_blocks && cols <= 4) {
+    cudaError_t e;
+    if (cols <= 2 && plan.all_even_chunks)
+      e = f16s ? configure_pair_slots<XT, true, 4>(plan, sm_count, fits) : configure_pair_slots<XT, false, 4>(plan, sm_count, fits);
+    else
+      e = f16s ? configure_pair_slots<XT, true, 2>(plan, sm_count, fits) : configure_pair_slots<XT, false, 2>(plan, sm_count, fits);
+    if (e != cudaSuccess || *fits) return e;
+  }
+  if (cols <= 2 && plan.all_even_chunks)
+    return f16s ? configure_slots<XT, true, 8, 4>(plan, sm_count, fits) : configure_slots<XT, false, 8, 4>(plan, sm_count, fits);
+  if (cols <= 4)
+    return f16s ? configure_slots<XT, true, 8, 2>(plan, sm_count, fits) : configure_slots<XT, false, 8, 2>(plan, sm_count, fits);
   if (cols <= 8)
-    return f16s ? configure_slots<XT, true, 8>(plan, sm_count, fits) : configure_slots<XT, false, 8>(plan, sm_count, fits);
+    return f16s ? configure_slots<XT, true, 8, 1>(plan, sm_count, fits) : configure_slots<XT, false, 8, 1>(plan, sm_count, fits);
   if (cols <= 16)
-    return f16s ? configure_slots<XT, true, 16>(plan, sm_count, fits) : configure_slots<XT, false, 16>(plan, sm_count, fits);
+    return f16s ? configure_slots<XT, true, 16, 1>(plan, sm_count, fits) : configure_slots<XT, false, 16, 1>(plan, sm_count, fits);
   if constexpr (kHasLo) {
-    return f16s ? configure_slots<XT, true, 32>(plan, sm_count, fits) : configure_slots<XT, false, 32>(plan, sm_count, fits);
+    return f16s ? configure_slots<XT, true, 32, 1>(plan, sm_count, fits) : configure_slots<XT, false, 32, 1>(plan, sm_count, fits);
   } else {
     return cudaErrorInvalidValue;
   }
@@ -470,14 +1023,19 @@ cudaError_t configure_any(Plan& plan, int sm_count, bool* fits) {
 
 // How an op is cut once the grid size is known: split K over S warps of a CTA until the
 // op offers work to most of the grid; a pure function of the shape.
-void shape_op(PlanOpDev& o, uint32_t grid, uint32_t* rot) {
-  uint32_t s = 1;
-  while (s < static_cast<uint32_t>(kPlanWarps) && s * 2 <= o.chunks_per_row &&
-         (o.row_blocks + kPlanWarps / s - 1) / (kPlanWarps / s) < (grid * 3) / 5)
+void shape_op(PlanOpDev& o, uint32_t grid, uint32_t unit_chunks, bool paired, uint32_t* rot) {
+  uint32_t s = 1, log2 = 0;
+  const uint32_t units_per_row = o.chunks_per_row / unit_chunks;
+  const uint32_t items = paired ? o.row_blocks / 2 : o.row_blocks;  // what one warp works on per round
+  while (s < static_cast<uint32_t>(kPlanWarps) && s * 2 <= units_per_row &&
+         (items + kPlanWarps / s - 1) / (kPlanWarps / s) < (grid * 3) / 5) {
     s *= 2;
+    ++log2;
+  }
   o.slabs = s;
-  o.chunks_per_slab = (o.chunks_per_row + s - 1) / s;
-  o.cta_items = (o.row_blocks + kPlanWarps / s - 1) / (kPlanWarps / s);
+  o.slabs_log2 = log2;
+  o.chunks_per_slab = (units_per_row + s - 1) / s * unit_chunks;
+  o.cta_items = (items + kPlanWarps / s - 1) / (kPlanWarps / s);
   o.rounds = (o.cta_items + grid - 1) / grid;
   o.rot = *rot;
   *rot = (*rot + o.cta_items) % grid;  // the next op starts where this one left the grid idle
@@ -547,6 +1105,8 @@ const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, 
     return "ops of one plan must share m, the activation type and the scale type";
   }
   plan->k_max = std::max(plan->k_max, o.k);
+  plan->all_even_chunks = plan->all_even_chunks && o.chunks_per_row % 2 == 0;
+  for (int i = 0; i < count; ++i) plan->all_even_blocks = plan->all_even_blocks && targets[i].w->n % 32 == 0;
   plan->ops.push_back(o);
   return "";
 }
@@ -567,7 +1127,7 @@ cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why) {
     return cudaErrorInvalidValue;
   }
   uint32_t rot = 0;
-  for (PlanOpDev& o : plan->ops) shape_op(o, static_cast<uint32_t>(plan->grid), &rot);
+  for (PlanOpDev& o : plan->ops) shape_op(o, static_cast<uint32_t>(plan->grid), plan->unit_chunks, plan->paired, &rot);
   e = cudaMalloc(reinterpret_cast<void**>(&plan->ops_dev), plan->ops.size() * sizeof(PlanOpDev));
   if (e == cudaSuccess) e = cudaMemcpy(plan->ops_dev, plan->ops.data(), plan->ops.size() * sizeof(PlanOpDev), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&plan->grid_bar), sizeof(unsigned int));
@@ -578,6 +1138,16 @@ cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why) {
   }
   return e;
 }
+
+#ifdef KQ_PLAN_TRACE
+static unsigned long long* g_trace_dev = nullptr;
+static uint32_t g_trace_ops = 0;
+extern "C" __attribute__((visibility("default"))) int kq_debug_plan_trace(unsigned long long* out, uint32_t* ops) {
+  cudaDeviceSynchronize();
+  *ops = g_trace_ops;
+  return cudaMemcpy(out, g_trace_dev, 148ull * g_trace_ops * 4 * 8, cudaMemcpyDeviceToHost);
+}
+#endif
 
 cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
   cudaError_t e = cudaSuccess;
@@ -595,6 +1165,13 @@ cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
   p.grid_bar = plan->grid_bar;
   p.error_flag = env.error_flag;
   p.status = plan->status_dev;
+#ifdef KQ_PLAN_TRACE
+  static unsigned long long* trace_dev = nullptr;
+  if (!trace_dev) cudaMalloc(reinterpret_cast<void**>(&trace_dev), 148ull * 256 * 4 * 8);
+  p.trace = trace_dev;
+  g_trace_dev = trace_dev;
+  g_trace_ops = p.op_count;
+#endif
   void* args[] = {&p};
   e = cudaLaunchCooperativeKernel(plan->kernel, dim3(plan->grid), dim3(kPlanWarps * 32), args, plan->smem, env.stream);
   if (e != cudaSuccess) return e;
@@ -668,6 +1245,8 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
   cfg.x_dtype = x_dtype;
   cfg.scale_dtype = target.w->scale_dtype;
   cfg.k_max = o.k;
+  cfg.all_even_chunks = o.chunks_per_row % 2 == 0;
+  cfg.all_even_blocks = target.w->n % 32 == 0;
   bool fits = false;
   e = configure_any(cfg, env.sm_count, &fits);
   if (e != cudaSuccess) return e;
@@ -677,7 +1256,7 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
     return cudaErrorInvalidValue;
   }
   uint32_t rot = 0;
-  shape_op(o, static_cast<uint32_t>(cfg.grid), &rot);
+  shape_op(o, static_cast<uint32_t>(cfg.grid), cfg.unit_chunks, cfg.paired, &rot);
 
   e = cudaMemcpyAsync(base + kStaticOpOff, &o, sizeof(o), cudaMemcpyHostToDevice, env.stream);
   if (e != cudaSuccess) return e;
@@ -691,6 +1270,10 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
   p.grid_bar = reinterpret_cast<unsigned int*>(base + kStaticBarOff);
   p.error_flag = env.error_flag;
   p.status = reinterpret_cast<int*>(base + kStaticStatusOff);
+#ifdef KQ_PLAN_TRACE
+  if (!g_trace_dev) cudaMalloc(reinterpret_cast<void**>(&g_trace_dev), 148ull * 256 * 4 * 8);
+  p.trace = g_trace_dev;
+#endif
   void* args[] = {&p};
   e = cudaLaunchCooperativeKernel(cfg.kernel, dim3(cfg.grid), dim3(kPlanWarps * 32), args, cfg.smem, env.stream);
   if (e != cudaSuccess) return e;
