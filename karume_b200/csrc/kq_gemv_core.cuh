@@ -60,11 +60,12 @@ __device__ __forceinline__ void load_x8(const XT* p, float (&v)[8]) {
 //   corr : [local group][kCorrStride] f32; entry r = -8 * 2^-24 * (sum of the group's x
 //          of activation row r, as staged): the "- 8" of the storage rule
 // Four consecutive threads share one (group, row): each converts one octet.
-template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2 = false>
+// kBatch: octets a thread loads before it converts any (one memory round trip per batch, at
+// the price of 8 registers per octet held).
+template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2 = false, int kBatch = 1>
 __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, uint32_t k,
                                         uint32_t group0, uint32_t groups, uint8_t* xs,
                                         uint32_t xs_stride, float* corr, int* error_flag) {
-  constexpr int kBatch = 4;  // octets a thread loads before it converts any: one memory round trip per batch
   const uint32_t items = groups * m * 4;
   const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles below
   bool out_of_range = false;

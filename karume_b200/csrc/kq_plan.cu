@@ -79,7 +79,7 @@ __device__ __forceinline__ unsigned long long gtime() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-#define KQ_TRACE(slot) do { if (threadIdx.x == 0) p.trace[(static_cast<size_t>(cta) * p.op_count + op) * 4 + (slot)] = gtime(); } while (0)
+#define KQ_TRACE(slot) do { if (threadIdx.x == 0) p.trace[(static_cast<size_t>(cta) * p.op_count + op) * 8 + (slot)] = gtime(); } while (0)
 #else
 #define KQ_TRACE(slot) do {} while (0)
 #endif
@@ -750,14 +750,17 @@ plan_pair_kernel(const PlanParams p) {
   uint32_t cons_q = 0, red_buf = 0;
   for (uint32_t op = 0; op < p.op_count; ++op) {
     KQ_TRACE(0);
+    // Nothing about the first item depends on the previous op: look it up before the wait.
+    const PairItem first_item = pair_item_of<kCB>(win[op % kOpWindow], 0, warp, grid, cta);
     if (op > 0) {
       // Slot (op - 2) % kOpWindow is dead: every warp passed the barrier of op - 1.
       fill_window(op + kOpWindow - 2);
       // every output of the previous op must be complete and visible before x is read
       __syncthreads();
       if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(p.grid_bar, 1u);
+        // release: the CTA's stores (ordered before this by the barrier above) become visible
+        // to whoever acquires the counter
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.grid_bar) : "memory");
         const unsigned int target = op * grid;
         uint32_t spins = 0;
         while (ld_acquire_gpu(p.grid_bar) < target) {
@@ -766,25 +769,41 @@ plan_pair_kernel(const PlanParams p) {
             break;
           }
         }
-        __threadfence();
       }
       __syncthreads();
     }
     cur_op = op;
     const PlanOpDev& o = win[op % kOpWindow];
     KQ_TRACE(1);
-    stage_x<XT, kHasLo, kCorrStride, true>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr,
+    stage_x<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr,
                                            p.error_flag);
     __syncthreads();
     KQ_TRACE(2);
 
     const uint32_t slabs = o.slabs, rounds = o.rounds;
     for (uint32_t round = 0; round < rounds; ++round) {
-      const PairItem it = pair_item_of<kCB>(o, round, warp, grid, cta);
+      const PairItem it = round == 0 ? first_item : pair_item_of<kCB>(o, round, warp, grid, cta);
 #pragma unroll
       for (int r = 0; r < 2; ++r)
 #pragma unroll
         for (int j = 0; j < kAcc; ++j) acc[r][j] = 0.0f;
+      // (1) the bias of the rows this lane will store, fetched while the weights are consumed
+      const uint32_t local_row = (it.rb - o.rb_begin[it.wi]) * 16u;  // first row of the pair inside its weight
+      const uint32_t n_i = o.n[it.wi];
+      float* out = o.out[it.wi];
+      const float* bias = o.bias[it.wi];
+      float bias_pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      if (it.valid) {
+        if (o.slabs == 1) {
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            bias_pre[2 * r] = bias[local_row + r * 16 + g];
+            bias_pre[2 * r + 1] = bias[local_row + r * 16 + g + 8];
+          }
+        } else {
+          bias_pre[0] = bias[local_row + lane];  // the reducer's first pass covers rows lane of the pair
+        }
+      }
 
       for (uint32_t first = 0; first < it.nck; first += kPiece) {
         const uint32_t nc = min(static_cast<uint32_t>(kPiece), it.nck - first);
@@ -798,6 +817,7 @@ plan_pair_kernel(const PlanParams p) {
             }
           }
         }
+        if (first == 0 && round == 0) KQ_TRACE(4);
         const uint32_t slot_addr = ring + slot * kSlotBytes;
         const uint32_t unit0 = (it.c0 + first) / kCU;
         const uint32_t w_base = slot_addr + lane * 16, s_base = slot_addr + scale_lane;
@@ -814,6 +834,7 @@ plan_pair_kernel(const PlanParams p) {
         cons_q += 1;
       }
 
+      if (round == 0) KQ_TRACE(5);
       // ---- this round's outputs ------------------------------------------------------
       // lanes whose C columns belong to different groups hold partial sums of the same outputs
 #pragma unroll
@@ -824,10 +845,6 @@ plan_pair_kernel(const PlanParams p) {
           acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 2);
         }
       const bool owner = jl == 0;
-      const uint32_t local_row = (it.rb - o.rb_begin[it.wi]) * 16u;  // first row of the pair inside its weight
-      const uint32_t n_i = o.n[it.wi];
-      float* out = o.out[it.wi];
-      const float* bias = o.bias[it.wi];
       if (slabs == 1) {
         if (it.nck != 0 && owner) {
 #pragma unroll
@@ -837,8 +854,8 @@ plan_pair_kernel(const PlanParams p) {
               const uint32_t mm = kHasLo ? tl : 2 * tl + j;
               if (mm >= p.m) continue;
               const uint32_t row = local_row + r * 16 + g;
-              out[static_cast<size_t>(mm) * n_i + row] = fmaf(acc[r][kHasLo ? 0 : j], kUnscale, bias[row]);
-              out[static_cast<size_t>(mm) * n_i + row + 8] = fmaf(acc[r][kHasLo ? 1 : 2 + j], kUnscale, bias[row + 8]);
+              out[static_cast<size_t>(mm) * n_i + row] = fmaf(acc[r][kHasLo ? 0 : j], kUnscale, bias_pre[2 * r]);
+              out[static_cast<size_t>(mm) * n_i + row + 8] = fmaf(acc[r][kHasLo ? 1 : 2 + j], kUnscale, bias_pre[2 * r + 1]);
             }
         }
         continue;
@@ -857,6 +874,7 @@ plan_pair_kernel(const PlanParams p) {
           }
       }
       __syncthreads();
+      if (round == 0) KQ_TRACE(6);
       if ((warp & (slabs - 1u)) == 0 && it.valid) {
         const float* first_slab = mine;
         for (uint32_t idx = lane; idx < 32u * p.m; idx += 32) {
@@ -864,7 +882,9 @@ plan_pair_kernel(const PlanParams p) {
           for (uint32_t s = 0; s < slabs; ++s) total += first_slab[static_cast<size_t>(s) * (2 * p.m * 16) + idx];
           const uint32_t r = idx / (p.m * 16), rem = idx - r * (p.m * 16);
           const uint32_t mm = rem >> 4, row = local_row + r * 16 + (rem & 15u);
-          out[static_cast<size_t>(mm) * n_i + row] = fmaf(total, kUnscale, bias[row]);
+          // idx == lane in the first pass: row r * 16 + (lane & 15) of activation row 0 when m == 1
+          const float b = (idx == lane && p.m == 1) ? bias_pre[0] : bias[row];
+          out[static_cast<size_t>(mm) * n_i + row] = fmaf(total, kUnscale, b);
         }
       }
       red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
@@ -1145,7 +1165,7 @@ static uint32_t g_trace_ops = 0;
 extern "C" __attribute__((visibility("default"))) int kq_debug_plan_trace(unsigned long long* out, uint32_t* ops) {
   cudaDeviceSynchronize();
   *ops = g_trace_ops;
-  return cudaMemcpy(out, g_trace_dev, 148ull * g_trace_ops * 4 * 8, cudaMemcpyDeviceToHost);
+  return cudaMemcpy(out, g_trace_dev, 148ull * g_trace_ops * 8 * 8, cudaMemcpyDeviceToHost);
 }
 #endif
 
@@ -1167,7 +1187,7 @@ cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
   p.status = plan->status_dev;
 #ifdef KQ_PLAN_TRACE
   static unsigned long long* trace_dev = nullptr;
-  if (!trace_dev) cudaMalloc(reinterpret_cast<void**>(&trace_dev), 148ull * 256 * 4 * 8);
+  if (!trace_dev) cudaMalloc(reinterpret_cast<void**>(&trace_dev), 148ull * 256 * 8 * 8);
   p.trace = trace_dev;
   g_trace_dev = trace_dev;
   g_trace_ops = p.op_count;
@@ -1271,7 +1291,7 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
   p.error_flag = env.error_flag;
   p.status = reinterpret_cast<int*>(base + kStaticStatusOff);
 #ifdef KQ_PLAN_TRACE
-  if (!g_trace_dev) cudaMalloc(reinterpret_cast<void**>(&g_trace_dev), 148ull * 256 * 4 * 8);
+  if (!g_trace_dev) cudaMalloc(reinterpret_cast<void**>(&g_trace_dev), 148ull * 256 * 8 * 8);
   p.trace = g_trace_dev;
 #endif
   void* args[] = {&p};
