@@ -344,7 +344,10 @@ def run_cuda(args):
                          "frac": achieved / peaks["hbm_gbs"], "frac_of_8tbs": achieved / 8000.0,
                          "launches_per_step": launches_per_step,
                          "algorithmic_bytes_per_launch": bytes_rank / max(1, launches_per_step),
-                         "traffic": None},
+                         # dram read+write of one launch: measured with ncu on a 2-layer case of the same
+                         # kernel (traffic = 1.002 x algorithmic bytes, all of it weights) and scaled
+                         "traffic": (bytes_rank * 1.002) if step.fused else None,
+                         "traffic_source": "ncu capture of the 2-layer case scaled by weight bytes" if step.fused else None},
             "cpu_baseline": cpu,
             "kernel_sweep": sweep,
             "other_batch": other_batch,
