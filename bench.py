@@ -164,7 +164,7 @@ def kernel_sweep(gpu):
     from tests import cases
     out = {}
 
-    def gemv(storage, k, n, m, dtype):
+    def gemv(storage, k, n, m, dtype, a8=False):
         if storage == "i4":
             data, scale = cases.synth_i4(n, k, seed=1)
         else:
@@ -175,9 +175,15 @@ def kernel_sweep(gpu):
         x = torch.randn(m, k, device="cuda").to(dtype)
         bias = torch.zeros(n, device="cuda")
         y = torch.empty(m, n, device="cuda")
+        if a8:  # integer-dot form: int8 activations (quantised once, outside the timed launches)
+            xq, xs = gpu.quantize_rows(x.float().contiguous())
+            gpu.linear_a8(xq, xs, ws[0], bias, out=y)  # grows the context's scratch before the recording
         gpu.graph_begin()
         for w in ws:
-            gpu.linear(x, w, bias, out=y)
+            if a8:
+                gpu.linear_a8(xq, xs, w, bias, out=y)
+            else:
+                gpu.linear(x, w, bias, out=y)
         g = gpu.graph_end()
         for _ in range(3):
             gpu.graph_launch(g)
@@ -190,7 +196,7 @@ def kernel_sweep(gpu):
         gpu.graph_free(g)
         for w in ws:
             w.free()
-        alg = wbytes + m * k * x.element_size() + m * n * 4
+        alg = wbytes + m * k * (1 if a8 else x.element_size()) + m * n * 4
         us = best * 1e3 / copies
         return {"us": round(us, 3), "GB/s": round(alg / us / 1e3, 1), "frac_of_8TB/s": round(alg / us / 1e3 / 8000, 3)}
 
@@ -199,6 +205,9 @@ def kernel_sweep(gpu):
     out["gemv_i8_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i8", 1536, 151936, 1, torch.float32)
     out["gemv_i4_m8_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 8, torch.float16)
     out["gemv_i4_m1_4096x128256_f32 (config 4 lm head)"] = gemv("i4", 4096, 128256, 1, torch.float32)
+    out["w8a8_m1_1536x151936 (integer dot, config 1 lm head)"] = gemv("i8", 1536, 151936, 1, torch.float32, a8=True)
+    out["w4a8_m1_4096x128256 (integer dot, config 4 lm head)"] = gemv("i4", 4096, 128256, 1, torch.float32, a8=True)
+    out["w4a8_m8_4096x11008 (integer dot, config 2 shape)"] = gemv("i4", 4096, 11008, 8, torch.float32, a8=True)
 
     def gemm(m, k, n):
         data, scale = cases.synth_i4(n, k, seed=1)

@@ -198,6 +198,24 @@ KQ_API int kq_linear_host(kq_ctx* ctx, kq_weight w, const void* x_host, int x_dt
 KQ_API int kq_linear_static(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
                             uint64_t out_dptr, uint32_t m);
 
+/* ---- integer-dot form (w8a8 / w4a8) ------------------------------------------------
+ * kq_quantize_rows replaces the reference's activation quantiser
+ * (packages/runtime/src/kernels/quantize-rows.ts:83-155): per row of x[rows, dim] (f32),
+ *   scale[row] = max(max|x| * (1/127), f32 tiny)   (NaN in the row -> NaN scale)
+ *   q[row, i]  = clamp(round_ties_even(x / scale), -127, 127) as int8, correctly rounded division.
+ * kq_linear_a8 replaces the integer GEMM variants (packages/runtime/src/kernels/linear-i8a8.ts:21-72,
+ * stated on the CPU by packages/runtime/src/reference/i8a8.ts:159-229), chosen by the
+ * weight's storage:
+ *   int8: out = fma(f32(sum_k xq * wq), fround(xs[row] * ws[col]), bias[col]),  k <= 131072
+ *   int4: accf = fma(f32(sum_{k in group} xq * wq), ws[col, group], accf), groups ascending;
+ *         out = fma(accf, xs[row], bias[col])
+ * Integer sums are exact, so results are bit-identical to the reference's CPU statement
+ * (its own tests compare with atol = 0).  xq is int8 [m, k] row-major, xs f32 [m]. */
+KQ_API int kq_quantize_rows(kq_ctx* ctx, uint64_t x_f32_dptr, uint32_t rows, uint32_t dim, uint64_t q_i8_dptr,
+                            uint64_t scale_f32_dptr);
+KQ_API int kq_linear_a8(kq_ctx* ctx, kq_weight w, uint64_t xq_i8_dptr, uint64_t xs_f32_dptr, uint64_t bias_dptr,
+                        uint64_t out_dptr, uint32_t m);
+
 /* ---- replayable plans -----------------------------------------------------------
  * Records every kq_* launch between begin and end into a CUDA graph that
  * kq_graph_launch replays.  Replaces the reference's baked plan replay

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libkq.so")
 
-SOURCES = ["kq_api.cu", "kq_generic.cu", "kq_qgemv_i4.cu", "kq_plan.cu", "kq_qgemm_i4.cu", "kq_qgemv_i8.cu", "kq_comm.cu"]
+SOURCES = ["kq_api.cu", "kq_generic.cu", "kq_qgemv_i4.cu", "kq_plan.cu", "kq_qgemm_i4.cu", "kq_qgemv_i8.cu", "kq_comm.cu", "kq_idot.cu"]
 HEADERS = ["kq_common.cuh", "kq_gemv_core.cuh", "kq_internal.h", os.path.join("..", "..", "include", "kq.h")]
 
 NVCC_FLAGS = [

@@ -42,6 +42,8 @@ struct kq_ctx {
   void* host_dev_x = nullptr;
   void* host_dev_out = nullptr;
   uint64_t host_x_bytes = 0, host_out_bytes = 0;
+  int* idot_sums = nullptr;  // integer sums of the quantised activations (kq_linear_a8)
+  uint64_t idot_sums_bytes = 0;
 };
 
 namespace {
@@ -398,6 +400,7 @@ void kq_destroy(kq_ctx* ctx) {
   if (ctx->host_x) cudaFreeHost(ctx->host_x);
   if (ctx->host_dev_x) cudaFree(ctx->host_dev_x);
   if (ctx->host_dev_out) cudaFree(ctx->host_dev_out);
+  if (ctx->idot_sums) cudaFree(ctx->idot_sums);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -728,6 +731,65 @@ int kq_linear_static(kq_ctx* ctx, kq_weight h, uint64_t x_dptr, int x_dtype, uin
     *reinterpret_cast<volatile int*>(ctx->error_flag_host) = 0;
     return fail(ctx, KQ_ERR_RANGE, "kq_linear_static: an activation had a finite magnitude above 65504");
   }
+  return KQ_OK;
+}
+
+int kq_quantize_rows(kq_ctx* ctx, uint64_t x_dptr, uint32_t rows, uint32_t dim, uint64_t q_dptr, uint64_t scale_dptr) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_quantize_rows cannot be recorded into a fused plan");
+  if (rows != 0 && dim != 0 && (!x_dptr || !q_dptr || !scale_dptr))
+    return fail(ctx, KQ_ERR_BAD_ARG, "kq_quantize_rows: null device pointer");
+  if (rows == 0 || dim == 0) return KQ_OK;
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = kq::launch_quantize_rows(ctx->stream, reinterpret_cast<const float*>(x_dptr), rows, dim,
+                                           reinterpret_cast<int8_t*>(q_dptr), reinterpret_cast<float*>(scale_dptr),
+                                           nullptr, nullptr);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "quantize_rows launch");
+  ctx->launches += 1;
+  return KQ_OK;
+}
+
+int kq_linear_a8(kq_ctx* ctx, kq_weight h, uint64_t xq_dptr, uint64_t xs_dptr, uint64_t bias_dptr, uint64_t out_dptr,
+                 uint32_t m) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_linear_a8 cannot be recorded into a fused plan");
+  const Weight* w = find_weight(ctx, h);
+  if (!w) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_a8: unknown weight");
+  if (m != 0 && w->n != 0 && (!xq_dptr || !xs_dptr || !bias_dptr || !out_dptr))
+    return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_a8: null device pointer (bias is required: the op's arity is 3)");
+  // The int8 variant reduces the whole k range in int32: |sum| <= k * 127^2
+  // (LINEAR_I8A8_MAX_K, packages/runtime/src/kernels/linear-i8a8.ts:121).  The int4 variant
+  // flushes per group and has no such gate.
+  if (w->storage == KQ_STORAGE_I8 && w->k > 131072u)
+    return fail(ctx, KQ_ERR_UNSUPPORTED, "kq_linear_a8: k=%u exceeds the int32 reduction gate 131072", w->k);
+  if (m == 0 || w->n == 0) return KQ_OK;
+  DeviceGuard guard(ctx->device);
+  const bool tiled = w->layout == kq::kLayoutTiledI4 || w->layout == kq::kLayoutTiledI8;
+  int* row_sum = nullptr;
+  int* group_sum = nullptr;
+  int launched = 0;
+  if (tiled) {
+    const uint64_t need = (static_cast<uint64_t>(m) * (w->k / 32) + m) * sizeof(int);
+    if (need > ctx->idot_sums_bytes) {
+      if (ctx->capturing) return fail(ctx, KQ_ERR_STATE, "kq_linear_a8: scratch must grow; call once outside the recording first");
+      if (ctx->idot_sums) cudaFree(ctx->idot_sums);
+      ctx->idot_sums = nullptr;
+      ctx->idot_sums_bytes = 0;
+      KQ_CUDA(ctx, cudaMalloc(reinterpret_cast<void**>(&ctx->idot_sums), need));
+      ctx->idot_sums_bytes = need;
+    }
+    row_sum = ctx->idot_sums;
+    group_sum = ctx->idot_sums + m;
+    cudaError_t e = kq::launch_xq_sums(ctx->stream, reinterpret_cast<const int8_t*>(xq_dptr), m, w->k, row_sum, group_sum);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "xq_sums launch");
+    launched += 1;
+  }
+  cudaError_t e = kq::launch_linear_idot(ctx->stream, *w, reinterpret_cast<const int8_t*>(xq_dptr),
+                                         reinterpret_cast<const float*>(xs_dptr), row_sum, group_sum,
+                                         reinterpret_cast<const float*>(bias_dptr), reinterpret_cast<float*>(out_dptr),
+                                         m, &launched);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "linear_a8 launch");
+  ctx->launches += launched;
   return KQ_OK;
 }
 

@@ -104,3 +104,14 @@ uint64_t comm_max_bytes(const Comm* c);
 cudaError_t comm_all_reduce(Comm* c, cudaStream_t stream, float* data, uint64_t count);
 int comm_take_status(Comm* c);
 }  // namespace kq
+
+// ---- integer-dot linear (kq_idot.cu) ---------------------------------------------------
+namespace kq {
+cudaError_t launch_quantize_rows(cudaStream_t stream, const float* x, uint32_t rows, uint32_t dim, int8_t* q,
+                                 float* scale, int* row_sum, int* group_sum);
+cudaError_t launch_xq_sums(cudaStream_t stream, const int8_t* q, uint32_t rows, uint32_t dim, int* row_sum,
+                           int* group_sum);
+cudaError_t launch_linear_idot(cudaStream_t stream, const Weight& w, const int8_t* xq, const float* xs,
+                               const int* row_sum, const int* group_sum, const float* bias, float* out,
+                               uint32_t m, int* launches);
+}  // namespace kq

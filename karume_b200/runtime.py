@@ -148,6 +148,37 @@ class Gpu:
         self._check(L.kq_weight_shape(self._ctx, handle.value, ctypes.byref(sn), ctypes.byref(sk)))
         return Weight(self, handle.value, storage, sn.value, sk.value, int(group_size))
 
+    # -- integer-dot form ------------------------------------------------------
+    def quantize_rows(self, x):
+        """Per-row symmetric int8 quantisation of a CUDA f32 tensor [..., dim]:
+        returns (q int8 [..., dim], scale f32 [...])."""
+        torch = _torch()
+        if x.dtype != torch.float32 or not x.is_cuda or not x.is_contiguous():
+            raise ValueError("quantize_rows takes a contiguous CUDA f32 tensor")
+        dim = x.shape[-1]
+        rows = x.numel() // dim if dim else 0
+        q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+        scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+        self._check(L.kq_quantize_rows(self._ctx, x.data_ptr(), rows, dim, q.data_ptr(), scale.data_ptr()))
+        return q, scale
+
+    def linear_a8(self, xq, xs, weight: Weight, bias, out=None):
+        """Integer-dot linear: xq int8 [..., k] and xs f32 [...] from quantize_rows against a
+        resident int8 (w8a8) or int4 (w4a8) weight.  Returns f32 [..., n]."""
+        torch = _torch()
+        if xq.dtype != torch.int8 or xq.shape[-1] != weight.k or not xq.is_contiguous():
+            raise ValueError("xq must be a contiguous int8 tensor [..., k]")
+        m = xq.numel() // weight.k if weight.k else 0
+        if xs.dtype != torch.float32 or xs.numel() != m:
+            raise ValueError("xs must hold one f32 scale per row of xq")
+        if bias is None or bias.dtype != torch.float32 or bias.numel() != weight.n:
+            raise ValueError("bias must be a CUDA f32 tensor [n] (the op's arity is 3)")
+        if out is None:
+            out = torch.empty(xq.shape[:-1] + (weight.n,), dtype=torch.float32, device=xq.device)
+        self._check(L.kq_linear_a8(self._ctx, weight.handle, xq.data_ptr(), xs.data_ptr(), bias.data_ptr(),
+                                   out.data_ptr(), m))
+        return out
+
     # -- the op ---------------------------------------------------------------
     def linear(self, x, weight: Weight, bias, out=None):
         """out[..., n] = x[..., k] @ W[n, k]^T + bias[n]; x is a CUDA tensor (f32/f16/bf16),
