@@ -198,6 +198,14 @@ KQ_API int kq_linear_host(kq_ctx* ctx, kq_weight w, const void* x_host, int x_dt
 KQ_API int kq_linear_static(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
                             uint64_t out_dptr, uint32_t m);
 
+/* ---- embedding gather ----------------------------------------------------------------
+ * out[row, :] = dequantised row index[row] of a resident weight [vocab, hidden] (the weight a
+ * tied LM head shares), f32.  Replaces the packed-weight variants of the reference's embedding
+ * kernel (packages/runtime/src/kernels/embedding.ts:70-117): same single-multiply dequant as
+ * kq_weight_dequant, and an index outside [0, vocab) writes quiet NaNs into its row instead
+ * of returning another row.  index is int32 [rows]. */
+KQ_API int kq_embedding(kq_ctx* ctx, kq_weight w, uint64_t index_i32_dptr, uint32_t rows, uint64_t out_dptr);
+
 /* ---- integer-dot form (w8a8 / w4a8) ------------------------------------------------
  * kq_quantize_rows replaces the reference's activation quantiser
  * (packages/runtime/src/kernels/quantize-rows.ts:83-155): per row of x[rows, dim] (f32),

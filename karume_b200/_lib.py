@@ -43,6 +43,7 @@ SYMBOLS = {
     "kq_weight_free": (_i32, [_vp, _u64]),
     "kq_weight_resident_bytes": (_u64, [_vp, _u64]),
     "kq_weight_shape": (_i32, [_vp, _u64, _pu32, _pu32]),
+    "kq_embedding": (_i32, [_vp, _u64, _u64, _u32, _u64]),
     "kq_quantize_rows": (_i32, [_vp, _u64, _u32, _u32, _u64, _u64]),
     "kq_linear_a8": (_i32, [_vp, _u64, _u64, _u64, _u64, _u64, _u32]),
     "kq_weight_dequant": (_i32, [_vp, _u64, _u64]),

@@ -734,6 +734,21 @@ int kq_linear_static(kq_ctx* ctx, kq_weight h, uint64_t x_dptr, int x_dtype, uin
   return KQ_OK;
 }
 
+int kq_embedding(kq_ctx* ctx, kq_weight h, uint64_t index_dptr, uint32_t rows, uint64_t out_dptr) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_embedding cannot be recorded into a fused plan");
+  const Weight* w = find_weight(ctx, h);
+  if (!w) return fail(ctx, KQ_ERR_BAD_ARG, "kq_embedding: unknown weight");
+  if (rows != 0 && w->k != 0 && (!index_dptr || !out_dptr)) return fail(ctx, KQ_ERR_BAD_ARG, "kq_embedding: null device pointer");
+  if (rows == 0 || w->k == 0) return KQ_OK;
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = kq::launch_embedding(env_of(ctx), *w, reinterpret_cast<const int*>(index_dptr), rows,
+                                       reinterpret_cast<float*>(out_dptr));
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "embedding launch");
+  ctx->launches += 1;
+  return KQ_OK;
+}
+
 int kq_quantize_rows(kq_ctx* ctx, uint64_t x_dptr, uint32_t rows, uint32_t dim, uint64_t q_dptr, uint64_t scale_dptr) {
   if (!ctx) return KQ_ERR_BAD_ARG;
   if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_quantize_rows cannot be recorded into a fused plan");

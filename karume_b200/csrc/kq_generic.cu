@@ -167,6 +167,52 @@ __global__ void dequant_tiled_i8(const uint8_t* __restrict__ tiled, const void* 
   }
 }
 
+// ---- embedding gather -----------------------------------------------------------------
+// out[row, col] = dequant(weight[index[row], col]) — the reference's embedding kernel with a
+// packed weight (packages/runtime/src/kernels/embedding.ts:70-117): same dequant rule as the
+// linear (one f32 multiply), group scale looked up per element for int4, and an index outside
+// [0, vocab) poisons its output elements with a quiet NaN instead of returning another row.
+struct EmbeddingParams {
+  const uint8_t* w;
+  const void* scale;
+  int layout, storage, scale_f16;
+  uint32_t vocab, hidden, gshift;
+  const int* index;
+  float* out;
+  uint64_t total;  // rows * hidden
+};
+
+__global__ void __launch_bounds__(256) embedding_kernel(const EmbeddingParams p) {
+  for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < p.total;
+       i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t row = static_cast<uint32_t>(i / p.hidden), col = static_cast<uint32_t>(i % p.hidden);
+    const int pick = p.index[row];
+    float v;
+    if (pick < 0 || static_cast<uint32_t>(pick) >= p.vocab) {
+      v = __int_as_float(0x7fc00000);
+    } else if (p.storage == KQ_STORAGE_I4) {
+      if (p.layout == kLayoutTiledI4) {
+        const TiledPos pos = tiled_i4_locate(static_cast<uint32_t>(pick), col, p.hidden, p.scale_f16 ? 2u : 4u);
+        const uint32_t word = *reinterpret_cast<const uint32_t*>(p.w + pos.word_offset);
+        const float s = p.scale_f16 ? load_scale<true>(p.w + pos.scale_offset, 0) : load_scale<false>(p.w + pos.scale_offset, 0);
+        v = dequant_i4((word >> (4 * pos.nibble)) & 0xFu, s);
+      } else {
+        const uint64_t flat = static_cast<uint64_t>(pick) * p.hidden + col;
+        const uint8_t byte = p.w[flat >> 1];
+        const uint32_t u = (flat & 1) ? (byte >> 4) : (byte & 0x0Fu);
+        const size_t si = static_cast<size_t>(pick) * (p.hidden >> p.gshift) + (col >> p.gshift);
+        v = dequant_i4(u, p.scale_f16 ? load_scale<true>(p.scale, si) : load_scale<false>(p.scale, si));
+      }
+    } else {
+      const int q = p.layout == kLayoutTiledI8
+                        ? static_cast<int>(p.w[tiled_i8_locate(static_cast<uint32_t>(pick), col, p.hidden)]) - 128
+                        : static_cast<int>(reinterpret_cast<const int8_t*>(p.w)[static_cast<uint64_t>(pick) * p.hidden + col]);
+      v = dequant_i8(q, p.scale_f16 ? load_scale<true>(p.scale, pick) : load_scale<false>(p.scale, pick));
+    }
+    p.out[i] = v;
+  }
+}
+
 // One thread per 32-bit word of the destination.
 __global__ void repack_i8_tiled(const uint8_t* __restrict__ payload, uint32_t n, uint32_t k,
                                 uint8_t* __restrict__ tiled) {
@@ -292,6 +338,27 @@ cudaError_t launch_dequant(const LaunchEnv& env, const Weight& w, float* out) {
     if (f16s) dequant_native_i8<true><<<grid, block, 0, env.stream>>>(static_cast<const int8_t*>(w.data), w.scale, out, w.n, w.k);
     else dequant_native_i8<false><<<grid, block, 0, env.stream>>>(static_cast<const int8_t*>(w.data), w.scale, out, w.n, w.k);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_embedding(const LaunchEnv& env, const Weight& w, const int* index, uint32_t rows, float* out) {
+  const uint64_t total = static_cast<uint64_t>(rows) * w.k;
+  if (total == 0) return cudaSuccess;
+  EmbeddingParams p = {};
+  p.w = static_cast<const uint8_t*>(w.data);
+  p.scale = w.scale;
+  p.layout = w.layout;
+  p.storage = w.storage;
+  p.scale_f16 = w.scale_dtype == KQ_F16;
+  p.vocab = w.n;
+  p.hidden = w.k;
+  p.gshift = w.storage == KQ_STORAGE_I4 ? log2_exact(w.group_size) : 0;
+  p.index = index;
+  p.out = out;
+  p.total = total;
+  const int block = 256;
+  const int grid = static_cast<int>(std::min<uint64_t>((total + block - 1) / block, static_cast<uint64_t>(env.sm_count) * 16));
+  embedding_kernel<<<grid, block, 0, env.stream>>>(p);
   return cudaGetLastError();
 }
 

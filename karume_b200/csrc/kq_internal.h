@@ -48,6 +48,7 @@ struct LaunchEnv {
 cudaError_t launch_linear_generic(const LaunchEnv& env, const Weight& w, const void* x, int x_dtype,
                                   const float* bias, float* out, uint32_t m);
 cudaError_t launch_dequant(const LaunchEnv& env, const Weight& w, float* out);
+cudaError_t launch_embedding(const LaunchEnv& env, const Weight& w, const int* index, uint32_t rows, float* out);
 
 // Tiled int4 layout.
 bool tiled_i4_eligible(int storage, uint32_t n, uint32_t k, uint32_t group_size);

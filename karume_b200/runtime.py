@@ -148,6 +148,16 @@ class Gpu:
         self._check(L.kq_weight_shape(self._ctx, handle.value, ctypes.byref(sn), ctypes.byref(sk)))
         return Weight(self, handle.value, storage, sn.value, sk.value, int(group_size))
 
+    def embedding(self, index, weight: Weight, out=None):
+        """Rows index[...] (CUDA int32) of a resident weight [vocab, hidden], dequantised to f32."""
+        torch = _torch()
+        if index.dtype != torch.int32 or not index.is_cuda or not index.is_contiguous():
+            raise ValueError("index must be a contiguous CUDA int32 tensor")
+        if out is None:
+            out = torch.empty(tuple(index.shape) + (weight.k,), dtype=torch.float32, device=index.device)
+        self._check(L.kq_embedding(self._ctx, weight.handle, index.data_ptr(), index.numel(), out.data_ptr()))
+        return out
+
     # -- integer-dot form ------------------------------------------------------
     def quantize_rows(self, x):
         """Per-row symmetric int8 quantisation of a CUDA f32 tensor [..., dim]:
