@@ -62,10 +62,13 @@ __device__ __forceinline__ void load_x8(const XT* p, float (&v)[8]) {
 // Four consecutive threads share one (group, row): each converts one octet.
 // kBatch: octets a thread loads before it converts any (one memory round trip per batch, at
 // the price of 8 registers per octet held).
+//   lo_offset != 0 selects the split layout: activation row r occupies column r, its hi part at
+//          byte offset 0 of the group and its lo part lo_offset bytes further on.
 template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2 = false, int kBatch = 1>
 __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, uint32_t k,
                                         uint32_t group0, uint32_t groups, uint8_t* xs,
-                                        uint32_t xs_stride, float* corr, int* error_flag) {
+                                        uint32_t xs_stride, float* corr, int* error_flag,
+                                        uint32_t lo_offset = 0) {
   const uint32_t items = groups * m * 4;
   const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles below
   bool out_of_range = false;
@@ -118,10 +121,10 @@ __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, ui
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
       if (valid) {
-        const uint32_t col = kHasLo ? 2 * row : row;
+        const uint32_t col = (kHasLo && lo_offset == 0) ? 2 * row : row;
         const uint32_t off = lg * xs_stride + col * 64 + q * 16;
         *reinterpret_cast<uint4*>(xs + off) = hi4;
-        if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + 64) = lo4;
+        if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + (lo_offset == 0 ? 64u : lo_offset)) = lo4;
         if (q == 0) corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
       }
     }
@@ -142,6 +145,16 @@ __device__ __forceinline__ void lds_f32_if(float& v, uint32_t addr, bool pred) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p ld.shared.f32 %0, [%1];\n\t}"
                : "+f"(v)
                : "r"(addr), "r"(static_cast<uint32_t>(pred)));
+}
+
+// D = A.B + C with C read from registers that are not overwritten.
+__device__ __forceinline__ void mma_f16_init(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                             float c0, float c1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%11,%10,%11};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
 }
 
 // D = A.B with a zero accumulator.

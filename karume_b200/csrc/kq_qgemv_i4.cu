@@ -58,6 +58,18 @@ constexpr int kWarps = 4;                // warps per CTA
 #ifndef KQ_TUNE_WANT
 #define KQ_TUNE_WANT 4
 #endif
+#ifndef KQ_TUNE_WIDE
+#define KQ_TUNE_WIDE 1
+#endif
+#ifndef KQ_TUNE_WIDE_SLAB
+#define KQ_TUNE_WIDE_SLAB 16384u
+#endif
+#ifndef KQ_TUNE_PRESTAGE
+#define KQ_TUNE_PRESTAGE 1
+#endif
+#ifndef KQ_TUNE_RB8
+#define KQ_TUNE_RB8 1
+#endif
 #ifndef KQ_TUNE_RB16
 #define KQ_TUNE_RB16 2
 #endif
@@ -86,6 +98,10 @@ struct GemvParams {
   uint32_t splits;
   uint32_t slab_chunks;  // chunks of x staged in shared memory at a time
   int* error_flag;
+  // Activations already converted to the staged layout by stage_x_global_kernel (wide kernel
+  // only; null: every CTA converts its own slab).
+  const uint8_t* staged_xs;
+  const float* staged_corr;
 };
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
@@ -718,12 +734,333 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
+// Converts the whole activation block to the staged layout ONCE per launch, into global
+// scratch.  With many activation rows the conversion is as much work as a CTA's share of the
+// matmul, and every CTA would repeat it for its k range; this way a CTA only copies bytes.
+template <typename XT, int kTiles>
+__global__ void __launch_bounds__(256)
+stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t* xs, float* corr, int* error_flag) {
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  constexpr uint32_t kLoOffset = kTiles * 512u;
+  constexpr uint32_t kXsStride = kLoOffset * (kHasLo ? 2u : 1u);
+  constexpr uint32_t kGroupsPerCta = 8;
+  const uint32_t groups = k / 32;
+  const uint32_t group0 = blockIdx.x * kGroupsPerCta;
+  if (group0 >= groups) return;
+  const uint32_t ng = min(kGroupsPerCta, groups - group0);
+  stage_x<XT, kHasLo, kTiles * 8>(x, m, k, group0, ng, xs + static_cast<size_t>(group0) * kXsStride, kXsStride,
+                                  corr + static_cast<size_t>(group0) * (kTiles * 8), error_flag,
+                                  kHasLo ? kLoOffset : 0u);
+}
+
+// ---- wide variant: more than 4 MMA columns (3 to 16 activation rows) -------------------
+// Column c of tile j is activation row 8 j + c for every input type.  The hi and lo parts of
+// an f32 / bf16 activation are two B operands that accumulate into the SAME C tile (two more
+// MMAs per group instead of twice the columns), and the "-8 sum x" term enters as the C
+// operand of the group's first MMA, so all that is left per group and C value is one FFMA
+// with the group scale.  Two row blocks per warp share every shared-memory load.
+template <typename XT, bool kScaleF16, int kTiles, int kRB, int kD>
+__global__ void __launch_bounds__(kWarps * 32)
+qgemv_i4_wide_kernel(const GemvParams p) {
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
+  constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;  // chunk bytes
+  constexpr int kCols = kTiles * 8;
+  constexpr uint32_t kLoOffset = kTiles * 512u;
+  constexpr uint32_t kXsStride = kLoOffset * (kHasLo ? 2u : 1u);
+  constexpr uint32_t kTileRowsCta = kWarps * kRB * 16;
+
+  extern __shared__ __align__(16) uint8_t smem[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+
+  if (!KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
+
+  uint32_t wi = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxMulti; ++i)
+    if (i < static_cast<int>(p.count) && blockIdx.x >= p.tile_begin[i]) wi = i;
+  const uint8_t* w_base = p.w[0];
+  const float* bias = p.bias[0];
+  float* out = p.out[0];
+  uint32_t n = p.n[0], tile0 = p.tile_begin[0];
+#pragma unroll
+  for (int i = 1; i < kMaxMulti; ++i)
+    if (wi == static_cast<uint32_t>(i)) {
+      w_base = p.w[i]; bias = p.bias[i]; out = p.out[i]; n = p.n[i]; tile0 = p.tile_begin[i];
+    }
+  const uint32_t tile = blockIdx.x - tile0;
+  const uint32_t row_block0 = (tile * kWarps + warp) * kRB;
+
+  const uint32_t chunks_per_row = p.k / kChunkK;
+  const uint32_t split = blockIdx.y;
+  const uint32_t cbeg = min(split * p.chunks_per_split, chunks_per_row);
+  const uint32_t cend = min(cbeg + p.chunks_per_split, chunks_per_row);
+  const uint32_t nch = cend - cbeg;
+
+  uint8_t* xs = smem;
+  float* corr = reinterpret_cast<float*>(smem + 2 * p.slab_chunks * kXsStride);
+
+  bool active[kRB];
+  const uint8_t* next[kRB];
+#pragma unroll
+  for (int r = 0; r < kRB; ++r) {
+    active[r] = (row_block0 + r) * 16u < n;
+    next[r] = w_base + (static_cast<size_t>(row_block0 + r) * chunks_per_row + cbeg) * kCB + lane * 16;
+  }
+  const uint32_t scale_off = kChunkWeightBytes - lane * 16 + g * (4 * kScaleBytes);
+
+  ChunkRegs<kScaleF16> ring[kD][kRB];
+  auto fetch = [&](ChunkRegs<kScaleF16>& dst, const uint8_t* src) {
+    dst.w = ldg_stream_v4(src);
+    if constexpr (kScaleF16) dst.s = ldg_stream_v2(src + scale_off);
+    else dst.s = ldg_stream_v4(src + scale_off);
+  };
+#pragma unroll
+  for (int d = 0; d < kD; ++d)
+#pragma unroll
+    for (int r = 0; r < kRB; ++r) {
+      ring[d][r].w = make_uint4(0, 0, 0, 0);
+      if constexpr (kScaleF16) ring[d][r].s = make_uint2(0, 0);
+      else ring[d][r].s = make_uint4(0, 0, 0, 0);
+      if (active[r] && static_cast<uint32_t>(d) < nch) fetch(ring[d][r], next[r] + d * kCB);
+    }
+#pragma unroll
+  for (int r = 0; r < kRB; ++r) next[r] += kD * kCB;
+
+  pdl_wait_prior_grid();
+
+  float acc[kRB][kTiles][4];
+#pragma unroll
+  for (int r = 0; r < kRB; ++r)
+#pragma unroll
+    for (int i = 0; i < kTiles; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[r][i][j] = 0.0f;
+
+  const XT* x = static_cast<const XT*>(p.x);
+  constexpr uint32_t kMask0 = 0x000F000Fu, kMask1 = 0x00F000F0u;
+
+  uint4 bhi[kTiles], blo[kTiles];
+  float cterm[kTiles][2];
+  bool load_b[kTiles], load_c[kTiles][2];
+#pragma unroll
+  for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+    bhi[tile_m] = make_uint4(0, 0, 0, 0);
+    blo[tile_m] = make_uint4(0, 0, 0, 0);
+    load_b[tile_m] = tile_m * 8 + g < p.m;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      cterm[tile_m][j] = 0.0f;
+      load_c[tile_m][j] = tile_m * 8 + 2 * t + j < p.m;
+    }
+  }
+  const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
+  const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) + 2 * t * 4;
+
+  auto process = [&](const int d, uint32_t xs_addr, uint32_t corr_addr, bool refill) {
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+#pragma unroll
+      for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+        lds_v4_if(bhi[tile_m], xs_addr + jj * kXsStride + tile_m * 512, load_b[tile_m]);
+        if constexpr (kHasLo) lds_v4_if(blo[tile_m], xs_addr + jj * kXsStride + kLoOffset + tile_m * 512, load_b[tile_m]);
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          lds_f32_if(cterm[tile_m][j], corr_addr + (jj * kCols + tile_m * 8 + j) * 4, load_c[tile_m][j]);
+      }
+#pragma unroll
+      for (int r = 0; r < kRB; ++r) {
+        const uint32_t wa = jj ? ring[d][r].w.z : ring[d][r].w.x;  // row g
+        const uint32_t wb = jj ? ring[d][r].w.w : ring[d][r].w.y;  // row g + 8
+        const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+        const uint32_t a0[4] = {wa & kMask0, wb & kMask0, wa & kMask1, wb & kMask1};
+        const uint32_t a1[4] = {wa8 & kMask0, wb8 & kMask0, wa8 & kMask1, wb8 & kMask1};
+        float2 s;  // .x = row g, .y = row g + 8
+        if constexpr (kScaleF16) {
+          s = __half22float2(*reinterpret_cast<const __half2*>(jj ? &ring[d][r].s.y : &ring[d][r].s.x));
+        } else {
+          s = jj ? make_float2(__uint_as_float(ring[d][r].s.z), __uint_as_float(ring[d][r].s.w))
+                 : make_float2(__uint_as_float(ring[d][r].s.x), __uint_as_float(ring[d][r].s.y));
+        }
+#pragma unroll
+        for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+          float cf[4];
+          mma_f16_init(cf, a0, bhi[tile_m].x, bhi[tile_m].y, cterm[tile_m][0], cterm[tile_m][1]);
+          mma_f16(cf, a1, bhi[tile_m].z, bhi[tile_m].w);
+          if constexpr (kHasLo) {
+            mma_f16(cf, a0, blo[tile_m].x, blo[tile_m].y);
+            mma_f16(cf, a1, blo[tile_m].z, blo[tile_m].w);
+          }
+          acc[r][tile_m][0] = fmaf(s.x, cf[0], acc[r][tile_m][0]);
+          acc[r][tile_m][1] = fmaf(s.x, cf[1], acc[r][tile_m][1]);
+          acc[r][tile_m][2] = fmaf(s.y, cf[2], acc[r][tile_m][2]);
+          acc[r][tile_m][3] = fmaf(s.y, cf[3], acc[r][tile_m][3]);
+        }
+      }
+    }
+    if (refill) {
+#pragma unroll
+      for (int r = 0; r < kRB; ++r)
+        if (active[r]) fetch(ring[d][r], next[r] + d * kCB);
+    }
+  };
+
+  for (uint32_t done = 0; done < nch;) {
+    const uint32_t slab_n = min(p.slab_chunks, nch - done);
+    if (done != 0) __syncthreads();
+    if (p.staged_xs != nullptr) {
+      const uint32_t first_group = 2 * (cbeg + done);
+      const uint4* src = reinterpret_cast<const uint4*>(p.staged_xs + static_cast<size_t>(first_group) * kXsStride);
+      uint4* dst = reinterpret_cast<uint4*>(xs);
+      const uint32_t n16 = 2 * slab_n * (kXsStride / 16);
+      for (uint32_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldg(src + i);
+      const float4* csrc = reinterpret_cast<const float4*>(p.staged_corr + static_cast<size_t>(first_group) * kCols);
+      float4* cdst = reinterpret_cast<float4*>(corr);
+      const uint32_t c16 = 2 * slab_n * (kCols / 4);
+      for (uint32_t i = threadIdx.x; i < c16; i += blockDim.x) cdst[i] = __ldg(csrc + i);
+    } else {
+      stage_x<XT, kHasLo, kCols>(x, p.m, p.k, 2 * (cbeg + done), 2 * slab_n, xs, kXsStride, corr, p.error_flag,
+                                 kHasLo ? kLoOffset : 0u);
+    }
+    __syncthreads();
+    uint32_t xs_addr = xs_lane, corr_addr = corr_lane;
+    uint32_t i = 0;
+    for (; i + kD <= slab_n; i += kD) {
+#pragma unroll
+      for (int d = 0; d < kD; ++d) {
+        process(d, xs_addr, corr_addr, done + i + d + kD < nch);
+        xs_addr += 2 * kXsStride;
+        corr_addr += 2 * kCols * 4;
+      }
+#pragma unroll
+      for (int r = 0; r < kRB; ++r) next[r] += kD * kCB;
+    }
+#pragma unroll
+    for (int d = 0; d < kD - 1; ++d) {
+      if (i + d < slab_n) {
+        process(d, xs_addr, corr_addr, false);
+        xs_addr += 2 * kXsStride;
+        corr_addr += 2 * kCols * 4;
+      }
+    }
+    done += slab_n;
+  }
+
+  if (KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
+
+  // lane owns rows g, g+8 of each block and activation rows 8 tile + 2t, 2t+1
+  float* red = reinterpret_cast<float*>(smem);
+  if (p.splits > 1) __syncthreads();
+#pragma unroll
+  for (int r = 0; r < kRB; ++r) {
+    if (!active[r]) continue;
+    const uint32_t row_a = (row_block0 + r) * 16u + g;
+    const uint32_t tr_a = (warp * kRB + r) * 16u + g;
+    float bias_a = 0.0f, bias_b = 0.0f;
+    if (p.splits == 1) {
+      bias_a = bias[row_a];
+      bias_b = bias[row_a + 8];
+    }
+#pragma unroll
+    for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t mm = tile_m * 8 + 2 * t + j;
+        if (mm >= p.m) continue;
+        const float va = acc[r][tile_m][j], vb = acc[r][tile_m][2 + j];
+        if (p.splits == 1) {
+          out[static_cast<size_t>(mm) * n + row_a] = fmaf(va, kUnscale, bias_a);
+          out[static_cast<size_t>(mm) * n + row_a + 8] = fmaf(vb, kUnscale, bias_b);
+        } else {
+          red[mm * kTileRowsCta + tr_a] = va;
+          red[mm * kTileRowsCta + tr_a + 8] = vb;
+        }
+      }
+    }
+  }
+  if (p.splits == 1) return;
+  cluster_reduce_store(p, red, kTileRowsCta, tile, split, n, out, bias);
+}
+
+template <typename XT, bool kScaleF16, int kTiles, int kRB, int kD>
+cudaError_t launch_typed_wide(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets,
+                              int* extra_launches) {
+  auto kernel = qgemv_i4_wide_kernel<XT, kScaleF16, kTiles, kRB, kD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  constexpr bool kHasLo = !std::is_same<XT, __half>::value;
+  constexpr uint32_t kTileRowsCta = kWarps * kRB * 16;
+  uint32_t tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    p.tile_begin[i] = tiles;
+    tiles += (targets[i].w->n + kTileRowsCta - 1) / kTileRowsCta;
+  }
+  for (int i = count; i <= kMaxMulti; ++i) p.tile_begin[i] = tiles;
+  const uint32_t chunks_per_row = p.k / kChunkK;
+  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * KQ_TUNE_WANT;
+  uint32_t splits = 1;
+  while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas && splits * 2 <= chunks_per_row)
+    splits *= 2;
+  p.splits = splits;
+  p.chunks_per_split = (chunks_per_row + splits - 1) / splits;
+  const uint32_t per_chunk = 2 * (kTiles * 512u * (kHasLo ? 2u : 1u) + kTiles * 8u * 4u);
+  const uint32_t slab_cap = std::max<uint32_t>(kD, (KQ_TUNE_WIDE_SLAB * kTiles / per_chunk) / kD * kD);
+  p.slab_chunks = std::max<uint32_t>(1u, std::min(p.chunks_per_split, slab_cap));
+  const size_t slab_bytes = static_cast<size_t>(p.slab_chunks) * per_chunk;
+  const size_t red_bytes = splits > 1 ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
+
+  // Convert the activations once, into the context's scratch, when it is large enough.
+  const uint32_t groups = p.k / 32;
+  const size_t xs_total = static_cast<size_t>(groups) * (kTiles * 512u * (kHasLo ? 2u : 1u));
+  const size_t corr_total = static_cast<size_t>(groups) * kTiles * 8u * sizeof(float);
+  p.staged_xs = nullptr;
+  p.staged_corr = nullptr;
+  if (KQ_TUNE_PRESTAGE && env.workspace != nullptr && xs_total + corr_total <= env.workspace_bytes) {
+    uint8_t* ws = static_cast<uint8_t*>(env.workspace);
+    stage_x_global_kernel<XT, kTiles><<<(groups + 7) / 8, 256, 0, env.stream>>>(
+        static_cast<const XT*>(p.x), p.m, p.k, ws, reinterpret_cast<float*>(ws + xs_total), p.error_flag);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    p.staged_xs = ws;
+    p.staged_corr = reinterpret_cast<const float*>(ws + xs_total);
+    if (extra_launches) *extra_launches += 1;
+  }
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles, splits, 1);
+  cfg.blockDim = dim3(kWarps * 32, 1, 1);
+  cfg.dynamicSmemBytes = std::max(slab_bytes, red_bytes);
+  cfg.stream = env.stream;
+  cudaLaunchAttribute attr[2];
+  unsigned int na = 0;
+  if (env.overlap) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (splits > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = splits;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // Columns of the MMA tile an activation row needs: 1 for binary16 input, 2 (hi, lo)
 // for f32 / bf16 input.  One row block per warp while a single MMA tile holds every
 // column; two (sharing the B fragments) beyond that, where shared-memory bandwidth
 // would otherwise bound the kernel.
 template <typename XT>
-cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* t, bool f16s) {
+cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* t, bool f16s, int* extra) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   const uint32_t cols = kHasLo ? 2 * p.m : p.m;
   // Few columns: pack several scale groups into one MMA tile (four groups need an even
@@ -732,8 +1069,30 @@ cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const Linea
     return f16s ? launch_typed_gp<XT, true, 4>(env, p, count, t) : launch_typed_gp<XT, false, 4>(env, p, count, t);
   if (KQ_TUNE_GP && cols <= 4)
     return f16s ? launch_typed_gp<XT, true, 2>(env, p, count, t) : launch_typed_gp<XT, false, 2>(env, p, count, t);
+  if (KQ_TUNE_WIDE && !(kHasLo && p.m <= 4)) {
+    // Two row blocks per warp (sharing the activation loads) pay off when a row block costs
+    // many MMAs (hi + lo parts, or two column tiles) and the matrix has rows to spare;
+    // otherwise one row block per warp and a deeper ring keep more CTAs in flight.  A pure
+    // function of the shape.
+    uint32_t row_blocks = 0;
+    for (int i = 0; i < count; ++i) row_blocks += t[i].w->n / 16;
+    const bool heavy = kHasLo || p.m > 8;
+    const bool pair = heavy && row_blocks >= 1024;
+    if (p.m <= 8) {
+      if (pair)
+        return f16s ? launch_typed_wide<XT, true, 1, 2, 2>(env, p, count, t, extra)
+                    : launch_typed_wide<XT, false, 1, 2, 2>(env, p, count, t, extra);
+      return f16s ? launch_typed_wide<XT, true, 1, 1, 4>(env, p, count, t, extra)
+                  : launch_typed_wide<XT, false, 1, 1, 4>(env, p, count, t, extra);
+    }
+    if (pair)
+      return f16s ? launch_typed_wide<XT, true, 2, 2, 2>(env, p, count, t, extra)
+                  : launch_typed_wide<XT, false, 2, 2, 2>(env, p, count, t, extra);
+    return f16s ? launch_typed_wide<XT, true, 2, 1, 4>(env, p, count, t, extra)
+                : launch_typed_wide<XT, false, 2, 1, 4>(env, p, count, t, extra);
+  }
   if (cols <= 8)
-    return f16s ? launch_typed<XT, true, 8, 1>(env, p, count, t) : launch_typed<XT, false, 8, 1>(env, p, count, t);
+    return f16s ? launch_typed<XT, true, 8, KQ_TUNE_RB8>(env, p, count, t) : launch_typed<XT, false, 8, KQ_TUNE_RB8>(env, p, count, t);
   if (cols <= 16)
     return f16s ? launch_typed<XT, true, 16, KQ_TUNE_RB16>(env, p, count, t) : launch_typed<XT, false, 16, KQ_TUNE_RB16>(env, p, count, t);
   if constexpr (kHasLo) {
@@ -771,9 +1130,9 @@ cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget*
   const bool f16s = scale_dtype == KQ_F16;
   cudaError_t e;
   switch (x_dtype) {
-    case KQ_F32: e = launch_x<float>(env, p, count, targets, f16s); break;
-    case KQ_F16: e = launch_x<__half>(env, p, count, targets, f16s); break;
-    case KQ_BF16: e = launch_x<__nv_bfloat16>(env, p, count, targets, f16s); break;
+    case KQ_F32: e = launch_x<float>(env, p, count, targets, f16s, launches); break;
+    case KQ_F16: e = launch_x<__half>(env, p, count, targets, f16s, launches); break;
+    case KQ_BF16: e = launch_x<__nv_bfloat16>(env, p, count, targets, f16s, launches); break;
     default: return cudaErrorInvalidValue;
   }
   if (e == cudaSuccess && launches) *launches += 1;
