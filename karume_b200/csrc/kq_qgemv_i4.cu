@@ -61,6 +61,9 @@ constexpr int kWarps = 4;                // warps per CTA
 #ifndef KQ_TUNE_WIDE
 #define KQ_TUNE_WIDE 1
 #endif
+#ifndef KQ_TUNE_GP_DEEP
+#define KQ_TUNE_GP_DEEP 1
+#endif
 #ifndef KQ_TUNE_WIDE_SLAB
 #define KQ_TUNE_WIDE_SLAB 16384u
 #endif
@@ -411,7 +414,7 @@ struct UnitScale {
   typename std::conditional<kScaleF16, uint32_t, uint2>::type v;  // rows g, g+8 of the lane's own group
 };
 
-template <typename XT, bool kScaleF16, int kG>
+template <typename XT, bool kScaleF16, int kG, int kD>
 __global__ void __launch_bounds__(kWarps * 32)
 qgemv_i4_gp_kernel(const GemvParams p) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
@@ -419,14 +422,14 @@ qgemv_i4_gp_kernel(const GemvParams p) {
   constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;  // chunk bytes
   constexpr int kCpg = 8 / kG;                 // MMA columns per group
   constexpr int kCU = kG / 2;                  // chunks per unit
-  constexpr int kUnits = kDepth / kCU;         // ring entries
+  constexpr int kUnits = kD / kCU;         // ring entries
   constexpr int kCorrStride = kHasLo ? kCpg / 2 : kCpg;  // activation rows a group's columns hold
   constexpr int kAcc = kHasLo ? 2 : 4;
   constexpr int kCorr = kHasLo ? 1 : 2;
   constexpr uint32_t kTileRowsCta = kWarps * 16;
   constexpr uint32_t kXsStride = kCpg * 64;    // staged bytes per group
   static_assert(kG == 2 || kG == 4, "units of two or four groups");
-  static_assert(kDepth % kCU == 0, "the ring holds whole units");
+  static_assert(kD % kCU == 0, "the ring holds whole units");
 
   extern __shared__ __align__(16) uint8_t smem[];
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -488,7 +491,7 @@ qgemv_i4_gp_kernel(const GemvParams p) {
     else ring_s[u].v = make_uint2(0, 0);
     if (active && static_cast<uint32_t>(u * kCU) < nch) fetch(u, next + u * (kCU * kCB));
   }
-  next += kDepth * kCB;
+  next += kD * kCB;
 
   pdl_wait_prior_grid();
 
@@ -556,14 +559,14 @@ qgemv_i4_gp_kernel(const GemvParams p) {
     __syncthreads();
     uint32_t xs_addr = xs_lane, corr_addr = corr_lane;
     uint32_t i = 0;
-    for (; i + kDepth <= slab_n; i += kDepth) {
+    for (; i + kD <= slab_n; i += kD) {
 #pragma unroll
       for (int u = 0; u < kUnits; ++u) {
-        process(u, xs_addr, corr_addr, done + i + u * kCU + kDepth < nch);
+        process(u, xs_addr, corr_addr, done + i + u * kCU + kD < nch);
         xs_addr += 512;
         corr_addr += kG * kCorrStride * 4;
       }
-      next += kDepth * kCB;
+      next += kD * kCB;
     }
 #pragma unroll
     for (int u = 0; u < kUnits - 1; ++u) {  // the last, short round of the split
@@ -676,9 +679,10 @@ cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const L
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
-template <typename XT, bool kScaleF16, int kG>
-cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets) {
-  auto kernel = qgemv_i4_gp_kernel<XT, kScaleF16, kG>;
+template <typename XT, bool kScaleF16, int kG, int kD>
+cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets,
+                                  bool probe_only, uint32_t* ctas_out, uint32_t* capacity_out) {
+  auto kernel = qgemv_i4_gp_kernel<XT, kScaleF16, kG, kD>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
@@ -704,11 +708,23 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
   p.splits = splits;
   p.chunks_per_split = (units_per_row + splits - 1) / splits * kCU;
   const uint32_t per_chunk = 2 * (kCpg * 64 + kCorrStride * 4);
-  const uint32_t slab_cap = std::max<uint32_t>(kDepth, (32768u / per_chunk) / kDepth * kDepth);
+  const uint32_t slab_cap = std::max<uint32_t>(kD, (32768u / per_chunk) / kD * kD);
   p.slab_chunks = std::max<uint32_t>(kCU, std::min(p.chunks_per_split, slab_cap));
 
   const size_t slab_bytes = static_cast<size_t>(p.slab_chunks) * per_chunk;
   const size_t red_bytes = splits > 1 ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
+
+  if (ctas_out) *ctas_out = tiles * splits;
+  if (capacity_out) {
+    static int per_sm = -1;  // with the shared memory of a typical launch; registers decide
+    if (per_sm < 0) {
+      int v = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, kWarps * 32, 16 * 1024) != cudaSuccess) v = 0;
+      per_sm = v;
+    }
+    *capacity_out = static_cast<uint32_t>(per_sm) * static_cast<uint32_t>(env.sm_count);
+  }
+  if (probe_only) return cudaSuccess;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles, splits, 1);
@@ -732,6 +748,18 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
   cfg.attrs = attr;
   cfg.numAttrs = na;
   return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+// A ring twice as deep keeps every byte of a small matrix in flight at once, but costs
+// registers: worth it only while the whole grid is still resident in one wave.
+template <typename XT, bool kScaleF16, int kG>
+cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets) {
+  uint32_t ctas = 0, capacity = 0;
+  cudaError_t e = launch_typed_gp_depth<XT, kScaleF16, kG, 2 * kDepth>(env, p, count, targets, true, &ctas, &capacity);
+  if (e != cudaSuccess) return e;
+  if (KQ_TUNE_GP_DEEP && ctas <= capacity)
+    return launch_typed_gp_depth<XT, kScaleF16, kG, 2 * kDepth>(env, p, count, targets, false, nullptr, nullptr);
+  return launch_typed_gp_depth<XT, kScaleF16, kG, kDepth>(env, p, count, targets, false, nullptr, nullptr);
 }
 
 // Converts the whole activation block to the staged layout ONCE per launch, into global
