@@ -273,6 +273,36 @@ def test_tiled_gemv_dtypes_and_ragged_m(gpu, scale_dtype, xdt, m):
     w.free()
 
 
+@pytest.mark.parametrize("xdt,m", [("f32", 5), ("f32", 8), ("f32", 16), ("bf16", 12), ("f16", 8), ("f16", 16)])
+def test_many_row_blocks_take_the_paired_wide_variant(gpu, xdt, m):
+    """n >= 16384 (1024 row blocks) with many MMAs per row block selects two row blocks per
+    warp; n is not a multiple of the 128-row CTA tile, so the last tile is ragged."""
+    import torch
+    n, k = 16384 + 48, 192  # 1027 row blocks, 3 chunks (an odd count)
+    data, scale, x, bias = synth_case(n, k, m, seed=100 + m)
+    if xdt == "f16":
+        x = oracle.round_to_f16(x)
+    elif xdt == "bf16":
+        x = oracle.round_to_bf16(x)
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[xdt]
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    ref = oracle.linear_i4(x, data, np.asarray(scale, np.float32), bias, n, k, 32)
+    assert_close(run_linear(gpu, w, x, bias, dtype=tdt), ref, f"{xdt} m={m}")
+    w.free()
+
+
+@pytest.mark.parametrize("m", [1, 2])
+def test_small_grids_take_the_deep_ring(gpu, m):
+    """A grid that is resident in one wave streams through a ring twice as deep; k chosen so
+    that splits end in short ring rounds (9 chunks per split)."""
+    n, k = 1024, 64 * 72
+    data, scale, x, bias = synth_case(n, k, m, seed=200 + m)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    ref = oracle.linear_i4(x, data, scale.astype(np.float32), bias, n, k, 32)
+    assert_close(run_linear(gpu, w, x, bias), ref, f"m={m}")
+    w.free()
+
+
 def test_m_above_16_runs_in_row_panels(gpu):
     n, k, m = 64, 256, 65
     data, scale, x, bias = synth_case(n, k, m, seed=65)
