@@ -273,9 +273,10 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
     // Prefill: bf16 activations, more than 16 rows -> tcgen05 GEMM, one launch per weight.
     for (uint32_t i = 0; i < count; ++i) {
       if (targets[i].w->n == 0) continue;
-      cudaError_t e = kq::launch_qgemm_i4(env, targets[i], reinterpret_cast<const void*>(x), m, ctx->error_flag_dev + 1);
+      int extra = 0;
+      cudaError_t e = kq::launch_qgemm_i4(env, targets[i], reinterpret_cast<const void*>(x), m, ctx->error_flag_dev + 1, &extra);
       if (e != cudaSuccess) return cuda_fail(ctx, e, "qgemm_i4 launch");
-      ctx->launches += 1;
+      ctx->launches += 1 + extra;
     }
     return KQ_OK;
   }
@@ -357,7 +358,7 @@ int kq_init(int device, uint64_t workspace_bytes, kq_ctx** out) {
   kq_ctx* ctx = new kq_ctx();
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
-  ctx->workspace_bytes = workspace_bytes ? workspace_bytes : (16ull << 20);
+  ctx->workspace_bytes = workspace_bytes ? workspace_bytes : (64ull << 20);
   ctx->counter_count = 8192;
   e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes);

@@ -73,7 +73,7 @@ cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget*
 namespace kq {
 bool qgemm_i4_supports(const Weight& w, int x_dtype, uint32_t m);
 cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, const void* x, uint32_t m,
-                            int* status_word);
+                            int* status_word, int* extra_launches);
 }  // namespace kq
 
 // ---- fused plans (kq_plan.cu) -------------------------------------------------------

@@ -59,6 +59,10 @@ struct GemmParams {
   float* out;
   uint32_t m, n, k;
   int* status;
+  // K split over blockIdx.z: each slice accumulates ksteps_per_split k-steps and, when there is
+  // more than one slice, leaves its partial sums (no bias) in partial[z][m][n].
+  uint32_t ksteps_per_split, splits;
+  float* partial;
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -162,7 +166,9 @@ qgemm_i4_kernel(const GemmParams p) {
   (void)abort_addr;
 
   const uint32_t n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
-  const uint32_t ksteps = p.k / kBK;
+  const uint32_t ks_begin = blockIdx.z * p.ksteps_per_split;
+  const uint32_t ks_end = min(ks_begin + p.ksteps_per_split, p.k / kBK);
+  const uint32_t ksteps = ks_end - ks_begin;  // k-steps of this slice; stage and phase count from 0
   const uint32_t chunks_per_row = p.k / kChunkK;
 
   if (warp == kProducerWarps) {
@@ -199,7 +205,7 @@ qgemm_i4_kernel(const GemmParams p) {
         if constexpr (kScaleF16) sc_next[cc] = make_uint2(0, 0);
         else sc_next[cc] = make_uint4(0, 0, 0, 0);
         if (row0 < p.n && ks < ksteps) {
-          const uint8_t* chunk = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks) * kCB;
+          const uint8_t* chunk = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks_begin + ks) * kCB;
           wq_next[cc] = *reinterpret_cast<const uint4*>(chunk + lane * 16);
           if constexpr (kScaleF16) sc_next[cc] = *reinterpret_cast<const uint2*>(chunk + kChunkWeightBytes + g * 8);
           else sc_next[cc] = *reinterpret_cast<const uint4*>(chunk + kChunkWeightBytes + g * 16);
@@ -218,7 +224,7 @@ qgemm_i4_kernel(const GemmParams p) {
         const uint32_t piece = tid + i * (kProducerWarps * 32u);
         const uint32_t r = piece >> 3, c = piece & 7u;
         const bool in_range = m0 + r < p.m;
-        const __nv_bfloat16* src = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + ks * kBK + c * 8;
+        const __nv_bfloat16* src = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + (ks_begin + ks) * kBK + c * 8;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_tile + swz(r, c)), "l"(src),
                      "r"(in_range ? 16u : 0u) : "memory");
       }
@@ -284,11 +290,14 @@ qgemm_i4_kernel(const GemmParams p) {
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const uint32_t col0 = n0 + cb * 32u;
       if (row < p.m) {
-        float* dst = p.out + static_cast<size_t>(row) * p.n + col0;
+        const bool final_sum = p.splits == 1;
+        float* dst = (final_sum ? p.out : p.partial + static_cast<size_t>(blockIdx.z) * p.m * p.n) +
+                     static_cast<size_t>(row) * p.n + col0;
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
           if (col0 + j < p.n) {  // n is a multiple of 16, so a valid quad is wholly valid
-            const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+            const float4 b = final_sum ? *reinterpret_cast<const float4*>(p.bias + col0 + j)
+                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             float4 o;
             o.x = __uint_as_float(v[j]) + b.x;
             o.y = __uint_as_float(v[j + 1]) + b.y;
@@ -333,6 +342,26 @@ qgemm_i4_kernel(const GemmParams p) {
   }
 }
 
+// out = bias + sum over the K slices, slices in ascending order (deterministic).
+__global__ void __launch_bounds__(256)
+qgemm_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ bias, float* __restrict__ out,
+                    uint32_t m, uint32_t n, uint32_t splits) {
+  const size_t quads = static_cast<size_t>(m) * n / 4;
+  const size_t slice = static_cast<size_t>(m) * n;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < quads;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const uint32_t col = static_cast<uint32_t>((i * 4) % n);
+    float4 acc = *reinterpret_cast<const float4*>(partial + i * 4);
+    for (uint32_t z = 1; z < splits; ++z) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + z * slice + i * 4);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const float4 b = *reinterpret_cast<const float4*>(bias + col);
+    acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+    *reinterpret_cast<float4*>(out + i * 4) = acc;
+  }
+}
+
 }  // namespace
 
 bool qgemm_i4_supports(const Weight& w, int x_dtype, uint32_t m) {
@@ -340,7 +369,7 @@ bool qgemm_i4_supports(const Weight& w, int x_dtype, uint32_t m) {
 }
 
 cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, const void* x, uint32_t m,
-                            int* status_word) {
+                            int* status_word, int* extra_launches) {
   const Weight& w = *target.w;
   if (w.layout != kLayoutTiledI4) return cudaErrorInvalidValue;
   GemmParams p = {};
@@ -353,7 +382,18 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
   p.k = w.k;
   p.status = status_word;
   const size_t smem = kStagesG * kStageBytes + 1024 + 256;
-  const dim3 grid((w.n + kBN - 1) / kBN, (m + kBM - 1) / kBM);
+  // Few output tiles: split K over blockIdx.z until the grid covers the machine, as long as a
+  // slice keeps at least 8 k-steps and the partial sums fit the context's scratch.
+  const uint32_t tiles = ((w.n + kBN - 1) / kBN) * ((m + kBM - 1) / kBM);
+  const uint32_t ksteps_total = w.k / kBK;
+  uint32_t splits = 1;
+  while (splits < 8 && tiles * splits * 2 <= static_cast<uint32_t>(env.sm_count) && ksteps_total / (splits * 2) >= 8 &&
+         static_cast<uint64_t>(splits * 2) * m * w.n * sizeof(float) <= env.workspace_bytes && env.workspace != nullptr)
+    splits *= 2;
+  p.splits = splits;
+  p.ksteps_per_split = (ksteps_total + splits - 1) / splits;
+  p.partial = static_cast<float*>(env.workspace);
+  const dim3 grid((w.n + kBN - 1) / kBN, (m + kBM - 1) / kBM, splits);
   cudaError_t e;
   if (w.scale_dtype == KQ_F16) {
     static bool configured = false;
@@ -372,6 +412,12 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
     }
     qgemm_i4_kernel<false><<<grid, kGemmThreads, smem, env.stream>>>(p);
   }
+  e = cudaGetLastError();
+  if (e != cudaSuccess || splits == 1) return e;
+  const size_t quads = static_cast<size_t>(m) * w.n / 4;
+  const int rgrid = static_cast<int>(std::min<size_t>((quads + 255) / 256, static_cast<size_t>(env.sm_count) * 8));
+  qgemm_reduce_kernel<<<rgrid, 256, 0, env.stream>>>(p.partial, p.bias, p.out, m, w.n, splits);
+  if (extra_launches) *extra_launches += 1;
   return cudaGetLastError();
 }
 

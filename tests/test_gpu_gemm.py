@@ -90,3 +90,34 @@ def test_prefill_benchmark_shapes_on_sampled_rows_and_columns(gpu, m, k, n):
     rep = oracle.allclose(got[np.ix_(rows, cols)], ref, atol=atol, rtol=1e-3)
     assert rep["pass"], (atol, rep)
     w.free()
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 256, 4096), (512, 4096, 14336), (17, 528, 1152)])
+def test_few_output_tiles_split_k_and_reduce_in_order(gpu, m, n, k):
+    """With fewer output tiles than SMs the K range is split over more CTAs and the partial
+    sums are added in slice order by a second kernel: same tolerance, and replaying the call
+    gives the same bits."""
+    import torch
+    data, scale = cases.synth_i4(n, k, seed=k + m)
+    rng = np.random.default_rng(11)
+    x = oracle.round_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    bias = rng.standard_normal(n).astype(np.float32)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    xd, bd = dev(x).to(torch.bfloat16), dev(bias)
+    out1 = torch.full((m, n), float("nan"), device="cuda")
+    out2 = torch.full((m, n), float("nan"), device="cuda")
+    gpu.linear(xd, w, bd, out=out1)
+    gpu.linear(xd, w, bd, out=out2)
+    gpu.sync()
+    got = out1.cpu().numpy()
+    assert np.array_equal(bits(got), bits(out2.cpu().numpy()))
+    rows = np.arange(m) if m <= 64 else rng.choice(m, 48, replace=False)
+    cols = np.arange(n) if n <= 528 else np.sort(rng.choice(n, 256, replace=False))
+    sub = data.reshape(n, k // 2)[cols]
+    wq = oracle.round_to_bf16(oracle.decode_i4(sub, (len(cols), k), scale.astype(np.float32)[cols], (len(cols), k // 32), 32))
+    ref = oracle.linear_f64(x[rows], wq, bias[cols])
+    atol = max(1e-5, 1e-4 * float(np.sqrt(np.mean(ref.astype(np.float64) ** 2))))
+    rep = oracle.allclose(got[np.ix_(rows, cols)], ref, atol=atol, rtol=1e-3)
+    assert rep["pass"], (atol, rep)
+    assert np.all(np.isfinite(got))
+    w.free()
