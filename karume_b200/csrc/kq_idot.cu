@@ -18,6 +18,7 @@
 // masks and a shift per 8 weights) and the stored offset is taken out as an exact integer
 // correction (128 * sum xq per row, 8 * sum xq per group).
 #include <algorithm>
+#include <type_traits>
 
 #include "kq_common.cuh"
 #include "kq_internal.h"
@@ -225,6 +226,7 @@ struct IdotTiledParams {
 };
 
 constexpr int kIdotWarps = 2;
+constexpr int kIdotDepth = 4;  // chunks a warp keeps in flight
 
 // int8 weights: chunk (R, J) = 16 rows x 32 k, lane 4g+t holds (a0, a1, a2, a3) of the MMA
 // verbatim (bytes q + 128).  One MMA per 512 bytes of weights; the whole K range accumulates
@@ -240,7 +242,8 @@ __global__ void __launch_bounds__(kIdotWarps * 32) idot_w8a8_tiled_kernel(const 
   const bool col_live = g < p.m;
   const int8_t* xrow = p.xq + static_cast<size_t>(col_live ? g : 0) * p.k + 4 * t;
   int c[4] = {0, 0, 0, 0};
-#pragma unroll 4
+  // independent loads and one accumulator chain: unrolled, the compiler keeps 8 chunks in flight
+#pragma unroll 8
   for (uint32_t j = 0; j < chunks; ++j) {
     const uint4 a = ldg_stream(src + static_cast<size_t>(j) * 512u);
     uint32_t b0 = 0, b1 = 0;
@@ -280,20 +283,39 @@ __global__ void __launch_bounds__(kIdotWarps * 32) idot_w4a8_tiled_kernel(const 
   const int* gs0 = p.group_sum + static_cast<size_t>(m0 < p.m ? m0 : 0) * groups;
   const int* gs1 = p.group_sum + static_cast<size_t>(m1 < p.m ? m1 : 0) * groups;
   float accf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 2
-  for (uint32_t j = 0; j < chunks; ++j) {
+  // weights and scales run kIdotDepth chunks ahead of the MMAs, in registers
+  using ScaleRegs = typename std::conditional<kScaleF16, uint2, uint4>::type;
+  uint4 ring_w[kIdotDepth];
+  ScaleRegs ring_s[kIdotDepth];
+  auto fetch = [&](int d, uint32_t j) {
     const uint8_t* chunk = src + static_cast<size_t>(j) * kCB;
-    const uint4 wq = ldg_stream(chunk + lane * 16);
+    ring_w[d] = ldg_stream(chunk + lane * 16);
+    if constexpr (kScaleF16) ring_s[d] = __ldg(reinterpret_cast<const uint2*>(chunk + kChunkWeightBytes + g * 8));
+    else ring_s[d] = __ldg(reinterpret_cast<const uint4*>(chunk + kChunkWeightBytes + g * 16));
+  };
+#pragma unroll
+  for (int d = 0; d < kIdotDepth; ++d) {
+    ring_w[d] = make_uint4(0, 0, 0, 0);
+    if constexpr (kScaleF16) ring_s[d] = make_uint2(0, 0);
+    else ring_s[d] = make_uint4(0, 0, 0, 0);
+    if (static_cast<uint32_t>(d) < chunks) fetch(d, d);
+  }
+  for (uint32_t j0 = 0; j0 < chunks; j0 += kIdotDepth) {
+#pragma unroll
+  for (int d = 0; d < kIdotDepth; ++d) {
+    const uint32_t j = j0 + d;
+    if (j >= chunks) break;
+    const uint4 wq = ring_w[d];
     float sc[4];  // row g grp 0 | row g+8 grp 0 | row g grp 1 | row g+8 grp 1
     if constexpr (kScaleF16) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(chunk + kChunkWeightBytes + g * 8);
-      const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-      const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&ring_s[d].x));
+      const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&ring_s[d].y));
       sc[0] = lo.x; sc[1] = lo.y; sc[2] = hi.x; sc[3] = hi.y;
     } else {
-      const float4 raw = *reinterpret_cast<const float4*>(chunk + kChunkWeightBytes + g * 16);
-      sc[0] = raw.x; sc[1] = raw.y; sc[2] = raw.z; sc[3] = raw.w;
+      sc[0] = __uint_as_float(ring_s[d].x); sc[1] = __uint_as_float(ring_s[d].y);
+      sc[2] = __uint_as_float(ring_s[d].z); sc[3] = __uint_as_float(ring_s[d].w);
     }
+    if (j + kIdotDepth < chunks) fetch(d, j + kIdotDepth);
 #pragma unroll
     for (int jj = 0; jj < 2; ++jj) {
       const uint32_t group = 2 * j + jj;
@@ -313,6 +335,7 @@ __global__ void __launch_bounds__(kIdotWarps * 32) idot_w4a8_tiled_kernel(const 
       accf[2] = fmaf(__int2float_rn(c[2] - s0), sb, accf[2]);
       accf[3] = fmaf(__int2float_rn(c[3] - s1), sb, accf[3]);
     }
+  }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
