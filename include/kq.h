@@ -264,6 +264,15 @@ KQ_API int kq_plan_free(kq_ctx* ctx, kq_plan plan);
 KQ_API int kq_comm_create(kq_ctx* ctx, uint32_t rank, uint32_t world, uint64_t max_bytes, uint8_t* out_handle);
 KQ_API int kq_comm_connect(kq_ctx* ctx, const uint8_t* all_handles);
 KQ_API int kq_all_reduce(kq_ctx* ctx, uint64_t f32_dptr, uint64_t count);
+/* Row-parallel linear: out = sum over ranks of (x_r . W_r^T) + bias, the same bits on every rank;
+ * every rank passes its K shard of W (KQ_SHARD_ROW) and the matching slice of x.  For the decode
+ * shapes (tiled int4 weight, one or two f32 / bf16 rows or up to four binary16 rows, a grid that
+ * is resident in one wave) this is ONE kernel: each CTA of the GEMV pushes its partial sums into
+ * the peers' exchange areas over NVLink, raises a flag there, waits (bounded) for the same CTA of
+ * every peer and adds the ranks' values in rank order.  Otherwise it runs kq_linear (bias on rank 0
+ * only) followed by kq_all_reduce.  All ranks must issue the same sequence of calls. */
+KQ_API int kq_linear_reduce(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
+                            uint64_t out_dptr, uint32_t m);
 
 /* ---- timing ---------------------------------------------------------------------
  * CUDA events on the context's stream.  Replaces the reference's opt-in

@@ -62,6 +62,7 @@ SYMBOLS = {
     "kq_comm_create": (_i32, [_vp, _u32, _u32, _u64, _vp]),
     "kq_comm_connect": (_i32, [_vp, _vp]),
     "kq_all_reduce": (_i32, [_vp, _u64, _u64]),
+    "kq_linear_reduce": (_i32, [_vp, _u64, _u64, _i32, _u64, _u64, _u32]),
     "kq_timer_start": (_i32, [_vp]),
     "kq_timer_stop": (_i32, [_vp, ctypes.POINTER(ctypes.c_float)]),
     "kq_launch_count": (_u64, [_vp]),

@@ -42,6 +42,8 @@ struct kq_ctx {
   void* host_dev_x = nullptr;
   void* host_dev_out = nullptr;
   uint64_t host_x_bytes = 0, host_out_bytes = 0;
+  float* zero_bias = nullptr;  // kq_linear_reduce's unfused path: ranks other than 0 add no bias
+  uint64_t zero_bias_count = 0;
   int* idot_sums = nullptr;  // integer sums of the quantised activations (kq_linear_a8)
   uint64_t idot_sums_bytes = 0;
 };
@@ -402,6 +404,7 @@ void kq_destroy(kq_ctx* ctx) {
   if (ctx->host_dev_x) cudaFree(ctx->host_dev_x);
   if (ctx->host_dev_out) cudaFree(ctx->host_dev_out);
   if (ctx->idot_sums) cudaFree(ctx->idot_sums);
+  if (ctx->zero_bias) cudaFree(ctx->zero_bias);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -843,6 +846,57 @@ int kq_all_reduce(kq_ctx* ctx, uint64_t dptr, uint64_t count) {
   DeviceGuard guard(ctx->device);
   cudaError_t e = kq::comm_all_reduce(ctx->comm, ctx->stream, reinterpret_cast<float*>(dptr), count);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "kq_all_reduce launch");
+  ctx->launches += 1;
+  return KQ_OK;
+}
+
+int kq_linear_reduce(kq_ctx* ctx, kq_weight h, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr, uint64_t out_dptr,
+                     uint32_t m) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_linear_reduce cannot be recorded into a fused plan");
+  if (!kq::comm_connected(ctx->comm)) return fail(ctx, KQ_ERR_STATE, "kq_linear_reduce before kq_comm_connect");
+  const Weight* w = find_weight(ctx, h);
+  const int rc = check_linear_args(ctx, w, x_dptr, x_dtype, bias_dptr, out_dptr);
+  if (rc != KQ_OK) return rc;
+  if (out_dptr & 15u) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_reduce: out must be 16-byte aligned");
+  const uint64_t count = static_cast<uint64_t>(m) * w->n;
+  if (count * sizeof(float) > kq::comm_max_bytes(ctx->comm))
+    return fail(ctx, KQ_ERR_SHAPE, "kq_linear_reduce: %llu bytes exceed the %llu the exchange was created for",
+                (unsigned long long)(count * sizeof(float)), (unsigned long long)kq::comm_max_bytes(ctx->comm));
+  if (count == 0) return KQ_OK;
+  DeviceGuard guard(ctx->device);
+  // One kernel: the group-packed GEMV adds the ranks' partial sums in its epilogue.
+  if (w->layout == kq::kLayoutTiledI4 && kq::qgemv_i4_supports(*w, m)) {
+    kq::LaunchEnv env = env_of(ctx);
+    env.fused = kq::comm_fused_view(ctx->comm);
+    const kq::LinearTarget target{w, reinterpret_cast<const float*>(bias_dptr), reinterpret_cast<float*>(out_dptr)};
+    int launched = 0;
+    cudaError_t e = kq::launch_qgemv_i4(env, 1, &target, reinterpret_cast<const void*>(x_dptr), x_dtype, m, &launched);
+    if (e == cudaSuccess) {
+      ctx->launches += launched;
+      return KQ_OK;
+    }
+    if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "fused linear + exchange launch");
+    (void)cudaGetLastError();
+  }
+  // Two steps: the linear with the bias on rank 0 only, then the all-reduce.
+  uint64_t bias_here = bias_dptr;
+  if (kq::comm_rank(ctx->comm) != 0) {
+    if (w->n > ctx->zero_bias_count) {
+      if (ctx->capturing) return fail(ctx, KQ_ERR_STATE, "kq_linear_reduce: scratch must grow; call once outside the recording first");
+      if (ctx->zero_bias) cudaFree(ctx->zero_bias);
+      ctx->zero_bias = nullptr;
+      ctx->zero_bias_count = 0;
+      KQ_CUDA(ctx, cudaMalloc(reinterpret_cast<void**>(&ctx->zero_bias), static_cast<size_t>(w->n) * sizeof(float)));
+      KQ_CUDA(ctx, cudaMemset(ctx->zero_bias, 0, static_cast<size_t>(w->n) * sizeof(float)));
+      ctx->zero_bias_count = w->n;
+    }
+    bias_here = reinterpret_cast<uint64_t>(ctx->zero_bias);
+  }
+  const int rc2 = run_linear(ctx, 1, &h, x_dptr, x_dtype, &bias_here, &out_dptr, m);
+  if (rc2 != KQ_OK) return rc2;
+  cudaError_t e = kq::comm_all_reduce(ctx->comm, ctx->stream, reinterpret_cast<float*>(out_dptr), count);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "kq_linear_reduce: all-reduce launch");
   ctx->launches += 1;
   return KQ_OK;
 }

@@ -44,6 +44,10 @@ __host__ __device__ inline uint64_t comm_epoch_off() { return comm_flags_bytes()
 __host__ __device__ inline uint64_t comm_slot_off(uint64_t slot_bytes, uint32_t slot) {
   return comm_flags_bytes() + 256 + slot * slot_bytes;
 }
+// Area of the fused GEMV + exchange: [epoch, done | 256 B][flags][data], after the two slots.
+inline uint64_t fused_off(uint64_t slot_bytes) { return (comm_slot_off(slot_bytes, 2) + 255) & ~uint64_t(255); }
+inline uint64_t fused_flags_bytes() { return uint64_t(2) * kFusedMaxWorld * kFusedMaxCtas * sizeof(unsigned int); }
+inline uint64_t fused_data_bytes() { return uint64_t(2) * kFusedMaxWorld * kFusedSlotBytes; }
 
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -118,6 +122,7 @@ struct Comm {
   bool connected = false;
   int* status_host = nullptr;
   int* status_dev = nullptr;
+  FusedCommDev* fused_dev = nullptr;  // device copy of the view, filled by comm_connect
 };
 
 Comm* comm_create(uint32_t rank, uint32_t world, uint64_t max_bytes, uint8_t* handle_out, cudaError_t* err,
@@ -138,7 +143,7 @@ Comm* comm_create(uint32_t rank, uint32_t world, uint64_t max_bytes, uint8_t* ha
   c->rank = rank;
   c->world = world;
   c->slot_bytes = (max_bytes + 255) & ~uint64_t(255);
-  const uint64_t total = comm_slot_off(c->slot_bytes, 2);
+  const uint64_t total = fused_off(c->slot_bytes) + 256 + fused_flags_bytes() + fused_data_bytes();
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->local), total);
   if (e == cudaSuccess) e = cudaMemset(c->local, 0, total);
   cudaIpcMemHandle_t h;
@@ -173,15 +178,32 @@ cudaError_t comm_connect(Comm* c, const uint8_t* all_handles) {
     if (e != cudaSuccess) return e;
     c->base[r] = static_cast<uint8_t*>(ptr);
   }
+  FusedCommDev view = {};
+  for (uint32_t r = 0; r < c->world; ++r) view.base[r] = c->base[r];
+  view.rank = c->rank;
+  view.world = c->world;
+  const uint64_t f0 = fused_off(c->slot_bytes);
+  view.flags_off = f0 + 256;
+  view.data_off = f0 + 256 + fused_flags_bytes();
+  view.epoch = reinterpret_cast<unsigned int*>(c->local + f0);
+  view.done = reinterpret_cast<unsigned int*>(c->local + f0 + 128);
+  view.status = c->status_dev;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->fused_dev), sizeof(FusedCommDev));
+  if (e == cudaSuccess) e = cudaMemcpy(c->fused_dev, &view, sizeof(view), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return e;
   c->connected = true;
   return cudaSuccess;
 }
+
+const FusedCommDev* comm_fused_view(const Comm* c) { return c && c->connected ? c->fused_dev : nullptr; }
+uint32_t comm_rank(const Comm* c) { return c ? c->rank : 0; }
 
 void comm_destroy(Comm* c) {
   if (!c) return;
   for (uint32_t r = 0; r < c->world; ++r)
     if (r != c->rank && c->base[r]) cudaIpcCloseMemHandle(c->base[r]);
   if (c->local) cudaFree(c->local);
+  if (c->fused_dev) cudaFree(c->fused_dev);
   if (c->status_host) cudaFreeHost(c->status_host);
   delete c;
 }

@@ -33,6 +33,21 @@ struct LinearTarget {
   float* out;
 };
 
+// Device-side view of the tensor-parallel exchange area a row-parallel GEMV uses to add its
+// partial sums across ranks inside its own epilogue (kq_comm.cu owns the memory).
+constexpr int kFusedMaxWorld = 8;
+constexpr uint32_t kFusedMaxCtas = 1024;          // flags per source rank and parity
+constexpr uint64_t kFusedSlotBytes = 64 * 1024;   // m * n * 4 bytes per source rank and parity
+struct FusedCommDev {
+  uint8_t* base[kFusedMaxWorld];  // every rank's allocation (own included), peer-mapped
+  uint32_t rank, world;
+  uint64_t flags_off;   // [2][world][kFusedMaxCtas] u32: written by peers
+  uint64_t data_off;    // [2][world][kFusedSlotBytes]: partial sums pushed by peers
+  unsigned int* epoch;  // local: advanced by the last CTA of every fused launch
+  unsigned int* done;   // local: CTAs that finished their epilogue
+  int* status;          // host-mapped: non-zero once a bounded wait gave up
+};
+
 struct LaunchEnv {
   cudaStream_t stream;
   bool overlap;          // programmatic dependent launch
@@ -42,6 +57,7 @@ struct LaunchEnv {
   uint32_t counter_count;
   int* error_flag;       // device word: non-zero once a kernel saw an out-of-domain activation
   int sm_count;
+  const FusedCommDev* fused = nullptr;  // non-null: add the output across ranks in the epilogue
 };
 
 // Generic kernels: any shape the storage contract allows, native layout.
@@ -104,6 +120,8 @@ bool comm_connected(const Comm* c);
 uint64_t comm_max_bytes(const Comm* c);
 cudaError_t comm_all_reduce(Comm* c, cudaStream_t stream, float* data, uint64_t count);
 int comm_take_status(Comm* c);
+const FusedCommDev* comm_fused_view(const Comm* c);
+uint32_t comm_rank(const Comm* c);
 }  // namespace kq
 
 // ---- integer-dot linear (kq_idot.cu) ---------------------------------------------------

@@ -105,6 +105,8 @@ struct GemvParams {
   // only; null: every CTA converts its own slab).
   const uint8_t* staged_xs;
   const float* staged_corr;
+  // Non-null: a row-parallel shard; the outputs are added across ranks in the epilogue.
+  const FusedCommDev* fcomm;
 };
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
@@ -161,6 +163,110 @@ __device__ __forceinline__ void cluster_reduce_store(const GemvParams& p, float*
     out[static_cast<size_t>(mm) * n + row] = fmaf(sum, kUnscale, bias[row]);
   }
   cluster_sync_all();  // nobody's shared memory may go away while a peer still reads it
+}
+
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_volatile_f32(const float* p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+constexpr uint32_t kFusedSpinLimit = 1u << 22;
+
+// Row-parallel shard: the tile's outputs (partial sums over this rank's k range, in `red`,
+// possibly spread over the CTAs of a cluster) are added across ranks here, CTA by CTA:
+//   1. every thread finishes its few outputs and PUSHES them into every peer's exchange
+//      area (slot = epoch parity, source = this rank) with plain stores over NVLink;
+//   2. system fence, CTA barrier, then one store per peer raises this CTA's flag there;
+//   3. wait (bounded) for the same CTA of every peer to raise its flag here;
+//   4. add the ranks' values in rank order (all ranks get the same bits) plus the bias.
+// A CTA depends only on its twins on the other GPUs, which run the same grid, so nothing
+// waits on a CTA that is not resident as long as the grid fits the GPU in one wave (the host
+// checks).  The last CTA to finish advances the epoch for the next launch.
+__device__ __forceinline__ void reduce_exchange_store(const GemvParams& p, float* red, uint32_t tile_rows,
+                                                      uint32_t tile, uint32_t split, uint32_t n, float* out,
+                                                      const float* bias, unsigned int epoch) {
+  const FusedCommDev& fc = *p.fcomm;
+  const uint32_t me = fc.rank, world = fc.world;
+  if (p.splits > 1) cluster_sync_all();
+  else __syncthreads();
+  const uint32_t rows_here = min(tile_rows, n - tile * tile_rows);
+  const uint32_t total = rows_here * p.m;
+  const uint32_t per_rank = (total + p.splits - 1) / p.splits;
+  const uint32_t lo = min(split * per_rank, total), hi = min(lo + per_rank, total);
+  const uint32_t red_base = static_cast<uint32_t>(__cvta_generic_to_shared(red));
+  constexpr int kMaxPer = 4;  // tile_rows * m / threads <= 64 * 4 / 128, with room to spare
+  float v[kMaxPer];
+  uint32_t off[kMaxPer], rowi[kMaxPer];
+  int cnt = 0;
+  for (uint32_t idx = lo + threadIdx.x; idx < hi && cnt < kMaxPer; idx += blockDim.x) {
+    const uint32_t mm = idx / rows_here, r = idx - mm * rows_here;
+    float sum = 0.0f;
+    if (p.splits > 1) {
+      const uint32_t local = red_base + (mm * tile_rows + r) * 4u;
+      for (uint32_t s = 0; s < p.splits; ++s) sum += ld_cluster_f32(cluster_map_shared(local, s));
+    } else {
+      sum = red[mm * tile_rows + r];
+    }
+    const uint32_t row = tile * tile_rows + r;
+    v[cnt] = sum * kUnscale;
+    off[cnt] = mm * n + row;
+    rowi[cnt] = row;
+    ++cnt;
+  }
+  const uint32_t parity = epoch & 1u;
+  const uint32_t cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+  const uint64_t my_slot = (static_cast<uint64_t>(parity) * kFusedMaxWorld + me) * kFusedSlotBytes;
+  for (uint32_t r = 0; r < world; ++r) {
+    if (r == me) continue;
+    float* dst = reinterpret_cast<float*>(fc.base[r] + fc.data_off + my_slot);
+    for (int i = 0; i < cnt; ++i) dst[off[i]] = v[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world && threadIdx.x != me) {
+    const uint32_t peer = threadIdx.x;
+    unsigned int* theirs = reinterpret_cast<unsigned int*>(fc.base[peer] + fc.flags_off) +
+                           (static_cast<size_t>(parity) * kFusedMaxWorld + me) * kFusedMaxCtas + cta_id;
+    st_release_sys_u32(theirs, epoch);
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(fc.base[me] + fc.flags_off) +
+                               (static_cast<size_t>(parity) * kFusedMaxWorld + peer) * kFusedMaxCtas + cta_id;
+    uint32_t spins = 0;
+    while (static_cast<int>(ld_acquire_sys_u32(mine) - epoch) < 0) {  // epochs only grow
+      if (++spins > kFusedSpinLimit) {
+        *reinterpret_cast<volatile int*>(fc.status) = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = 0; i < cnt; ++i) {
+    float sum = 0.0f;
+    for (uint32_t r = 0; r < world; ++r) {
+      const float* src = reinterpret_cast<const float*>(
+          fc.base[me] + fc.data_off + (static_cast<uint64_t>(parity) * kFusedMaxWorld + r) * kFusedSlotBytes);
+      sum += r == me ? v[i] : ld_volatile_f32(src + off[i]);
+    }
+    out[off[i]] = sum + bias[rowi[i]];
+  }
+  if (p.splits > 1) cluster_sync_all();  // nobody's shared memory may go away while a peer still reads it
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int finished = atomicAdd(fc.done, 1u) + 1u;
+    if (finished == gridDim.x * gridDim.y) {
+      *reinterpret_cast<volatile unsigned int*>(fc.done) = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(fc.epoch) = epoch;
+    }
+  }
 }
 
 template <bool kScaleF16>
@@ -494,6 +600,8 @@ qgemv_i4_gp_kernel(const GemvParams p) {
   next += kD * kCB;
 
   pdl_wait_prior_grid();
+  // the epoch of this exchange: written by the previous fused launch, which has finished now
+  const unsigned int epoch = p.fcomm != nullptr ? *reinterpret_cast<volatile unsigned int*>(p.fcomm->epoch) + 1u : 0u;
 
   float acc[kAcc];
 #pragma unroll
@@ -589,7 +697,8 @@ qgemv_i4_gp_kernel(const GemvParams p) {
     acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 2);
   }
   float* red = reinterpret_cast<float*>(smem);  // [m][kTileRowsCta], aliases the x slab
-  if (p.splits > 1) __syncthreads();
+  const bool fused = p.fcomm != nullptr;
+  if (p.splits > 1 || fused) __syncthreads();
   if (active && jl == 0) {
     const uint32_t row_a = row_block * 16u + g;
     const uint32_t tr_a = warp * 16u + g;
@@ -599,7 +708,7 @@ qgemv_i4_gp_kernel(const GemvParams p) {
       if (mm >= p.m) continue;
       const float va = acc[kHasLo ? 0 : j];
       const float vb = acc[kHasLo ? 1 : 2 + j];
-      if (p.splits == 1) {
+      if (p.splits == 1 && !fused) {
         out[static_cast<size_t>(mm) * n + row_a] = fmaf(va, kUnscale, bias[row_a]);
         out[static_cast<size_t>(mm) * n + row_a + 8] = fmaf(vb, kUnscale, bias[row_a + 8]);
       } else {
@@ -607,6 +716,10 @@ qgemv_i4_gp_kernel(const GemvParams p) {
         red[mm * kTileRowsCta + tr_a + 8] = vb;
       }
     }
+  }
+  if (fused) {
+    reduce_exchange_store(p, red, kTileRowsCta, tile, split, n, out, bias, epoch);
+    return;
   }
   if (p.splits == 1) return;
   cluster_reduce_store(p, red, kTileRowsCta, tile, split, n, out, bias);
@@ -712,7 +825,8 @@ cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count
   p.slab_chunks = std::max<uint32_t>(kCU, std::min(p.chunks_per_split, slab_cap));
 
   const size_t slab_bytes = static_cast<size_t>(p.slab_chunks) * per_chunk;
-  const size_t red_bytes = splits > 1 ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
+  p.fcomm = env.fused;
+  const size_t red_bytes = (splits > 1 || env.fused != nullptr) ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
 
   if (ctas_out) *ctas_out = tiles * splits;
   if (capacity_out) {
@@ -751,14 +865,24 @@ cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count
 }
 
 // A ring twice as deep keeps every byte of a small matrix in flight at once, but costs
-// registers: worth it only while the whole grid is still resident in one wave.
+// registers: worth it only while the whole grid is still resident in one wave.  The fused
+// exchange NEEDS one wave (its CTAs wait for their twins on the other GPUs): when the grid
+// does not fit, the caller gets cudaErrorNotSupported and runs the exchange separately.
 template <typename XT, bool kScaleF16, int kG>
 cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets) {
   uint32_t ctas = 0, capacity = 0;
   cudaError_t e = launch_typed_gp_depth<XT, kScaleF16, kG, 2 * kDepth>(env, p, count, targets, true, &ctas, &capacity);
   if (e != cudaSuccess) return e;
+  if (env.fused != nullptr && (count != 1 || ctas > kFusedMaxCtas ||
+                               static_cast<uint64_t>(p.m) * targets[0].w->n * sizeof(float) > kFusedSlotBytes))
+    return cudaErrorNotSupported;
   if (KQ_TUNE_GP_DEEP && ctas <= capacity)
     return launch_typed_gp_depth<XT, kScaleF16, kG, 2 * kDepth>(env, p, count, targets, false, nullptr, nullptr);
+  if (env.fused != nullptr) {
+    e = launch_typed_gp_depth<XT, kScaleF16, kG, kDepth>(env, p, count, targets, true, &ctas, &capacity);
+    if (e != cudaSuccess) return e;
+    if (ctas > capacity) return cudaErrorNotSupported;
+  }
   return launch_typed_gp_depth<XT, kScaleF16, kG, kDepth>(env, p, count, targets, false, nullptr, nullptr);
 }
 
@@ -1097,6 +1221,7 @@ cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const Linea
     return f16s ? launch_typed_gp<XT, true, 4>(env, p, count, t) : launch_typed_gp<XT, false, 4>(env, p, count, t);
   if (KQ_TUNE_GP && cols <= 4)
     return f16s ? launch_typed_gp<XT, true, 2>(env, p, count, t) : launch_typed_gp<XT, false, 2>(env, p, count, t);
+  if (env.fused != nullptr) return cudaErrorNotSupported;  // only the group-packed kernel exchanges in its epilogue
   if (KQ_TUNE_WIDE && !(kHasLo && p.m <= 4)) {
     // Two row blocks per warp (sharing the activation loads) pay off when a row block costs
     // many MMAs (hi + lo parts, or two column tiles) and the matrix has rows to spare;

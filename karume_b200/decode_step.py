@@ -164,6 +164,15 @@ class DecodeStep:
         elif self.world > 1:
             self.torch.distributed.all_reduce(t, group=self.pg)
 
+    def _row_parallel(self, x, w, out):
+        """o / down: K-sharded; the ranks' partial sums are added by libkq (inside the GEMV when
+        it can) or by NCCL."""
+        if self.exchange == "kq":
+            self.gpu.linear_reduce(x, w, self._bias(self.cfg.hidden), out=out)
+        else:
+            self.gpu.linear(x, w, self._bias(self.cfg.hidden), out=out)
+            self._all_reduce(out)
+
     def enqueue(self) -> None:
         """Enqueues the step's launches on the context's stream (no host sync)."""
         g, W = self.gpu, self.weights
@@ -174,12 +183,10 @@ class DecodeStep:
             g.linear_multi(cur, [W[p + "q"], W[p + "k"], W[p + "v"]],
                            [self._bias(self.q.shape[1]), self._bias(self.k.shape[1]), self._bias(self.v.shape[1])],
                            [self.q, self.k, self.v])
-            g.linear(self.q, W[p + "o"], self._bias(self.cfg.hidden), out=self.o)
-            self._all_reduce(self.o)
+            self._row_parallel(self.q, W[p + "o"], self.o)
             g.linear_multi(self.o, [W[p + "gate"], W[p + "up"]],
                            [self._bias(self.gate.shape[1]), self._bias(self.up.shape[1])], [self.gate, self.up])
-            g.linear(self.gate, W[p + "down"], self._bias(self.cfg.hidden), out=self.h)
-            self._all_reduce(self.h)
+            self._row_parallel(self.gate, W[p + "down"], self.h)
         g.linear(self.h, W["lm_head"], self._bias(self.logits.shape[1]), out=self.logits)
 
     # -- recorded plans ---------------------------------------------------------------------

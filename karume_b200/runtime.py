@@ -288,6 +288,19 @@ class Gpu:
             raise KqError(1, "all_reduce takes a contiguous f32 tensor")
         self._check(L.kq_all_reduce(self._ctx, t.data_ptr(), t.numel()))
 
+    def linear_reduce(self, x, weight: Weight, bias, out=None):
+        """Row-parallel linear: every rank passes its K shard; out = sum over ranks + bias, the
+        same bits on every rank (one kernel for decode shapes, else linear + all_reduce)."""
+        torch = _torch()
+        if x.shape[-1] != weight.k:
+            raise KqError(2, f"x[..., {x.shape[-1]}] does not match the shard's k={weight.k}")
+        m = x.numel() // weight.k if weight.k else 0
+        if out is None:
+            out = torch.empty(tuple(x.shape[:-1]) + (weight.n,), dtype=torch.float32, device=x.device)
+        self._check(L.kq_linear_reduce(self._ctx, weight.handle, x.data_ptr(), _tensor_dtype_code(x), bias.data_ptr(),
+                                       out.data_ptr(), m))
+        return out
+
     def timer_start(self) -> None:
         self._check(L.kq_timer_start(self._ctx))
 

@@ -65,6 +65,48 @@ def _worker(rank, world, port, out_dir):
         dist.barrier()
     results.append(("graph_replay", good))
     gpu.use_stream(torch.cuda.current_stream())
+    # 2b. row-parallel linear with the exchange inside the GEMV (kq_linear_reduce): every rank
+    # holds a K shard; the result is the full linear, the same bits on both ranks, also when
+    # the launch is replayed from a graph (the epoch lives on the device)
+    from tests import cases
+    from karume_b200._consts import KQ_SHARD_ROW
+    fused_ok = True
+    for (n, k, m) in [(512, 1024, 1), (4096, 2048, 2), (272, 256, 1)]:
+        data, scale = cases.synth_i4(n, k, seed=n + m)
+        rng = np.random.default_rng(5)
+        xf = rng.standard_normal((m, k)).astype(np.float32)
+        bias = rng.standard_normal(n).astype(np.float32)
+        w = gpu.upload_weight("i4", data, scale, (n, k), 32, shard=KQ_SHARD_ROW, rank=rank, world=world)
+        ks = k // world
+        xs = torch.from_numpy(np.ascontiguousarray(xf[:, rank * ks:(rank + 1) * ks])).cuda()
+        bd = torch.from_numpy(bias).cuda()
+        torch.cuda.synchronize()
+        ref = oracle.linear_i4(xf, data, scale.astype(np.float32), bias, n, k, 32)
+        for _ in range(3):
+            out = gpu.linear_reduce(xs, w, bd)
+            gpu.sync()
+            fused_ok = fused_ok and oracle.allclose(out.cpu().numpy(), ref, atol=1e-5, rtol=1e-3)["pass"]
+            both = [torch.empty_like(out) for _ in range(world)]
+            dist.all_gather(both, out)
+            fused_ok = fused_ok and bool(torch.equal(both[0], both[1]))
+        gpu.use_stream(stream)
+        torch.cuda.synchronize()
+        out_g = torch.zeros((m, n), device="cuda")
+        gpu.graph_begin()
+        gpu.linear_reduce(xs, w, bd, out=out_g)
+        gpu.linear_reduce(xs, w, bd, out=out_g)
+        gg = gpu.graph_end()
+        for _ in range(3):
+            out_g.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            gpu.graph_launch(gg)
+            gpu.sync()
+            fused_ok = fused_ok and oracle.allclose(out_g.cpu().numpy(), ref, atol=1e-5, rtol=1e-3)["pass"]
+        gpu.graph_free(gg)
+        gpu.use_stream(torch.cuda.current_stream())
+        w.free()
+    results.append(("linear_reduce", fused_ok))
     gpu.destroy()
     # 3. tensor-parallel decode step (column / row shards + libkq all-reduce) vs the oracle
     from tests.test_gpu_decode_step import reference_step
@@ -93,8 +135,8 @@ def test_two_gpu_all_reduce_and_tensor_parallel_step(tmp_path):
     world = 2
     port = 29700 + os.getpid() % 200
     ctx = mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=False, daemon=True)
-    ctx.join(timeout=150)
+    ctx.join(timeout=240)
     for rank in range(world):
         path = tmp_path / f"rank{rank}.txt"
         assert path.exists(), f"rank {rank} did not finish"
-        assert open(path).read() == "all_reduce=1 graph_replay=1 tp_decode_step=1"
+        assert open(path).read() == "all_reduce=1 graph_replay=1 linear_reduce=1 tp_decode_step=1"
