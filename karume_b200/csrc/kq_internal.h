@@ -36,13 +36,13 @@ struct LinearTarget {
 // Device-side view of the tensor-parallel exchange area a row-parallel GEMV uses to add its
 // partial sums across ranks inside its own epilogue (kq_comm.cu owns the memory).
 constexpr int kFusedMaxWorld = 8;
-constexpr uint32_t kFusedMaxCtas = 1024;          // flags per source rank and parity
-constexpr uint64_t kFusedSlotBytes = 64 * 1024;   // m * n * 4 bytes per source rank and parity
+constexpr uint32_t kFusedMaxCtas = 1024;          // largest grid the fused exchange accepts
+constexpr uint64_t kFusedSlotBytes = 64 * 1024;   // m * n entries of 8 bytes {value, epoch} per source rank and parity
 struct FusedCommDev {
   uint8_t* base[kFusedMaxWorld];  // every rank's allocation (own included), peer-mapped
   uint32_t rank, world;
-  uint64_t flags_off;   // [2][world][kFusedMaxCtas] u32: written by peers
-  uint64_t data_off;    // [2][world][kFusedSlotBytes]: partial sums pushed by peers
+  uint64_t flags_off;   // reserved
+  uint64_t data_off;    // [2][world][kFusedSlotBytes]: {value, epoch} entries pushed by peers
   unsigned int* epoch;  // local: advanced by the last CTA of every fused launch
   unsigned int* done;   // local: CTAs that finished their epilogue
   int* status;          // host-mapped: non-zero once a bounded wait gave up

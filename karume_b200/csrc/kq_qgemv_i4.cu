@@ -165,28 +165,14 @@ __device__ __forceinline__ void cluster_reduce_store(const GemvParams& p, float*
   cluster_sync_all();  // nobody's shared memory may go away while a peer still reads it
 }
 
-__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_volatile_f32(const float* p) {
-  float v;
-  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
-  return v;
-}
 constexpr uint32_t kFusedSpinLimit = 1u << 22;
 
 // Row-parallel shard: the tile's outputs (partial sums over this rank's k range, in `red`,
 // possibly spread over the CTAs of a cluster) are added across ranks here, CTA by CTA:
-//   1. every thread finishes its few outputs and PUSHES them into every peer's exchange
-//      area (slot = epoch parity, source = this rank) with plain stores over NVLink;
-//   2. system fence, CTA barrier, then one store per peer raises this CTA's flag there;
-//   3. wait (bounded) for the same CTA of every peer to raise its flag here;
-//   4. add the ranks' values in rank order (all ranks get the same bits) plus the bias.
+//   1. every thread finishes its few outputs and PUSHES each into every peer's exchange area
+//      (slot = epoch parity, source = this rank) as one 8-byte store {value, epoch};
+//   2. it then polls (bounded) its own area until the peers' entries carry this epoch;
+//   3. and adds the ranks' values in rank order (all ranks get the same bits) plus the bias.
 // A CTA depends only on its twins on the other GPUs, which run the same grid, so nothing
 // waits on a CTA that is not resident as long as the grid fits the GPU in one wave (the host
 // checks).  The last CTA to finish advances the epoch for the next launch.
@@ -221,38 +207,38 @@ __device__ __forceinline__ void reduce_exchange_store(const GemvParams& p, float
     rowi[cnt] = row;
     ++cnt;
   }
+  // Low-latency exchange: every output travels as one aligned 8-byte store {value, epoch}, so
+  // data and flag arrive together and no fence or separate flag is needed; the receiver polls
+  // the entry itself.  Entries of consecutive epochs alternate between two slots, so a peer
+  // that is one exchange ahead never overwrites an entry that has not been read.
   const uint32_t parity = epoch & 1u;
-  const uint32_t cta_id = blockIdx.y * gridDim.x + blockIdx.x;
-  const uint64_t my_slot = (static_cast<uint64_t>(parity) * kFusedMaxWorld + me) * kFusedSlotBytes;
+  const uint64_t slot_entries = kFusedSlotBytes / 8;
   for (uint32_t r = 0; r < world; ++r) {
     if (r == me) continue;
-    float* dst = reinterpret_cast<float*>(fc.base[r] + fc.data_off + my_slot);
-    for (int i = 0; i < cnt; ++i) dst[off[i]] = v[i];
+    uint2* dst = reinterpret_cast<uint2*>(fc.base[r] + fc.data_off) + (static_cast<uint64_t>(parity) * kFusedMaxWorld + me) * slot_entries;
+    for (int i = 0; i < cnt; ++i)
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + off[i]), "r"(__float_as_uint(v[i])), "r"(epoch) : "memory");
   }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < world && threadIdx.x != me) {
-    const uint32_t peer = threadIdx.x;
-    unsigned int* theirs = reinterpret_cast<unsigned int*>(fc.base[peer] + fc.flags_off) +
-                           (static_cast<size_t>(parity) * kFusedMaxWorld + me) * kFusedMaxCtas + cta_id;
-    st_release_sys_u32(theirs, epoch);
-    const unsigned int* mine = reinterpret_cast<const unsigned int*>(fc.base[me] + fc.flags_off) +
-                               (static_cast<size_t>(parity) * kFusedMaxWorld + peer) * kFusedMaxCtas + cta_id;
-    uint32_t spins = 0;
-    while (static_cast<int>(ld_acquire_sys_u32(mine) - epoch) < 0) {  // epochs only grow
-      if (++spins > kFusedSpinLimit) {
-        *reinterpret_cast<volatile int*>(fc.status) = 1;
-        break;
-      }
-    }
-  }
-  __syncthreads();
   for (int i = 0; i < cnt; ++i) {
     float sum = 0.0f;
     for (uint32_t r = 0; r < world; ++r) {
-      const float* src = reinterpret_cast<const float*>(
-          fc.base[me] + fc.data_off + (static_cast<uint64_t>(parity) * kFusedMaxWorld + r) * kFusedSlotBytes);
-      sum += r == me ? v[i] : ld_volatile_f32(src + off[i]);
+      if (r == me) {
+        sum += v[i];
+        continue;
+      }
+      const uint2* src = reinterpret_cast<const uint2*>(fc.base[me] + fc.data_off) +
+                         (static_cast<uint64_t>(parity) * kFusedMaxWorld + r) * slot_entries + off[i];
+      uint2 e;
+      uint32_t spins = 0;
+      while (true) {
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "l"(src) : "memory");
+        if (e.y == epoch) break;
+        if (++spins > kFusedSpinLimit) {
+          *reinterpret_cast<volatile int*>(fc.status) = 1;
+          break;
+        }
+      }
+      sum += __uint_as_float(e.x);
     }
     out[off[i]] = sum + bias[rowi[i]];
   }
@@ -874,7 +860,7 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
   cudaError_t e = launch_typed_gp_depth<XT, kScaleF16, kG, 2 * kDepth>(env, p, count, targets, true, &ctas, &capacity);
   if (e != cudaSuccess) return e;
   if (env.fused != nullptr && (count != 1 || ctas > kFusedMaxCtas ||
-                               static_cast<uint64_t>(p.m) * targets[0].w->n * sizeof(float) > kFusedSlotBytes))
+                               static_cast<uint64_t>(p.m) * targets[0].w->n * 8u > kFusedSlotBytes))
     return cudaErrorNotSupported;
   if (KQ_TUNE_GP_DEEP && ctas <= capacity)
     return launch_typed_gp_depth<XT, kScaleF16, kG, 2 * kDepth>(env, p, count, targets, false, nullptr, nullptr);
