@@ -71,7 +71,7 @@ def _worker(rank, world, port, out_dir):
     from tests import cases
     from karume_b200._consts import KQ_SHARD_ROW
     fused_ok = True
-    for (n, k, m) in [(512, 1024, 1), (4096, 2048, 2), (272, 256, 1)]:
+    for (n, k, m) in [(512, 1024, 1), (4096, 2048, 2), (272, 256, 1), (272, 512, 5)]:  # m = 5: linear + all-reduce
         data, scale = cases.synth_i4(n, k, seed=n + m)
         rng = np.random.default_rng(5)
         xf = rng.standard_normal((m, k)).astype(np.float32)
