@@ -49,7 +49,7 @@ enum kq_status {
   KQ_ERR_CUDA = 4,        /* a CUDA runtime call failed; message carries the CUDA error */
   KQ_ERR_UNSUPPORTED = 5, /* valid request this build has no kernel for (never a silent alternate path) */
   KQ_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up (multi-GPU exchange) */
-  KQ_ERR_RANGE = 7,       /* an activation was outside the domain a kernel documents */
+  /* 7 is retired (it reported activations beyond the binary16 range; the kernels now take any value) */
   KQ_ERR_STATE = 8        /* call not legal now (e.g. graph capture already open) */
 };
 

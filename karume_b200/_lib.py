@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "libkq.so")
 KQ_OK = 0
 STATUS_NAMES = {
     0: "KQ_OK", 1: "KQ_ERR_BAD_ARG", 2: "KQ_ERR_SHAPE", 3: "KQ_ERR_OOM", 4: "KQ_ERR_CUDA",
-    5: "KQ_ERR_UNSUPPORTED", 6: "KQ_ERR_TIMEOUT", 7: "KQ_ERR_RANGE", 8: "KQ_ERR_STATE",
+    5: "KQ_ERR_UNSUPPORTED", 6: "KQ_ERR_TIMEOUT", 8: "KQ_ERR_STATE",
 }
 from ._consts import (KQ_BF16, KQ_F16, KQ_F32, KQ_SHARD_COLUMN, KQ_SHARD_NONE, KQ_SHARD_ROW,  # noqa: F401
                       KQ_STORAGE_I4, KQ_STORAGE_I8)

@@ -33,8 +33,8 @@ struct kq_ctx {
   uint64_t workspace_bytes = 0;
   unsigned int* counters = nullptr;
   uint32_t counter_count = 0;
-  int* error_flag_host = nullptr;  // mapped, page-locked: [0] activation range flag, [1] GEMM wait status
-  int* error_flag_dev = nullptr;
+  int* gemm_status_host = nullptr;  // mapped, page-locked: non-zero once a bounded wait of the tcgen05 GEMM gave up
+  int* gemm_status_dev = nullptr;
   int sm_count = 0;
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
   uint64_t launches = 0;
@@ -94,7 +94,6 @@ kq::LaunchEnv env_of(kq_ctx* ctx) {
   env.workspace_bytes = ctx->workspace_bytes;
   env.counters = ctx->counters;
   env.counter_count = ctx->counter_count;
-  env.error_flag = ctx->error_flag_dev;
   env.sm_count = ctx->sm_count;
   return env;
 }
@@ -276,7 +275,7 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
     for (uint32_t i = 0; i < count; ++i) {
       if (targets[i].w->n == 0) continue;
       int extra = 0;
-      cudaError_t e = kq::launch_qgemm_i4(env, targets[i], reinterpret_cast<const void*>(x), m, ctx->error_flag_dev + 1, &extra);
+      cudaError_t e = kq::launch_qgemm_i4(env, targets[i], reinterpret_cast<const void*>(x), m, ctx->gemm_status_dev, &extra);
       if (e != cudaSuccess) return cuda_fail(ctx, e, "qgemm_i4 launch");
       ctx->launches += 1 + extra;
     }
@@ -366,11 +365,10 @@ int kq_init(int device, uint64_t workspace_bytes, kq_ctx** out) {
   if (e == cudaSuccess) e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ctx->counters), ctx->counter_count * sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMemset(ctx->counters, 0, ctx->counter_count * sizeof(unsigned int));
-  if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->error_flag_host), 2 * sizeof(int), cudaHostAllocMapped);
+  if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->gemm_status_host), sizeof(int), cudaHostAllocMapped);
   if (e == cudaSuccess) {
-    ctx->error_flag_host[0] = 0;
-    ctx->error_flag_host[1] = 0;
-    e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->error_flag_dev), ctx->error_flag_host, 0);
+    ctx->gemm_status_host[0] = 0;
+    e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->gemm_status_dev), ctx->gemm_status_host, 0);
   }
   if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_start);
   if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_stop);
@@ -399,7 +397,7 @@ void kq_destroy(kq_ctx* ctx) {
   }
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->counters) cudaFree(ctx->counters);
-  if (ctx->error_flag_host) cudaFreeHost(ctx->error_flag_host);
+  if (ctx->gemm_status_host) cudaFreeHost(ctx->gemm_status_host);
   if (ctx->host_x) cudaFreeHost(ctx->host_x);
   if (ctx->host_dev_x) cudaFree(ctx->host_dev_x);
   if (ctx->host_dev_out) cudaFree(ctx->host_dev_out);
@@ -431,9 +429,9 @@ int kq_sync(kq_ctx* ctx) {
   if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_sync while a graph or plan is being recorded");
   DeviceGuard guard(ctx->device);
   KQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  if (reinterpret_cast<volatile int*>(ctx->error_flag_host)[1] != 0) {
-    const int code = reinterpret_cast<volatile int*>(ctx->error_flag_host)[1];
-    reinterpret_cast<volatile int*>(ctx->error_flag_host)[1] = 0;
+  if (*reinterpret_cast<volatile int*>(ctx->gemm_status_host) != 0) {
+    const int code = *reinterpret_cast<volatile int*>(ctx->gemm_status_host);
+    *reinterpret_cast<volatile int*>(ctx->gemm_status_host) = 0;
     return fail(ctx, KQ_ERR_TIMEOUT, "a bounded wait inside the tcgen05 GEMM gave up (stage %d); its outputs are not valid", code);
   }
   if (ctx->comm && kq::comm_take_status(ctx->comm) != 0)
@@ -443,12 +441,6 @@ int kq_sync(kq_ctx* ctx) {
     if (st != 0)
       return fail(ctx, KQ_ERR_TIMEOUT, "a bounded wait inside the fused plan kernel gave up (%s); its outputs are not valid",
                   st == 1 ? "grid barrier between ops" : "weight copy completion");
-  }
-  if (*reinterpret_cast<volatile int*>(ctx->error_flag_host) != 0) {
-    *reinterpret_cast<volatile int*>(ctx->error_flag_host) = 0;
-    return fail(ctx, KQ_ERR_RANGE,
-                "an activation had a finite magnitude above 65504, outside the tensor-core GEMV's domain; "
-                "outputs of the launches since the last kq_sync are not valid");
   }
   return KQ_OK;
 }
@@ -473,7 +465,10 @@ int kq_buffer_write(kq_ctx* ctx, uint64_t dptr, uint64_t offset, const void* hos
   if (!ctx || !dptr || (!host && bytes)) return fail(ctx, KQ_ERR_BAD_ARG, "kq_buffer_write: null argument");
   DeviceGuard guard(ctx->device);
   if (ctx->recording) {
-    if (bytes) kq::plan_add_copy(ctx->recording, true, reinterpret_cast<uint8_t*>(dptr) + offset, const_cast<void*>(host), bytes);
+    if (bytes) {
+      const char* why = kq::plan_add_copy(ctx->recording, true, reinterpret_cast<uint8_t*>(dptr) + offset, const_cast<void*>(host), bytes);
+      if (why[0] != 0 && ctx->recording_refusal.empty()) ctx->recording_refusal = why;
+    }
     return KQ_OK;
   }
   if (bytes)
@@ -486,7 +481,10 @@ int kq_buffer_read(kq_ctx* ctx, uint64_t dptr, uint64_t offset, void* host, uint
   if (!ctx || !dptr || (!host && bytes)) return fail(ctx, KQ_ERR_BAD_ARG, "kq_buffer_read: null argument");
   DeviceGuard guard(ctx->device);
   if (ctx->recording) {
-    if (bytes) kq::plan_add_copy(ctx->recording, false, reinterpret_cast<uint8_t*>(dptr) + offset, host, bytes);
+    if (bytes) {
+      const char* why = kq::plan_add_copy(ctx->recording, false, reinterpret_cast<uint8_t*>(dptr) + offset, host, bytes);
+      if (why[0] != 0 && ctx->recording_refusal.empty()) ctx->recording_refusal = why;
+    }
     return KQ_OK;
   }
   if (bytes)
@@ -731,10 +729,6 @@ int kq_linear_static(kq_ctx* ctx, kq_weight h, uint64_t x_dptr, int x_dtype, uin
   ctx->launches += 1;
   if (device_status != 0)
     return fail(ctx, KQ_ERR_TIMEOUT, "kq_linear_static: a bounded wait inside the kernel gave up; the output is not valid");
-  if (*reinterpret_cast<volatile int*>(ctx->error_flag_host) != 0) {
-    *reinterpret_cast<volatile int*>(ctx->error_flag_host) = 0;
-    return fail(ctx, KQ_ERR_RANGE, "kq_linear_static: an activation had a finite magnitude above 65504");
-  }
   return KQ_OK;
 }
 

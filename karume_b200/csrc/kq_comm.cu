@@ -63,6 +63,12 @@ __device__ __forceinline__ float4 ld_peer_f4(const float4* p) {
   return v;
 }
 
+__device__ __forceinline__ float ld_peer_f32(const float* p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
 __global__ void __launch_bounds__(kCommThreads)
 all_reduce_kernel(const CommParams p) {
   const uint32_t b = blockIdx.x;
@@ -75,13 +81,19 @@ all_reduce_kernel(const CommParams p) {
   const uint32_t slot = epoch & 1u;
 
   // this CTA's slice, in float4 units: always the same 16 KB stripe of the slots, whatever
-  // the size of the exchange, so the per-CTA epochs order every reuse of a stripe
-  const uint64_t vec = (p.count + 3) / 4;
+  // the size of the exchange, so the per-CTA epochs order every reuse of a stripe.  A count
+  // that is not a multiple of four ends in a partial vector: the CTA whose stripe holds it
+  // moves those one to three elements with scalar accesses, so nothing beyond the caller's
+  // vector is read or written.
+  const uint64_t vec = (p.count + 3) / 4, full = p.count / 4;
   const uint64_t v0 = min(static_cast<uint64_t>(b) * kStripeVec, vec), v1 = min(v0 + kStripeVec, vec);
+  const uint64_t v1_full = min(v1, full);
+  const uint32_t tail = (v0 <= full && full < v1) ? static_cast<uint32_t>(p.count - full * 4) : 0u;
 
   float4* my_slot = reinterpret_cast<float4*>(mine + comm_slot_off(p.slot_bytes, slot));
   const float4* src = reinterpret_cast<const float4*>(p.data);
-  for (uint64_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) my_slot[i] = src[i];
+  for (uint64_t i = v0 + threadIdx.x; i < v1_full; i += blockDim.x) my_slot[i] = src[i];
+  if (threadIdx.x < tail) reinterpret_cast<float*>(my_slot)[full * 4 + threadIdx.x] = p.data[full * 4 + threadIdx.x];
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x < p.world) {
@@ -101,13 +113,19 @@ all_reduce_kernel(const CommParams p) {
   }
   __syncthreads();
   float4* dst = reinterpret_cast<float4*>(p.data);
-  for (uint64_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+  for (uint64_t i = v0 + threadIdx.x; i < v1_full; i += blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t r = 0; r < p.world; ++r) {
       const float4 v = ld_peer_f4(reinterpret_cast<const float4*>(p.base[r] + comm_slot_off(p.slot_bytes, slot)) + i);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     dst[i] = acc;
+  }
+  if (threadIdx.x < tail) {
+    float acc = 0.f;
+    for (uint32_t r = 0; r < p.world; ++r)
+      acc += ld_peer_f32(reinterpret_cast<const float*>(p.base[r] + comm_slot_off(p.slot_bytes, slot)) + full * 4 + threadIdx.x);
+    p.data[full * 4 + threadIdx.x] = acc;
   }
   if (threadIdx.x == 0) epochs[b] = epoch;
 }

@@ -51,32 +51,73 @@ __device__ __forceinline__ void load_x8(const XT* p, float (&v)[8]) {
     }
   }
 }
+// ---- power-of-two pre-scale of the activations -------------------------------------------
+// binary16 has a narrow exponent range, f32 activations do not.  Before an activation is split
+// into binary16 parts it is multiplied by 2^e, with e chosen from the largest magnitude of the
+// values that share it (a 32-k scale group of one activation row, or a whole activation row),
+// so that this maximum lands in [2^13, 2^14).  The multiplication is exact, the matching
+// 2^-e is applied in f32 to the group's (or row's) partial sum, and the result no longer
+// depends on the magnitude of x: there is neither an upper limit at 65504 nor an absolute
+// error floor at the binary16 subnormal grid (the parts then resolve 2^-37 of the maximum,
+// 2^-33 for the odd positions that are stored divided by 16).
+// A maximum of zero or a non-finite one leaves the values as they are (e = 0): Inf and NaN
+// reach the MMA unchanged and make the outputs of that activation row non-finite, as they do
+// in an f32 multiply-add.
+struct Pow2 {
+  float scale;  // 2^e
+  float inv;    // 2^-e
+};
+__device__ __forceinline__ Pow2 pow2_prescale(float amax) {
+  const uint32_t bits = __float_as_uint(amax) & 0x7fffffffu;
+  int e = 0;
+  if (bits != 0u && bits < 0x7f800000u) {
+    e = 13 + 127 - static_cast<int>(bits >> 23);  // subnormal maxima count as 2^-127
+    e = max(-114, min(126, e));
+  }
+  Pow2 r;
+  r.scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
+  r.inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+  return r;
+}
+__device__ __forceinline__ float absmax8(const float (&v)[8]) {
+  float a = fabsf(v[0]);
+#pragma unroll
+  for (int e = 1; e < 8; ++e) a = fmaxf(a, fabsf(v[e]));
+  // fmaxf drops NaN operands; an Inf is enough to switch the pre-scale off, and a NaN next to
+  // finite values is staged as NaN whatever the scale is
+  return a;
+}
+
 // Stages groups [group0, group0 + groups) of x into shared memory.
 //   xs   : [local group][active columns][32 halfs]; activation row r occupies column r
 //          (binary16 input) or columns 2r (hi) and 2r+1 (lo).  The 8 values of each
 //          k-octet are stored in the order 0,4,1,5,2,6,3,7, and the odd ones (1,3,5,7)
 //          are stored divided by 16: their nibbles reach the MMA as u * 2^-20 instead
-//          of u * 2^-24.
-//   corr : [local group][kCorrStride] f32; entry r = -8 * 2^-24 * (sum of the group's x
-//          of activation row r, as staged): the "- 8" of the storage rule
+//          of u * 2^-24.  Every value is pre-scaled by the 2^e of its (row, group), see above.
+//   corr : kPerGroup  : [local group][kCorrStride] float2; entry r =
+//                       { -8 * 2^-24 * (sum of the group's x of activation row r, as staged),
+//                         2^-e of that (row, group) }
+//          !kPerGroup : [local group][kCorrStride] f32, the first of the two only; the
+//                       caller passes one scale per activation row in row_scale
 // Four consecutive threads share one (group, row): each converts one octet.
 // kBatch: octets a thread loads before it converts any (one memory round trip per batch, at
 // the price of 8 registers per octet held).
 //   lo_offset != 0 selects the split layout: activation row r occupies column r, its hi part at
 //          byte offset 0 of the group and its lo part lo_offset bytes further on.
-template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2 = false, int kBatch = 1>
+template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2 = false, int kBatch = 1, bool kPerGroup = true>
 __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, uint32_t k,
                                         uint32_t group0, uint32_t groups, uint8_t* xs,
-                                        uint32_t xs_stride, float* corr, int* error_flag,
-                                        uint32_t lo_offset = 0) {
+                                        uint32_t xs_stride, float* corr, uint32_t lo_offset = 0,
+                                        const float* row_scale = nullptr) {
   const uint32_t items = groups * m * 4;
   const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles below
-  bool out_of_range = false;
   for (uint32_t base = threadIdx.x; base < items_padded; base += blockDim.x * kBatch) {
     float v[kBatch][8];
 #pragma unroll
     for (int b = 0; b < kBatch; ++b) {
       const uint32_t item = base + b * blockDim.x;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[b][e] = 0.0f;
       if (item < items) {
         const uint32_t rest = item >> 2;
         const uint32_t row = rest % m, lg = rest / m;
@@ -93,15 +134,23 @@ __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, ui
       const uint32_t rest = item >> 2;
       const uint32_t row = rest % m;
       const uint32_t lg = rest / m;
+      Pow2 ps;
+      if constexpr (kPerGroup) {
+        float amax = absmax8(v[b]);
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        ps = pow2_prescale(amax);
+      } else {
+        ps.scale = valid ? row_scale[row] : 1.0f;
+        ps.inv = 1.0f;
+      }
       uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
       float sum = 0.0f;
       if (valid) {
         __half h[8], l[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float a = fabsf(v[b][e]);
-          if (a > 65504.0f && a < __int_as_float(0x7f800000)) out_of_range = true;
-          const float staged = (e & 1) ? v[b][e] * 0.0625f : v[b][e];
+          const float staged = v[b][e] * ((e & 1) ? ps.scale * 0.0625f : ps.scale);
           const float back = (e & 1) ? 16.0f : 1.0f;
           h[e] = __float2half_rn(staged);
           const float hf = __half2float(h[e]);
@@ -125,11 +174,15 @@ __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, ui
         const uint32_t off = lg * xs_stride + col * 64 + q * 16;
         *reinterpret_cast<uint4*>(xs + off) = hi4;
         if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + (lo_offset == 0 ? 64u : lo_offset)) = lo4;
-        if (q == 0) corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
+        if (q == 0) {
+          if constexpr (kPerGroup)
+            reinterpret_cast<float2*>(corr)[lg * kCorrStride + row] = make_float2(sum * (-8.0f / kUnscale), ps.inv);
+          else
+            corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
+        }
       }
     }
   }
-  if (out_of_range) *reinterpret_cast<volatile int*>(error_flag) = 1;  // sticky, host-mapped word
 }
 
 
@@ -144,6 +197,13 @@ __device__ __forceinline__ void lds_v4_if(uint4& v, uint32_t addr, bool pred) {
 __device__ __forceinline__ void lds_f32_if(float& v, uint32_t addr, bool pred) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p ld.shared.f32 %0, [%1];\n\t}"
                : "+f"(v)
+               : "r"(addr), "r"(static_cast<uint32_t>(pred)));
+}
+
+// {corr, 2^-e} pair of a (group, activation row), see stage_x
+__device__ __forceinline__ void lds_v2f_if(float& a, float& b, uint32_t addr, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %3, 0;\n\t@p ld.shared.v2.f32 {%0,%1}, [%2];\n\t}"
+               : "+f"(a), "+f"(b)
                : "r"(addr), "r"(static_cast<uint32_t>(pred)));
 }
 

@@ -55,7 +55,6 @@ struct LaunchEnv {
   uint64_t workspace_bytes;
   unsigned int* counters;  // split-K arrival counters (zero between launches)
   uint32_t counter_count;
-  int* error_flag;       // device word: non-zero once a kernel saw an out-of-domain activation
   int sm_count;
   const FusedCommDev* fused = nullptr;  // non-null: add the output across ranks in the epilogue
 };
@@ -97,7 +96,7 @@ namespace kq {
 struct Plan;
 Plan* plan_create();
 void plan_destroy(Plan* plan);
-void plan_add_copy(Plan* plan, bool to_device, void* device, void* host, uint64_t bytes);
+const char* plan_add_copy(Plan* plan, bool to_device, void* device, void* host, uint64_t bytes);
 const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, const void* x, int x_dtype,
                             uint32_t m);
 uint32_t plan_op_count(const Plan* plan);

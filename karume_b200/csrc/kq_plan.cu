@@ -31,13 +31,7 @@
 namespace kq {
 namespace {
 
-#ifndef KQ_PLAN_PAIRED
-#define KQ_PLAN_PAIRED 1
-#endif
-#ifndef KQ_PLAN_WARPS
-#define KQ_PLAN_WARPS 16
-#endif
-constexpr int kPlanWarps = KQ_PLAN_WARPS;
+constexpr int kPlanWarps = 16;
 constexpr int kSlots = 2;  // ring slots per warp
 constexpr uint32_t kOpWindow = 16;  // op descriptors the paired kernel keeps in shared memory
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -67,22 +61,8 @@ struct PlanParams {
   uint32_t m;
   uint32_t xs_bytes;       // shared memory reserved for the staged activations of one op
   unsigned int* grid_bar;  // arrivals at the inter-op barrier (zeroed before every launch)
-  int* error_flag;         // activation out of domain
   int* status;             // non-zero: a bounded wait gave up
-#ifdef KQ_PLAN_TRACE
-  unsigned long long* trace;  // [cta][op][4] globaltimer stamps
-#endif
 };
-#ifdef KQ_PLAN_TRACE
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define KQ_TRACE(slot) do { if (threadIdx.x == 0) p.trace[(static_cast<size_t>(cta) * p.op_count + op) * 8 + (slot)] = gtime(); } while (0)
-#else
-#define KQ_TRACE(slot) do {} while (0)
-#endif
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -177,8 +157,8 @@ plan_kernel(const PlanParams p) {
   const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
   const uint32_t xs_stride = kG > 1 ? kCpg * 64u : active_cols * 64;
   const uint32_t groups_max = p.xs_bytes / xs_stride;
-  float* corr = reinterpret_cast<float*>(xs + p.xs_bytes);
-  float* red = corr + groups_max * kCorrStride;  // [2][kPlanWarps][m][16]
+  float* corr = reinterpret_cast<float*>(xs + p.xs_bytes);  // {-8 sum x, 2^-e} pairs, see stage_x
+  float* red = corr + groups_max * kCorrStride * 2;  // [2][kPlanWarps][m][16]
 
   if (lane == 0) {
 #pragma unroll
@@ -227,7 +207,7 @@ plan_kernel(const PlanParams p) {
 
   // Persistent per-lane state of the MMA operands (see qgemv_i4_kernel).
   uint4 bfrag[kTiles];
-  float cterm[kTiles][kCorrPerTile];
+  float cterm[kTiles][kCorrPerTile], cinv[kTiles][kCorrPerTile];
   bool load_b[kTiles], load_c[kTiles][kCorrPerTile];
 #pragma unroll
   for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
@@ -236,12 +216,13 @@ plan_kernel(const PlanParams p) {
 #pragma unroll
     for (int j = 0; j < kCorrPerTile; ++j) {
       cterm[tile_m][j] = 0.0f;
+      cinv[tile_m][j] = 0.0f;
       const uint32_t mm = kHasLo ? tile_m * 4 + t : tile_m * 8 + 2 * t + j;
       load_c[tile_m][j] = mm < p.m;
     }
   }
   const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
-  const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) + (kHasLo ? t : 2 * t) * 4;
+  const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) + (kHasLo ? t : 2 * t) * 8;
 
   // Group packing: the group (inside a unit) and activation row(s) of this lane's two C
   // columns, the group whose activations it feeds the MMAs with, one register set per group.
@@ -249,7 +230,7 @@ plan_kernel(const PlanParams p) {
   const uint32_t tl = kG > 1 ? t % (kCpg / 2) : t;
   uint4 bset[kG];
   bool load_bset[kG];
-  float gterm[kCorrPerTile];
+  float gterm[kCorrPerTile], ginv[kCorrPerTile];
   bool load_g[kCorrPerTile];
 #pragma unroll
   for (int j = 0; j < kG; ++j) {
@@ -259,16 +240,16 @@ plan_kernel(const PlanParams p) {
 #pragma unroll
   for (int j = 0; j < kCorrPerTile; ++j) {
     gterm[j] = 0.0f;
+    ginv[j] = 0.0f;
     load_g[j] = (kHasLo ? tl : 2 * tl + j) < p.m;
   }
   const uint32_t gcorr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) +
-                              (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 4;
+                              (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 8;
   const uint32_t gscale_off = (jl >> 1) * kCB + kChunkWeightBytes + g * (4 * kScaleBytes) + (jl & 1u) * (2 * kScaleBytes);
 
   uint32_t cons_q = 0, red_buf = 0;
   for (uint32_t op = 0; op < p.op_count; ++op) {
     const PlanOpDev& o = p.ops[op];
-    KQ_TRACE(0);
     if (op > 0) {
       // every output of the previous op must be complete and visible before x is read
       __syncthreads();
@@ -287,12 +268,9 @@ plan_kernel(const PlanParams p) {
       }
       __syncthreads();
     }
-    KQ_TRACE(1);
     // stage the op's whole activation block (it fits: checked when the plan was built)
-    stage_x<XT, kHasLo, kCorrStride, true>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, xs_stride, corr,
-                                           p.error_flag);
+    stage_x<XT, kHasLo, kCorrStride, true>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, xs_stride, corr);
     __syncthreads();
-    KQ_TRACE(2);
 
     const uint32_t slabs = o.slabs;
     for (uint32_t round = 0; round < o.rounds; ++round) {
@@ -341,7 +319,7 @@ plan_kernel(const PlanParams p) {
             for (int j = 0; j < kG; ++j) lds_v4_if(bset[j], xs_lane + unit * 512, load_bset[j]);
 #pragma unroll
             for (int j = 0; j < kCorrPerTile; ++j)
-              lds_f32_if(gterm[j], gcorr_lane + (unit * (kG * kCorrStride) + j) * 4, load_g[j]);
+              lds_v2f_if(gterm[j], ginv[j], gcorr_lane + (unit * (kG * kCorrStride) + j) * 8, load_g[j]);
             float cf[4];
 #pragma unroll
             for (int j = 0; j < kG; ++j) {
@@ -355,13 +333,13 @@ plan_kernel(const PlanParams p) {
               mma_f16(cf, a1, bset[j].z, bset[j].w);
             }
             if constexpr (kHasLo) {
-              acc[0][0] = fmaf(s.x, (cf[0] + cf[1]) + gterm[0], acc[0][0]);
-              acc[0][1] = fmaf(s.y, (cf[2] + cf[3]) + gterm[0], acc[0][1]);
+              acc[0][0] = fmaf(s.x, ((cf[0] + cf[1]) + gterm[0]) * ginv[0], acc[0][0]);
+              acc[0][1] = fmaf(s.y, ((cf[2] + cf[3]) + gterm[0]) * ginv[0], acc[0][1]);
             } else {
-              acc[0][0] = fmaf(s.x, cf[0] + gterm[0], acc[0][0]);
-              acc[0][1] = fmaf(s.x, cf[1] + gterm[1], acc[0][1]);
-              acc[0][2] = fmaf(s.y, cf[2] + gterm[0], acc[0][2]);
-              acc[0][3] = fmaf(s.y, cf[3] + gterm[1], acc[0][3]);
+              acc[0][0] = fmaf(s.x, (cf[0] + gterm[0]) * ginv[0], acc[0][0]);
+              acc[0][1] = fmaf(s.x, (cf[1] + gterm[1]) * ginv[1], acc[0][1]);
+              acc[0][2] = fmaf(s.y, (cf[2] + gterm[0]) * ginv[0], acc[0][2]);
+              acc[0][3] = fmaf(s.y, (cf[3] + gterm[1]) * ginv[1], acc[0][3]);
             }
           }
         } else {
@@ -394,8 +372,8 @@ plan_kernel(const PlanParams p) {
               lds_v4_if(bfrag[tile_m], xs_lane + lg * xs_stride + tile_m * 512, load_b[tile_m]);
 #pragma unroll
               for (int j = 0; j < kCorrPerTile; ++j)
-                lds_f32_if(cterm[tile_m][j], corr_lane + (lg * kCorrStride + tile_m * (kHasLo ? 4 : 8) + j) * 4,
-                           load_c[tile_m][j]);
+                lds_v2f_if(cterm[tile_m][j], cinv[tile_m][j],
+                           corr_lane + (lg * kCorrStride + tile_m * (kHasLo ? 4 : 8) + j) * 8, load_c[tile_m][j]);
             }
             const uint32_t wa = jj ? wq.z : wq.x;  // row g
             const uint32_t wb = jj ? wq.w : wq.y;  // row g + 8
@@ -409,13 +387,13 @@ plan_kernel(const PlanParams p) {
               mma_f16_zero(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y);
               mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
               if constexpr (kHasLo) {
-                acc[tile_m][0] = fmaf(s.x, (cf[0] + cf[1]) + cterm[tile_m][0], acc[tile_m][0]);
-                acc[tile_m][1] = fmaf(s.y, (cf[2] + cf[3]) + cterm[tile_m][0], acc[tile_m][1]);
+                acc[tile_m][0] = fmaf(s.x, ((cf[0] + cf[1]) + cterm[tile_m][0]) * cinv[tile_m][0], acc[tile_m][0]);
+                acc[tile_m][1] = fmaf(s.y, ((cf[2] + cf[3]) + cterm[tile_m][0]) * cinv[tile_m][0], acc[tile_m][1]);
               } else {
-                acc[tile_m][0] = fmaf(s.x, cf[0] + cterm[tile_m][0], acc[tile_m][0]);
-                acc[tile_m][1] = fmaf(s.x, cf[1] + cterm[tile_m][1], acc[tile_m][1]);
-                acc[tile_m][2] = fmaf(s.y, cf[2] + cterm[tile_m][0], acc[tile_m][2]);
-                acc[tile_m][3] = fmaf(s.y, cf[3] + cterm[tile_m][1], acc[tile_m][3]);
+                acc[tile_m][0] = fmaf(s.x, (cf[0] + cterm[tile_m][0]) * cinv[tile_m][0], acc[tile_m][0]);
+                acc[tile_m][1] = fmaf(s.x, (cf[1] + cterm[tile_m][1]) * cinv[tile_m][1], acc[tile_m][1]);
+                acc[tile_m][2] = fmaf(s.y, (cf[2] + cterm[tile_m][0]) * cinv[tile_m][0], acc[tile_m][2]);
+                acc[tile_m][3] = fmaf(s.y, (cf[3] + cterm[tile_m][1]) * cinv[tile_m][1], acc[tile_m][3]);
               }
             }
           }
@@ -482,7 +460,6 @@ plan_kernel(const PlanParams p) {
       }
       red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
     }
-    KQ_TRACE(3);
   }
 }
 
@@ -533,9 +510,9 @@ __device__ __forceinline__ void lds_v4_if_at(uint4& v, uint32_t base, bool pred)
                : "r"(base), "r"(static_cast<uint32_t>(pred)), "n"(kOff));
 }
 template <int kOff>
-__device__ __forceinline__ void lds_f32_if_at(float& v, uint32_t base, bool pred) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p ld.shared.f32 %0, [%1+%3];\n\t}"
-               : "+f"(v) : "r"(base), "r"(static_cast<uint32_t>(pred)), "n"(kOff));
+__device__ __forceinline__ void lds_v2f_if_at(float& a, float& b, uint32_t base, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %3, 0;\n\t@p ld.shared.v2.f32 {%0,%1}, [%2+%4];\n\t}"
+               : "+f"(a), "+f"(b) : "r"(base), "r"(static_cast<uint32_t>(pred)), "n"(kOff));
 }
 
 struct PairItem {
@@ -609,8 +586,8 @@ plan_pair_kernel(const PlanParams p) {
   const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
   constexpr uint32_t kXsStride = kCpg * 64u;
   const uint32_t groups_max = p.xs_bytes / kXsStride;
-  float* corr = reinterpret_cast<float*>(xs + p.xs_bytes);
-  float* red = corr + groups_max * kCorrStride;  // [2][kPlanWarps][2][m][16]
+  float* corr = reinterpret_cast<float*>(xs + p.xs_bytes);  // {-8 sum x, 2^-e} pairs, see stage_x
+  float* red = corr + groups_max * kCorrStride * 2;  // [2][kPlanWarps][2][m][16]
   // A window of op descriptors in shared memory (entry i lives in slot i % kOpWindow): the
   // producer and the consumer read them every item, and a chain of dependent global loads
   // there would sit on every warp's critical path.
@@ -673,7 +650,7 @@ plan_pair_kernel(const PlanParams p) {
   const uint32_t tl = t % (kCpg / 2);       // which activation row(s) inside that group
   uint4 bset[kG];
   bool load_bset[kG];
-  float gterm[kCorr];
+  float gterm[kCorr], ginv[kCorr];
   bool load_g[kCorr];
 #pragma unroll
   for (int j = 0; j < kG; ++j) {
@@ -683,11 +660,12 @@ plan_pair_kernel(const PlanParams p) {
 #pragma unroll
   for (int j = 0; j < kCorr; ++j) {
     gterm[j] = 0.0f;
+    ginv[j] = 0.0f;
     load_g[j] = (kHasLo ? tl : 2 * tl + j) < p.m;
   }
   const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
   const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) +
-                             (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 4;
+                             (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 8;
   const uint32_t scale_lane = (jl >> 1) * kCB + kChunkWeightBytes + g * (4 * kScaleBytes) + (jl & 1u) * (2 * kScaleBytes);
 
   float acc[2][kAcc];
@@ -715,7 +693,7 @@ plan_pair_kernel(const PlanParams p) {
     for (int j = 0; j < kG; ++j) lds_v4_if_at<kU * 512>(bset[j], xs_base, load_bset[j]);
     static_for<kCorr>([&](auto kj) {
       constexpr int kJ = decltype(kj)::value;
-      lds_f32_if_at<(kU * kG * kCorrStride + kJ) * 4>(gterm[kJ], corr_base, load_g[kJ]);
+      lds_v2f_if_at<(kU * kG * kCorrStride + kJ) * 8>(gterm[kJ], ginv[kJ], corr_base, load_g[kJ]);
     });
     float cf[2][4];
 #pragma unroll
@@ -736,20 +714,19 @@ plan_pair_kernel(const PlanParams p) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       if constexpr (kHasLo) {
-        acc[r][0] = fmaf(sc[r].x, (cf[r][0] + cf[r][1]) + gterm[0], acc[r][0]);
-        acc[r][1] = fmaf(sc[r].y, (cf[r][2] + cf[r][3]) + gterm[0], acc[r][1]);
+        acc[r][0] = fmaf(sc[r].x, ((cf[r][0] + cf[r][1]) + gterm[0]) * ginv[0], acc[r][0]);
+        acc[r][1] = fmaf(sc[r].y, ((cf[r][2] + cf[r][3]) + gterm[0]) * ginv[0], acc[r][1]);
       } else {
-        acc[r][0] = fmaf(sc[r].x, cf[r][0] + gterm[0], acc[r][0]);
-        acc[r][1] = fmaf(sc[r].x, cf[r][1] + gterm[1], acc[r][1]);
-        acc[r][2] = fmaf(sc[r].y, cf[r][2] + gterm[0], acc[r][2]);
-        acc[r][3] = fmaf(sc[r].y, cf[r][3] + gterm[1], acc[r][3]);
+        acc[r][0] = fmaf(sc[r].x, (cf[r][0] + gterm[0]) * ginv[0], acc[r][0]);
+        acc[r][1] = fmaf(sc[r].x, (cf[r][1] + gterm[1]) * ginv[1], acc[r][1]);
+        acc[r][2] = fmaf(sc[r].y, (cf[r][2] + gterm[0]) * ginv[0], acc[r][2]);
+        acc[r][3] = fmaf(sc[r].y, (cf[r][3] + gterm[1]) * ginv[1], acc[r][3]);
       }
     }
   };
 
   uint32_t cons_q = 0, red_buf = 0;
   for (uint32_t op = 0; op < p.op_count; ++op) {
-    KQ_TRACE(0);
     // Nothing about the first item depends on the previous op: look it up before the wait.
     const PairItem first_item = pair_item_of<kCB>(win[op % kOpWindow], 0, warp, grid, cta);
     if (op > 0) {
@@ -774,11 +751,8 @@ plan_pair_kernel(const PlanParams p) {
     }
     cur_op = op;
     const PlanOpDev& o = win[op % kOpWindow];
-    KQ_TRACE(1);
-    stage_x<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr,
-                                           p.error_flag);
+    stage_x<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr);
     __syncthreads();
-    KQ_TRACE(2);
 
     const uint32_t slabs = o.slabs, rounds = o.rounds;
     for (uint32_t round = 0; round < rounds; ++round) {
@@ -817,24 +791,22 @@ plan_pair_kernel(const PlanParams p) {
             }
           }
         }
-        if (first == 0 && round == 0) KQ_TRACE(4);
         const uint32_t slot_addr = ring + slot * kSlotBytes;
         const uint32_t unit0 = (it.c0 + first) / kCU;
         const uint32_t w_base = slot_addr + lane * 16, s_base = slot_addr + scale_lane;
-        const uint32_t xs_base = xs_lane + unit0 * 512, corr_base = corr_lane + unit0 * (kG * kCorrStride * 4);
+        const uint32_t xs_base = xs_lane + unit0 * 512, corr_base = corr_lane + unit0 * (kG * kCorrStride * 8);
         if (nc == kPiece) {
           static_for<kPieceUnits>([&](auto ku) { unit_step(ku, w_base, s_base, xs_base, corr_base); });
         } else {
           for (uint32_t u = 0; u * kCU < nc; ++u)
             unit_step(std::integral_constant<int, 0>{}, w_base + u * (kCU * kCB), s_base + u * (kCU * kCB),
-                      xs_base + u * 512, corr_base + u * (kG * kCorrStride * 4));
+                      xs_base + u * 512, corr_base + u * (kG * kCorrStride * 8));
         }
         __syncwarp();  // every lane has read the slot: it can take the next piece
         produce();
         cons_q += 1;
       }
 
-      if (round == 0) KQ_TRACE(5);
       // ---- this round's outputs ------------------------------------------------------
       // lanes whose C columns belong to different groups hold partial sums of the same outputs
 #pragma unroll
@@ -874,7 +846,6 @@ plan_pair_kernel(const PlanParams p) {
           }
       }
       __syncthreads();
-      if (round == 0) KQ_TRACE(6);
       if ((warp & (slabs - 1u)) == 0 && it.valid) {
         const float* first_slab = mine;
         for (uint32_t idx = lane; idx < 32u * p.m; idx += 32) {
@@ -889,7 +860,6 @@ plan_pair_kernel(const PlanParams p) {
       }
       red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
     }
-    KQ_TRACE(3);
   }
 }
 
@@ -940,7 +910,7 @@ cudaError_t configure(Plan& plan, int sm_count, bool* fits) {
   const size_t xs_bytes = static_cast<size_t>(groups) * (kG > 1 ? kCpg : active_cols) * 64;
   const uint32_t corr_stride = kG > 1 ? (kHasLo ? kCpg / 2 : kCpg) : (kHasLo ? kCols / 2 : kCols);
   const size_t smem = static_cast<size_t>(kPlanWarps) * kSlots * kSlotChunks * cb + kPlanWarps * kSlots * 8 + xs_bytes +
-                      static_cast<size_t>(groups) * corr_stride * 4 +
+                      static_cast<size_t>(groups) * corr_stride * 8 +
                       static_cast<size_t>(2) * kPlanWarps * plan.m * 16 * sizeof(float);
   plan.unit_chunks = kG > 1 ? kG / 2 : 1;
   *fits = smem <= kSmemBudget;
@@ -967,7 +937,7 @@ cudaError_t configure_pair(Plan& plan, int sm_count, bool* fits) {
   const uint32_t groups = plan.k_max / 32;
   const size_t xs_bytes = static_cast<size_t>(groups) * kCpg * 64;
   const size_t smem = static_cast<size_t>(kPlanWarps) * kSlots * 2 * kPiece * cb + kPlanWarps * kSlots * 8 + xs_bytes +
-                      static_cast<size_t>(groups) * (kHasLo ? kCpg / 2 : kCpg) * 4 +
+                      static_cast<size_t>(groups) * (kHasLo ? kCpg / 2 : kCpg) * 8 +
                       static_cast<size_t>(2) * kPlanWarps * 2 * plan.m * 16 * sizeof(float) + 16 +
                       kOpWindow * sizeof(PlanOpDev);
   *fits = smem <= kSmemBudget;
@@ -1009,7 +979,7 @@ cudaError_t configure_x(Plan& plan, int sm_count, bool* fits) {
   const uint32_t cols = kHasLo ? 2 * plan.m : plan.m;
   // Few columns: several scale groups share one MMA tile (four need whole pairs of chunks);
   // with whole 32-row pairs everywhere, the paired kernel.
-  if (KQ_PLAN_PAIRED && plan.all_even_blocks && cols <= 4) {
+  if (plan.all_even_blocks && cols <= 4) {
     cudaError_t e;
     if (cols <= 2 && plan.all_even_chunks)
       e = f16s ? configure_pair_slots<XT, true, 4>(plan, sm_count, fits) : configure_pair_slots<XT, false, 4>(plan, sm_count, fits);
@@ -1103,8 +1073,19 @@ void plan_destroy(Plan* plan) {
   delete plan;
 }
 
-void plan_add_copy(Plan* plan, bool to_device, void* device, void* host, uint64_t bytes) {
-  (plan->ops.empty() ? plan->before : plan->after).push_back(PlanCopy{to_device, device, host, bytes});
+// Host-to-device copies run before the kernel and device-to-host copies after it, so a write
+// recorded after the first linear or a read recorded before it cannot keep its place in the
+// recorded order: both are refused (the plan then fails to finalize) rather than replayed
+// somewhere else.  Returns an empty string when the copy was recorded.
+const char* plan_add_copy(Plan* plan, bool to_device, void* device, void* host, uint64_t bytes) {
+  if (to_device) {
+    if (!plan->ops.empty()) return "a host write was recorded after a linear; writes must come before the first op";
+    plan->before.push_back(PlanCopy{true, device, host, bytes});
+  } else {
+    if (plan->ops.empty()) return "a host read was recorded before any linear; reads must come after the last op";
+    plan->after.push_back(PlanCopy{false, device, host, bytes});
+  }
+  return "";
 }
 
 // Returns an empty string when the op was recorded, else why the fused kernel cannot run it.
@@ -1159,16 +1140,6 @@ cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why) {
   return e;
 }
 
-#ifdef KQ_PLAN_TRACE
-static unsigned long long* g_trace_dev = nullptr;
-static uint32_t g_trace_ops = 0;
-extern "C" __attribute__((visibility("default"))) int kq_debug_plan_trace(unsigned long long* out, uint32_t* ops) {
-  cudaDeviceSynchronize();
-  *ops = g_trace_ops;
-  return cudaMemcpy(out, g_trace_dev, 148ull * g_trace_ops * 8 * 8, cudaMemcpyDeviceToHost);
-}
-#endif
-
 cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
   cudaError_t e = cudaSuccess;
   for (const PlanCopy& c : plan->before) {
@@ -1183,15 +1154,7 @@ cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
   p.m = plan->m;
   p.xs_bytes = plan->xs_bytes;
   p.grid_bar = plan->grid_bar;
-  p.error_flag = env.error_flag;
   p.status = plan->status_dev;
-#ifdef KQ_PLAN_TRACE
-  static unsigned long long* trace_dev = nullptr;
-  if (!trace_dev) cudaMalloc(reinterpret_cast<void**>(&trace_dev), 148ull * 256 * 8 * 8);
-  p.trace = trace_dev;
-  g_trace_dev = trace_dev;
-  g_trace_ops = p.op_count;
-#endif
   void* args[] = {&p};
   e = cudaLaunchCooperativeKernel(plan->kernel, dim3(plan->grid), dim3(kPlanWarps * 32), args, plan->smem, env.stream);
   if (e != cudaSuccess) return e;
@@ -1288,12 +1251,7 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
   p.m = m;
   p.xs_bytes = cfg.xs_bytes;
   p.grid_bar = reinterpret_cast<unsigned int*>(base + kStaticBarOff);
-  p.error_flag = env.error_flag;
   p.status = reinterpret_cast<int*>(base + kStaticStatusOff);
-#ifdef KQ_PLAN_TRACE
-  if (!g_trace_dev) cudaMalloc(reinterpret_cast<void**>(&g_trace_dev), 148ull * 256 * 8 * 8);
-  p.trace = g_trace_dev;
-#endif
   void* args[] = {&p};
   e = cudaLaunchCooperativeKernel(cfg.kernel, dim3(cfg.grid), dim3(kPlanWarps * 32), args, cfg.smem, env.stream);
   if (e != cudaSuccess) return e;

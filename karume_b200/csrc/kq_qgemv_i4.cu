@@ -21,7 +21,8 @@
 //   * the activations are the B operand.  They are staged once per CTA in shared
 //     memory as binary16 in the k-order the nibble pairs come out in, so one 128-bit
 //     shared load feeds two MMAs and is reused by both row blocks of the warp.  f32 and
-//     bf16 activations are split as x = hi + lo (binary16 each, ~2^-25 absolute) and
+//     bf16 activations are split as x = hi + lo (binary16 each, after the power-of-two
+//     pre-scale of their group: ~2^-22 of the value) and
 //     the two parts sit in ADJACENT columns of the same MMA tile, so the extra
 //     precision costs no extra MMA: the lane that owns column pair (2t, 2t+1) adds the
 //     two partial sums;
@@ -40,8 +41,10 @@
 //   * griddepcontrol lets the next launch start streaming its weights while this one
 //     drains; nothing that depends on the previous kernel is touched before the wait.
 //
-// Activation domain: finite |x| <= 65504 (binary16 range).  Larger finite values raise
-// the context's range flag, reported by the next kq_sync as KQ_ERR_RANGE.
+// Activation domain: any f32 / binary16 / bfloat16 value.  Every 32-k group of an activation
+// row (every whole row in the wide kernel) is pre-scaled by an exact power of two before it is
+// split into binary16 parts, and the inverse is applied to the group's partial sum in f32
+// (kq_gemv_core.cuh: pow2_prescale), so the result does not depend on the magnitude of x.
 #include <algorithm>
 #include <type_traits>
 
@@ -52,40 +55,9 @@ namespace kq {
 namespace {
 
 constexpr int kWarps = 4;                // warps per CTA
-#ifndef KQ_TUNE_DEPTH
-#define KQ_TUNE_DEPTH 4
-#endif
-#ifndef KQ_TUNE_WANT
-#define KQ_TUNE_WANT 4
-#endif
-#ifndef KQ_TUNE_WIDE
-#define KQ_TUNE_WIDE 1
-#endif
-#ifndef KQ_TUNE_GP_DEEP
-#define KQ_TUNE_GP_DEEP 1
-#endif
-#ifndef KQ_TUNE_WIDE_SLAB
-#define KQ_TUNE_WIDE_SLAB 16384u
-#endif
-#ifndef KQ_TUNE_PRESTAGE
-#define KQ_TUNE_PRESTAGE 1
-#endif
-#ifndef KQ_TUNE_RB8
-#define KQ_TUNE_RB8 1
-#endif
-#ifndef KQ_TUNE_RB16
-#define KQ_TUNE_RB16 2
-#endif
-#ifndef KQ_TUNE_RB32
-#define KQ_TUNE_RB32 2
-#endif
-#ifndef KQ_TUNE_GP
-#define KQ_TUNE_GP 1
-#endif
-#ifndef KQ_TUNE_LATE_TRIGGER
-#define KQ_TUNE_LATE_TRIGGER 0
-#endif
-constexpr int kDepth = KQ_TUNE_DEPTH;    // chunks in flight per row block, in registers
+constexpr int kDepth = 4;                // chunks in flight per row block, in registers
+constexpr uint32_t kWantCtasPerSm = 4;   // K is split over a cluster until the grid offers this many CTAs per SM
+constexpr uint32_t kWideSlabBytes = 16384;  // staged activations per column tile the wide kernel holds at a time
 constexpr int kMaxCluster = 8;           // portable cluster size: K splits per row tile
 
 struct GemvParams {
@@ -100,11 +72,11 @@ struct GemvParams {
   uint32_t chunks_per_split;
   uint32_t splits;
   uint32_t slab_chunks;  // chunks of x staged in shared memory at a time
-  int* error_flag;
   // Activations already converted to the staged layout by stage_x_global_kernel (wide kernel
   // only; null: every CTA converts its own slab).
   const uint8_t* staged_xs;
   const float* staged_corr;
+  const float* staged_inv;  // [m]: 2^-e of every activation row (wide kernel)
   // Non-null: a row-parallel shard; the outputs are added across ranks in the epilogue.
   const FusedCommDev* fcomm;
 };
@@ -167,6 +139,20 @@ __device__ __forceinline__ void cluster_reduce_store(const GemvParams& p, float*
 
 constexpr uint32_t kFusedSpinLimit = 1u << 22;
 
+// One exchange entry = {value, epoch} in ONE aligned 64-bit word, written and polled with
+// scalar 64-bit accesses: those are single-copy atomic, so a reader that sees the new epoch
+// also sees the value that was stored with it (a two-word vector access gives no such
+// guarantee).  Relaxed, system scope: the entry carries its own flag, nothing else is ordered.
+__device__ __forceinline__ void st_entry(uint2* p, float value, unsigned int epoch) {
+  const unsigned long long word = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(value);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(word) : "memory");
+}
+__device__ __forceinline__ uint2 ld_entry(const uint2* p) {
+  unsigned long long word;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(p) : "memory");
+  return make_uint2(static_cast<uint32_t>(word), static_cast<uint32_t>(word >> 32));
+}
+
 // Row-parallel shard: the tile's outputs (partial sums over this rank's k range, in `red`,
 // possibly spread over the CTAs of a cluster) are added across ranks here, CTA by CTA:
 //   1. every thread finishes its few outputs and PUSHES each into every peer's exchange area
@@ -217,7 +203,7 @@ __device__ __forceinline__ void reduce_exchange_store(const GemvParams& p, float
     if (r == me) continue;
     uint2* dst = reinterpret_cast<uint2*>(fc.base[r] + fc.data_off) + (static_cast<uint64_t>(parity) * kFusedMaxWorld + me) * slot_entries;
     for (int i = 0; i < cnt; ++i)
-      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + off[i]), "r"(__float_as_uint(v[i])), "r"(epoch) : "memory");
+      st_entry(dst + off[i], v[i], epoch);
   }
   for (int i = 0; i < cnt; ++i) {
     float sum = 0.0f;
@@ -231,7 +217,7 @@ __device__ __forceinline__ void reduce_exchange_store(const GemvParams& p, float
       uint2 e;
       uint32_t spins = 0;
       while (true) {
-        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "l"(src) : "memory");
+        e = ld_entry(src);
         if (e.y == epoch) break;
         if (++spins > kFusedSpinLimit) {
           *reinterpret_cast<volatile int*>(fc.status) = 1;
@@ -276,7 +262,7 @@ qgemv_i4_kernel(const GemvParams p) {
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
 
-  if (!KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
+  pdl_launch_dependents();
 
   // which weight of the launch this CTA's row tile belongs to
   uint32_t wi = 0;
@@ -352,7 +338,7 @@ qgemv_i4_kernel(const GemvParams p) {
   // B fragments and "-8 sum x" terms live in registers that only lanes with a real
   // column / activation row ever load into; everybody else keeps the initial zeros.
   uint4 bfrag[kTiles];
-  float cterm[kTiles][kCorrPerTile];
+  float cterm[kTiles][kCorrPerTile], cinv[kTiles][kCorrPerTile];  // {-8 sum x, 2^-e} of the lane's activation rows
   bool load_b[kTiles], load_c[kTiles][kCorrPerTile];
 #pragma unroll
   for (int tile_m = 0; tile_m < kTiles; ++tile_m) {
@@ -361,12 +347,13 @@ qgemv_i4_kernel(const GemvParams p) {
 #pragma unroll
     for (int j = 0; j < kCorrPerTile; ++j) {
       cterm[tile_m][j] = 0.0f;
+      cinv[tile_m][j] = 0.0f;
       const uint32_t mm = kHasLo ? tile_m * 4 + t : tile_m * 8 + 2 * t + j;
       load_c[tile_m][j] = mm < p.m;
     }
   }
   const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
-  const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) + (kHasLo ? t : 2 * t) * 4;
+  const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) + (kHasLo ? t : 2 * t) * 8;
 
   // One chunk (64 k = two scale groups) of every row block of the warp, out of ring
   // slot d; then the slot is refilled with the chunk kDepth further on.
@@ -378,7 +365,7 @@ qgemv_i4_kernel(const GemvParams p) {
         lds_v4_if(bfrag[tile_m], xs_addr + jj * xs_stride + tile_m * 512, load_b[tile_m]);
 #pragma unroll
         for (int j = 0; j < kCorrPerTile; ++j)
-          lds_f32_if(cterm[tile_m][j], corr_addr + (jj * kCorrStride + tile_m * (kHasLo ? 4 : 8) + j) * 4,
+          lds_v2f_if(cterm[tile_m][j], cinv[tile_m][j], corr_addr + (jj * kCorrStride + tile_m * (kHasLo ? 4 : 8) + j) * 8,
                      load_c[tile_m][j]);
       }
 #pragma unroll
@@ -401,13 +388,13 @@ qgemv_i4_kernel(const GemvParams p) {
           mma_f16_zero(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y);
           mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
           if constexpr (kHasLo) {
-            acc[r][tile_m][0] = fmaf(s.x, (cf[0] + cf[1]) + cterm[tile_m][0], acc[r][tile_m][0]);
-            acc[r][tile_m][1] = fmaf(s.y, (cf[2] + cf[3]) + cterm[tile_m][0], acc[r][tile_m][1]);
+            acc[r][tile_m][0] = fmaf(s.x, ((cf[0] + cf[1]) + cterm[tile_m][0]) * cinv[tile_m][0], acc[r][tile_m][0]);
+            acc[r][tile_m][1] = fmaf(s.y, ((cf[2] + cf[3]) + cterm[tile_m][0]) * cinv[tile_m][0], acc[r][tile_m][1]);
           } else {
-            acc[r][tile_m][0] = fmaf(s.x, cf[0] + cterm[tile_m][0], acc[r][tile_m][0]);
-            acc[r][tile_m][1] = fmaf(s.x, cf[1] + cterm[tile_m][1], acc[r][tile_m][1]);
-            acc[r][tile_m][2] = fmaf(s.y, cf[2] + cterm[tile_m][0], acc[r][tile_m][2]);
-            acc[r][tile_m][3] = fmaf(s.y, cf[3] + cterm[tile_m][1], acc[r][tile_m][3]);
+            acc[r][tile_m][0] = fmaf(s.x, (cf[0] + cterm[tile_m][0]) * cinv[tile_m][0], acc[r][tile_m][0]);
+            acc[r][tile_m][1] = fmaf(s.x, (cf[1] + cterm[tile_m][1]) * cinv[tile_m][1], acc[r][tile_m][1]);
+            acc[r][tile_m][2] = fmaf(s.y, (cf[2] + cterm[tile_m][0]) * cinv[tile_m][0], acc[r][tile_m][2]);
+            acc[r][tile_m][3] = fmaf(s.y, (cf[3] + cterm[tile_m][1]) * cinv[tile_m][1], acc[r][tile_m][3]);
           }
         }
       }
@@ -422,8 +409,7 @@ qgemv_i4_kernel(const GemvParams p) {
   for (uint32_t done = 0; done < nch;) {
     const uint32_t slab_n = min(p.slab_chunks, nch - done);
     if (done != 0) __syncthreads();  // everyone is done reading the previous slab
-    stage_x<XT, kHasLo, kCorrStride>(x, p.m, p.k, 2 * (cbeg + done), 2 * slab_n, xs, xs_stride, corr,
-                                     p.error_flag);
+    stage_x<XT, kHasLo, kCorrStride>(x, p.m, p.k, 2 * (cbeg + done), 2 * slab_n, xs, xs_stride, corr);
     __syncthreads();
     uint32_t xs_addr = xs_lane, corr_addr = corr_lane;
     uint32_t i = 0;
@@ -432,7 +418,7 @@ qgemv_i4_kernel(const GemvParams p) {
       for (int d = 0; d < kDepth; ++d) {
         process(d, xs_addr, corr_addr, done + i + d + kDepth < nch);
         xs_addr += 2 * xs_stride;
-        corr_addr += 2 * kCorrStride * 4;
+        corr_addr += 2 * kCorrStride * 8;
       }
 #pragma unroll
       for (int r = 0; r < kRB; ++r) next[r] += kDepth * kCB;
@@ -442,13 +428,11 @@ qgemv_i4_kernel(const GemvParams p) {
       if (i + d < slab_n) {
         process(d, xs_addr, corr_addr, false);
         xs_addr += 2 * xs_stride;
-        corr_addr += 2 * kCorrStride * 4;
+        corr_addr += 2 * kCorrStride * 8;
       }
     }
     done += slab_n;
   }
-
-  if (KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
 
   // ---- epilogue -----------------------------------------------------------------
   // lane owns, per row block and tile: rows g and g+8 of the block and activation rows
@@ -527,7 +511,7 @@ qgemv_i4_gp_kernel(const GemvParams p) {
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
 
-  if (!KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
+  pdl_launch_dependents();
 
   uint32_t wi = 0;
 #pragma unroll
@@ -601,22 +585,23 @@ qgemv_i4_gp_kernel(const GemvParams p) {
     bset[j] = make_uint4(0, 0, 0, 0);
     load_b[j] = col_live && jb == static_cast<uint32_t>(j);
   }
-  float cterm[kCorr];
+  float cterm[kCorr], cinv[kCorr];  // {-8 sum x, 2^-e} of the lane's own group and activation rows
   bool load_c[kCorr];
 #pragma unroll
   for (int j = 0; j < kCorr; ++j) {
     cterm[j] = 0.0f;
+    cinv[j] = 0.0f;
     load_c[j] = (kHasLo ? tl : 2 * tl + j) < p.m;
   }
   const uint32_t xs_lane = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + lane * 16;
   const uint32_t corr_lane = static_cast<uint32_t>(__cvta_generic_to_shared(corr)) +
-                             (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 4;
+                             (jl * kCorrStride + (kHasLo ? tl : 2 * tl)) * 8;
 
   auto process = [&](const int u, uint32_t xs_addr, uint32_t corr_addr, bool refill) {
 #pragma unroll
     for (int j = 0; j < kG; ++j) lds_v4_if(bset[j], xs_addr, load_b[j]);
 #pragma unroll
-    for (int j = 0; j < kCorr; ++j) lds_f32_if(cterm[j], corr_addr + j * 4, load_c[j]);
+    for (int j = 0; j < kCorr; ++j) lds_v2f_if(cterm[j], cinv[j], corr_addr + j * 8, load_c[j]);
     float cf[4];
 #pragma unroll
     for (int j = 0; j < kG; ++j) {
@@ -634,13 +619,13 @@ qgemv_i4_gp_kernel(const GemvParams p) {
     if constexpr (kScaleF16) s = __half22float2(*reinterpret_cast<const __half2*>(&ring_s[u].v));
     else s = make_float2(__uint_as_float(ring_s[u].v.x), __uint_as_float(ring_s[u].v.y));
     if constexpr (kHasLo) {
-      acc[0] = fmaf(s.x, (cf[0] + cf[1]) + cterm[0], acc[0]);
-      acc[1] = fmaf(s.y, (cf[2] + cf[3]) + cterm[0], acc[1]);
+      acc[0] = fmaf(s.x, ((cf[0] + cf[1]) + cterm[0]) * cinv[0], acc[0]);
+      acc[1] = fmaf(s.y, ((cf[2] + cf[3]) + cterm[0]) * cinv[0], acc[1]);
     } else {
-      acc[0] = fmaf(s.x, cf[0] + cterm[0], acc[0]);
-      acc[1] = fmaf(s.x, cf[1] + cterm[1], acc[1]);
-      acc[2] = fmaf(s.y, cf[2] + cterm[0], acc[2]);
-      acc[3] = fmaf(s.y, cf[3] + cterm[1], acc[3]);
+      acc[0] = fmaf(s.x, (cf[0] + cterm[0]) * cinv[0], acc[0]);
+      acc[1] = fmaf(s.x, (cf[1] + cterm[1]) * cinv[1], acc[1]);
+      acc[2] = fmaf(s.y, (cf[2] + cterm[0]) * cinv[0], acc[2]);
+      acc[3] = fmaf(s.y, (cf[3] + cterm[1]) * cinv[1], acc[3]);
     }
     if (refill && active) fetch(u, next + u * (kCU * kCB));
   };
@@ -649,7 +634,7 @@ qgemv_i4_gp_kernel(const GemvParams p) {
   for (uint32_t done = 0; done < nch;) {
     const uint32_t slab_n = min(p.slab_chunks, nch - done);
     if (done != 0) __syncthreads();
-    stage_x<XT, kHasLo, kCorrStride>(x, p.m, p.k, 2 * (cbeg + done), 2 * slab_n, xs, kXsStride, corr, p.error_flag);
+    stage_x<XT, kHasLo, kCorrStride>(x, p.m, p.k, 2 * (cbeg + done), 2 * slab_n, xs, kXsStride, corr);
     __syncthreads();
     uint32_t xs_addr = xs_lane, corr_addr = corr_lane;
     uint32_t i = 0;
@@ -658,7 +643,7 @@ qgemv_i4_gp_kernel(const GemvParams p) {
       for (int u = 0; u < kUnits; ++u) {
         process(u, xs_addr, corr_addr, done + i + u * kCU + kD < nch);
         xs_addr += 512;
-        corr_addr += kG * kCorrStride * 4;
+        corr_addr += kG * kCorrStride * 8;
       }
       next += kD * kCB;
     }
@@ -667,13 +652,11 @@ qgemv_i4_gp_kernel(const GemvParams p) {
       if (i + u * kCU < slab_n) {
         process(u, xs_addr, corr_addr, false);
         xs_addr += 512;
-        corr_addr += kG * kCorrStride * 4;
+        corr_addr += kG * kCorrStride * 8;
       }
     }
     done += slab_n;
   }
-
-  if (KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
 
   // ---- epilogue: lanes whose C columns belong to different groups hold partial sums of the
   // same outputs; add them (fixed order), then the lanes of group 0 own the result.
@@ -714,7 +697,7 @@ qgemv_i4_gp_kernel(const GemvParams p) {
 template <typename XT, int kCols>
 uint32_t group_smem_bytes(uint32_t m) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
-  return (kHasLo ? 2 * m : m) * 64 + (kHasLo ? kCols / 2 : kCols) * 4;
+  return (kHasLo ? 2 * m : m) * 64 + (kHasLo ? kCols / 2 : kCols) * 8;  // staged halves + {corr, 2^-e} pairs
 }
 
 template <typename XT, bool kScaleF16, int kCols, int kRB>
@@ -738,7 +721,7 @@ cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const L
 
   // Split K over a cluster until the grid fills the machine (about four CTAs per SM);
   // a pure function of the shape, never autotuned.
-  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * KQ_TUNE_WANT;
+  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * kWantCtasPerSm;
   uint32_t splits = 1;
   while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas &&
          splits * 2 <= chunks_per_row)
@@ -778,6 +761,48 @@ cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const L
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
+// How many CTAs of a launch configuration fit on the device at the same time (0 when the
+// query fails, which callers treat as "does not fit").  The decision the fused exchange
+// depends on: its CTAs wait for their twins on the other GPUs, so the whole grid has to be
+// resident in one wave.
+struct ResidencyKey {
+  const void* kernel;
+  int device;
+  size_t smem;
+  uint32_t splits;
+  uint32_t ctas;
+};
+uint32_t resident_ctas(const void* kernel, int device, const cudaLaunchConfig_t& cfg, uint32_t splits, int sm_count) {
+  static ResidencyKey cache[64];
+  static int cached = 0;
+  for (int i = 0; i < cached; ++i)
+    if (cache[i].kernel == kernel && cache[i].device == device && cache[i].smem == cfg.dynamicSmemBytes &&
+        cache[i].splits == splits)
+      return cache[i].ctas;
+  uint32_t ctas = 0;
+  if (splits > 1) {
+    cudaLaunchConfig_t probe = cfg;
+    cudaLaunchAttribute cluster;
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = 1;
+    cluster.val.clusterDim.y = splits;
+    cluster.val.clusterDim.z = 1;
+    probe.attrs = &cluster;
+    probe.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &probe) == cudaSuccess && clusters > 0)
+      ctas = static_cast<uint32_t>(clusters) * splits;
+  } else {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, static_cast<int>(cfg.blockDim.x),
+                                                      cfg.dynamicSmemBytes) == cudaSuccess && per_sm > 0)
+      ctas = static_cast<uint32_t>(per_sm) * static_cast<uint32_t>(sm_count);
+  }
+  (void)cudaGetLastError();
+  if (cached < 64) cache[cached++] = ResidencyKey{kernel, device, cfg.dynamicSmemBytes, splits, ctas};
+  return ctas;
+}
+
 template <typename XT, bool kScaleF16, int kG, int kD>
 cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets,
                                   bool probe_only, uint32_t* ctas_out, uint32_t* capacity_out) {
@@ -800,31 +825,19 @@ cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count
   for (int i = count; i <= kMaxMulti; ++i) p.tile_begin[i] = tiles;
 
   const uint32_t units_per_row = p.k / kChunkK / kCU;  // the caller checked divisibility
-  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * KQ_TUNE_WANT;
+  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * kWantCtasPerSm;
   uint32_t splits = 1;
   while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas && splits * 2 <= units_per_row)
     splits *= 2;
   p.splits = splits;
   p.chunks_per_split = (units_per_row + splits - 1) / splits * kCU;
-  const uint32_t per_chunk = 2 * (kCpg * 64 + kCorrStride * 4);
+  const uint32_t per_chunk = 2 * (kCpg * 64 + kCorrStride * 8);
   const uint32_t slab_cap = std::max<uint32_t>(kD, (32768u / per_chunk) / kD * kD);
   p.slab_chunks = std::max<uint32_t>(kCU, std::min(p.chunks_per_split, slab_cap));
 
   const size_t slab_bytes = static_cast<size_t>(p.slab_chunks) * per_chunk;
   p.fcomm = env.fused;
   const size_t red_bytes = (splits > 1 || env.fused != nullptr) ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
-
-  if (ctas_out) *ctas_out = tiles * splits;
-  if (capacity_out) {
-    static int per_sm = -1;  // with the shared memory of a typical launch; registers decide
-    if (per_sm < 0) {
-      int v = 0;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, kWarps * 32, 16 * 1024) != cudaSuccess) v = 0;
-      per_sm = v;
-    }
-    *capacity_out = static_cast<uint32_t>(per_sm) * static_cast<uint32_t>(env.sm_count);
-  }
-  if (probe_only) return cudaSuccess;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles, splits, 1);
@@ -845,6 +858,17 @@ cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count
     attr[na].val.clusterDim.z = 1;
     ++na;
   }
+  if (ctas_out) *ctas_out = tiles * splits;
+  if (capacity_out) {
+    // CTAs of THIS launch that can be resident at once: asked with the launch's own dynamic
+    // shared memory and, when K is split, its cluster shape (clusters co-schedule fewer CTAs
+    // than the per-SM limit suggests).  Cached per (device, shared memory, splits).
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    *capacity_out = resident_ctas(reinterpret_cast<const void*>(kernel), device, cfg, splits, env.sm_count);
+  }
+  if (probe_only) return cudaSuccess;
   cfg.attrs = attr;
   cfg.numAttrs = na;
   return cudaLaunchKernelEx(&cfg, kernel, p);
@@ -862,7 +886,7 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
   if (env.fused != nullptr && (count != 1 || ctas > kFusedMaxCtas ||
                                static_cast<uint64_t>(p.m) * targets[0].w->n * 8u > kFusedSlotBytes))
     return cudaErrorNotSupported;
-  if (KQ_TUNE_GP_DEEP && ctas <= capacity)
+  if (ctas <= capacity)
     return launch_typed_gp_depth<XT, kScaleF16, kG, 2 * kDepth>(env, p, count, targets, false, nullptr, nullptr);
   if (env.fused != nullptr) {
     e = launch_typed_gp_depth<XT, kScaleF16, kG, kDepth>(env, p, count, targets, true, &ctas, &capacity);
@@ -875,9 +899,37 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
 // Converts the whole activation block to the staged layout ONCE per launch, into global
 // scratch.  With many activation rows the conversion is as much work as a CTA's share of the
 // matmul, and every CTA would repeat it for its k range; this way a CTA only copies bytes.
+// The wide kernel pre-scales each activation ROW by one power of two (a per-group factor would
+// have to multiply every C value of every group; a per-row one leaves the inner loop alone and
+// is applied once in the epilogue).  One CTA per activation row: largest magnitude of the row,
+// then scale[row] = 2^e and inv[row] = 2^-e (kq_gemv_core.cuh: pow2_prescale).
+template <typename XT>
+__global__ void __launch_bounds__(256)
+row_scale_kernel(const XT* __restrict__ x, uint32_t k, float* scale, float* inv) {
+  const XT* row = x + static_cast<size_t>(blockIdx.x) * k;
+  float amax = 0.0f;
+  for (uint32_t i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {  // k is a multiple of 64
+    float v[8];
+    load_x8<XT>(row + i, v);
+    amax = fmaxf(amax, absmax8(v));
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+  __shared__ float part[8];
+  if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, part[w]);
+    const Pow2 ps = pow2_prescale(amax);
+    scale[blockIdx.x] = ps.scale;
+    inv[blockIdx.x] = ps.inv;
+  }
+}
+
 template <typename XT, int kTiles>
 __global__ void __launch_bounds__(256)
-stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t* xs, float* corr, int* error_flag) {
+stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t* xs, float* corr,
+                      const float* __restrict__ row_scale) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kLoOffset = kTiles * 512u;
   constexpr uint32_t kXsStride = kLoOffset * (kHasLo ? 2u : 1u);
@@ -886,9 +938,9 @@ stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t*
   const uint32_t group0 = blockIdx.x * kGroupsPerCta;
   if (group0 >= groups) return;
   const uint32_t ng = min(kGroupsPerCta, groups - group0);
-  stage_x<XT, kHasLo, kTiles * 8>(x, m, k, group0, ng, xs + static_cast<size_t>(group0) * kXsStride, kXsStride,
-                                  corr + static_cast<size_t>(group0) * (kTiles * 8), error_flag,
-                                  kHasLo ? kLoOffset : 0u);
+  stage_x<XT, kHasLo, kTiles * 8, false, 1, false>(x, m, k, group0, ng, xs + static_cast<size_t>(group0) * kXsStride,
+                                                   kXsStride, corr + static_cast<size_t>(group0) * (kTiles * 8),
+                                                   kHasLo ? kLoOffset : 0u, row_scale);
 }
 
 // ---- wide variant: more than 4 MMA columns (3 to 16 activation rows) -------------------
@@ -912,7 +964,7 @@ qgemv_i4_wide_kernel(const GemvParams p) {
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
 
-  if (!KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
+  pdl_launch_dependents();
 
   uint32_t wi = 0;
 #pragma unroll
@@ -976,7 +1028,6 @@ qgemv_i4_wide_kernel(const GemvParams p) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[r][i][j] = 0.0f;
 
-  const XT* x = static_cast<const XT*>(p.x);
   constexpr uint32_t kMask0 = 0x000F000Fu, kMask1 = 0x00F000F0u;
 
   uint4 bhi[kTiles], blo[kTiles];
@@ -1047,7 +1098,7 @@ qgemv_i4_wide_kernel(const GemvParams p) {
   for (uint32_t done = 0; done < nch;) {
     const uint32_t slab_n = min(p.slab_chunks, nch - done);
     if (done != 0) __syncthreads();
-    if (p.staged_xs != nullptr) {
+    {  // the activations were converted once per launch by stage_x_global_kernel: copy bytes
       const uint32_t first_group = 2 * (cbeg + done);
       const uint4* src = reinterpret_cast<const uint4*>(p.staged_xs + static_cast<size_t>(first_group) * kXsStride);
       uint4* dst = reinterpret_cast<uint4*>(xs);
@@ -1057,9 +1108,6 @@ qgemv_i4_wide_kernel(const GemvParams p) {
       float4* cdst = reinterpret_cast<float4*>(corr);
       const uint32_t c16 = 2 * slab_n * (kCols / 4);
       for (uint32_t i = threadIdx.x; i < c16; i += blockDim.x) cdst[i] = __ldg(csrc + i);
-    } else {
-      stage_x<XT, kHasLo, kCols>(x, p.m, p.k, 2 * (cbeg + done), 2 * slab_n, xs, kXsStride, corr, p.error_flag,
-                                 kHasLo ? kLoOffset : 0u);
     }
     __syncthreads();
     uint32_t xs_addr = xs_lane, corr_addr = corr_lane;
@@ -1085,8 +1133,6 @@ qgemv_i4_wide_kernel(const GemvParams p) {
     done += slab_n;
   }
 
-  if (KQ_TUNE_LATE_TRIGGER) pdl_launch_dependents();
-
   // lane owns rows g, g+8 of each block and activation rows 8 tile + 2t, 2t+1
   float* red = reinterpret_cast<float*>(smem);
   if (p.splits > 1) __syncthreads();
@@ -1106,7 +1152,8 @@ qgemv_i4_wide_kernel(const GemvParams p) {
       for (int j = 0; j < 2; ++j) {
         const uint32_t mm = tile_m * 8 + 2 * t + j;
         if (mm >= p.m) continue;
-        const float va = acc[r][tile_m][j], vb = acc[r][tile_m][2 + j];
+        const float inv = __ldg(p.staged_inv + mm);  // undo the row's power-of-two pre-scale (exact)
+        const float va = acc[r][tile_m][j] * inv, vb = acc[r][tile_m][2 + j] * inv;
         if (p.splits == 1) {
           out[static_cast<size_t>(mm) * n + row_a] = fmaf(va, kUnscale, bias_a);
           out[static_cast<size_t>(mm) * n + row_a + 8] = fmaf(vb, kUnscale, bias_b);
@@ -1140,33 +1187,39 @@ cudaError_t launch_typed_wide(const LaunchEnv& env, GemvParams& p, int count, co
   }
   for (int i = count; i <= kMaxMulti; ++i) p.tile_begin[i] = tiles;
   const uint32_t chunks_per_row = p.k / kChunkK;
-  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * KQ_TUNE_WANT;
+  const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * kWantCtasPerSm;
   uint32_t splits = 1;
   while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas && splits * 2 <= chunks_per_row)
     splits *= 2;
   p.splits = splits;
   p.chunks_per_split = (chunks_per_row + splits - 1) / splits;
   const uint32_t per_chunk = 2 * (kTiles * 512u * (kHasLo ? 2u : 1u) + kTiles * 8u * 4u);
-  const uint32_t slab_cap = std::max<uint32_t>(kD, (KQ_TUNE_WIDE_SLAB * kTiles / per_chunk) / kD * kD);
+  const uint32_t slab_cap = std::max<uint32_t>(kD, (kWideSlabBytes * kTiles / per_chunk) / kD * kD);
   p.slab_chunks = std::max<uint32_t>(1u, std::min(p.chunks_per_split, slab_cap));
   const size_t slab_bytes = static_cast<size_t>(p.slab_chunks) * per_chunk;
   const size_t red_bytes = splits > 1 ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
 
-  // Convert the activations once, into the context's scratch, when it is large enough.
+  // Convert the activations once per launch, into the context's scratch: the row scales first
+  // (one CTA per activation row), then the staged halves and the "-8 sum x" terms.
   const uint32_t groups = p.k / 32;
   const size_t xs_total = static_cast<size_t>(groups) * (kTiles * 512u * (kHasLo ? 2u : 1u));
   const size_t corr_total = static_cast<size_t>(groups) * kTiles * 8u * sizeof(float);
-  p.staged_xs = nullptr;
-  p.staged_corr = nullptr;
-  if (KQ_TUNE_PRESTAGE && env.workspace != nullptr && xs_total + corr_total <= env.workspace_bytes) {
+  const size_t scale_total = 2 * 16 * sizeof(float);
+  if (env.workspace == nullptr || xs_total + corr_total + scale_total > env.workspace_bytes)
+    return cudaErrorMemoryAllocation;  // the context's workspace is too small for this k
+  {
     uint8_t* ws = static_cast<uint8_t*>(env.workspace);
+    float* corr_ws = reinterpret_cast<float*>(ws + xs_total);
+    float* scale_ws = reinterpret_cast<float*>(ws + xs_total + corr_total);
+    row_scale_kernel<XT><<<p.m, 256, 0, env.stream>>>(static_cast<const XT*>(p.x), p.k, scale_ws, scale_ws + 16);
     stage_x_global_kernel<XT, kTiles><<<(groups + 7) / 8, 256, 0, env.stream>>>(
-        static_cast<const XT*>(p.x), p.m, p.k, ws, reinterpret_cast<float*>(ws + xs_total), p.error_flag);
+        static_cast<const XT*>(p.x), p.m, p.k, ws, corr_ws, scale_ws);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     p.staged_xs = ws;
-    p.staged_corr = reinterpret_cast<const float*>(ws + xs_total);
-    if (extra_launches) *extra_launches += 1;
+    p.staged_corr = corr_ws;
+    p.staged_inv = scale_ws + 16;
+    if (extra_launches) *extra_launches += 2;
   }
 
   cudaLaunchConfig_t cfg = {};
@@ -1203,42 +1256,33 @@ cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const Linea
   const uint32_t cols = kHasLo ? 2 * p.m : p.m;
   // Few columns: pack several scale groups into one MMA tile (four groups need an even
   // number of 64-k chunks per row).
-  if (KQ_TUNE_GP && cols <= 2 && (p.k / kChunkK) % 2 == 0)
+  if (cols <= 2 && (p.k / kChunkK) % 2 == 0)
     return f16s ? launch_typed_gp<XT, true, 4>(env, p, count, t) : launch_typed_gp<XT, false, 4>(env, p, count, t);
-  if (KQ_TUNE_GP && cols <= 4)
+  if (cols <= 4)
     return f16s ? launch_typed_gp<XT, true, 2>(env, p, count, t) : launch_typed_gp<XT, false, 2>(env, p, count, t);
   if (env.fused != nullptr) return cudaErrorNotSupported;  // only the group-packed kernel exchanges in its epilogue
-  if (KQ_TUNE_WIDE && !(kHasLo && p.m <= 4)) {
-    // Two row blocks per warp (sharing the activation loads) pay off when a row block costs
-    // many MMAs (hi + lo parts, or two column tiles) and the matrix has rows to spare;
-    // otherwise one row block per warp and a deeper ring keep more CTAs in flight.  A pure
-    // function of the shape.
-    uint32_t row_blocks = 0;
-    for (int i = 0; i < count; ++i) row_blocks += t[i].w->n / 16;
-    const bool heavy = kHasLo || p.m > 8;
-    const bool pair = heavy && row_blocks >= 1024;
-    if (p.m <= 8) {
-      if (pair)
-        return f16s ? launch_typed_wide<XT, true, 1, 2, 2>(env, p, count, t, extra)
-                    : launch_typed_wide<XT, false, 1, 2, 2>(env, p, count, t, extra);
-      return f16s ? launch_typed_wide<XT, true, 1, 1, 4>(env, p, count, t, extra)
-                  : launch_typed_wide<XT, false, 1, 1, 4>(env, p, count, t, extra);
-    }
+  if (kHasLo && p.m <= 4)  // three or four f32 / bf16 rows: hi and lo in adjacent columns of one tile
+    return f16s ? launch_typed<XT, true, 8, 1>(env, p, count, t) : launch_typed<XT, false, 8, 1>(env, p, count, t);
+  // Five or more rows.  Two row blocks per warp (sharing the activation loads) pay off when a
+  // row block costs many MMAs (hi + lo parts, or two column tiles) and the matrix has rows to
+  // spare; otherwise one row block per warp and a deeper ring keep more CTAs in flight.  A pure
+  // function of the shape.
+  uint32_t row_blocks = 0;
+  for (int i = 0; i < count; ++i) row_blocks += t[i].w->n / 16;
+  const bool heavy = kHasLo || p.m > 8;
+  const bool pair = heavy && row_blocks >= 1024;
+  if (p.m <= 8) {
     if (pair)
-      return f16s ? launch_typed_wide<XT, true, 2, 2, 2>(env, p, count, t, extra)
-                  : launch_typed_wide<XT, false, 2, 2, 2>(env, p, count, t, extra);
-    return f16s ? launch_typed_wide<XT, true, 2, 1, 4>(env, p, count, t, extra)
-                : launch_typed_wide<XT, false, 2, 1, 4>(env, p, count, t, extra);
+      return f16s ? launch_typed_wide<XT, true, 1, 2, 2>(env, p, count, t, extra)
+                  : launch_typed_wide<XT, false, 1, 2, 2>(env, p, count, t, extra);
+    return f16s ? launch_typed_wide<XT, true, 1, 1, 4>(env, p, count, t, extra)
+                : launch_typed_wide<XT, false, 1, 1, 4>(env, p, count, t, extra);
   }
-  if (cols <= 8)
-    return f16s ? launch_typed<XT, true, 8, KQ_TUNE_RB8>(env, p, count, t) : launch_typed<XT, false, 8, KQ_TUNE_RB8>(env, p, count, t);
-  if (cols <= 16)
-    return f16s ? launch_typed<XT, true, 16, KQ_TUNE_RB16>(env, p, count, t) : launch_typed<XT, false, 16, KQ_TUNE_RB16>(env, p, count, t);
-  if constexpr (kHasLo) {
-    return f16s ? launch_typed<XT, true, 32, KQ_TUNE_RB32>(env, p, count, t) : launch_typed<XT, false, 32, KQ_TUNE_RB32>(env, p, count, t);
-  } else {
-    return cudaErrorInvalidValue;
-  }
+  if (pair)
+    return f16s ? launch_typed_wide<XT, true, 2, 2, 2>(env, p, count, t, extra)
+                : launch_typed_wide<XT, false, 2, 2, 2>(env, p, count, t, extra);
+  return f16s ? launch_typed_wide<XT, true, 2, 1, 4>(env, p, count, t, extra)
+              : launch_typed_wide<XT, false, 2, 1, 4>(env, p, count, t, extra);
 }
 
 }  // namespace
@@ -1265,7 +1309,6 @@ cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget*
   p.x = x;
   p.m = m;
   p.k = k;
-  p.error_flag = env.error_flag;
   const bool f16s = scale_dtype == KQ_F16;
   cudaError_t e;
   switch (x_dtype) {

@@ -13,7 +13,10 @@
 //     y[n] = s[n] * ( sum_k b[n,k] x[k]  -  128 sum_k x[k] ) + bias[n].
 // This is the factored form; the bit-exact per-element dequant (one f32 multiply,
 // kq::dequant_i8) is what kq_weight_dequant and the generic kernel use.
-// Activation domain: finite |x| <= 65504, as for the int4 kernel.
+// Activation domain: any value.  Because the MMAs of a row chain over the whole K range, the
+// power-of-two pre-scale of the activations (kq_gemv_core.cuh: pow2_prescale) is chosen per
+// activation ROW, from the largest magnitude inside the CTA's own k range, in a short pass
+// before the first slab is staged; its inverse multiplies the CTA's partial sum once, in f32.
 #include <algorithm>
 #include <type_traits>
 
@@ -36,7 +39,6 @@ struct Gemv8Params {
   const void* x;
   uint32_t m, n, k;
   uint32_t chunks_per_split, splits, slab_chunks;
-  int* error_flag;
 };
 
 __device__ __forceinline__ uint4 ldg_stream_v4_8(const void* p) {
@@ -63,13 +65,13 @@ __device__ __forceinline__ void cluster_sync_all8() {
 //   xs   : [local chunk][active columns][64 B]; inside a column block, 16 B per t = 0..3:
 //          x[4t], x[4t+2], x[4t+1], x[4t+3] of the first 16 k, then the same of the second 16 k
 //   corr : [local chunk][kCorrStride] f32 = sum of the chunk's 32 activations as staged
+//   row_scale : [m] the 2^e every value of an activation row is multiplied by before the split
 template <typename XT, bool kHasLo, int kCorrStride>
 __device__ __forceinline__ void stage_x8(const XT* __restrict__ x, uint32_t m, uint32_t k, uint32_t chunk0,
                                          uint32_t chunks, uint8_t* xs, uint32_t xs_stride, float* corr,
-                                         int* error_flag) {
+                                         const float* row_scale) {
   const uint32_t items = chunks * m * 4;
   const uint32_t items_padded = (items + 31u) & ~31u;
-  bool out_of_range = false;
   for (uint32_t item = threadIdx.x; item < items_padded; item += blockDim.x) {
     const bool valid = item < items;
     const uint32_t t = item & 3u;
@@ -80,17 +82,16 @@ __device__ __forceinline__ void stage_x8(const XT* __restrict__ x, uint32_t m, u
     float sum = 0.0f;
     if (valid) {
       const XT* src = x + static_cast<size_t>(row) * k + (static_cast<size_t>(chunk0 + lc) << 5) + (t << 2);
+      const float scale = row_scale[row];
       float v[8];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        v[e] = to_f32(src[e]);
-        v[4 + e] = to_f32(src[16 + e]);
+        v[e] = to_f32(src[e]) * scale;
+        v[4 + e] = to_f32(src[16 + e]) * scale;
       }
       __half h[8], l[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const float a = fabsf(v[e]);
-        if (a > 65504.0f && a < __int_as_float(0x7f800000)) out_of_range = true;
         h[e] = __float2half_rn(v[e]);
         const float hf = __half2float(h[e]);
         if constexpr (kHasLo) {
@@ -114,7 +115,6 @@ __device__ __forceinline__ void stage_x8(const XT* __restrict__ x, uint32_t m, u
       if (t == 0) corr[lc * kCorrStride + row] = sum;
     }
   }
-  if (out_of_range) *reinterpret_cast<volatile int*>(error_flag) = 1;
 }
 
 template <typename XT, bool kScaleF16, int kCols, int kRB>
@@ -163,6 +163,35 @@ qgemv_i8_kernel(const Gemv8Params p) {
   for (int r = 0; r < kRB; ++r) next[r] += kDepth8 * kCB8;
 
   pdl_wait_prior_grid();
+
+  // Per activation row: largest magnitude inside this CTA's k range -> 2^e and 2^-e.
+  __shared__ float amax_part[kWarps8][16];
+  __shared__ float row_scale[16], row_inv[16];
+  {
+    const XT* xin = static_cast<const XT*>(p.x);
+    const uint32_t k0 = cbeg * kChunkK8, k1 = cend * kChunkK8;
+    for (uint32_t row = 0; row < p.m; ++row) {
+      float amax = 0.0f;
+      for (uint32_t i = k0 + threadIdx.x * 8; i < k1; i += blockDim.x * 8) {
+        float v[8];
+        load_x8<XT>(xin + static_cast<size_t>(row) * p.k + i, v);
+        amax = fmaxf(amax, absmax8(v));
+      }
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+      if (lane == 0) amax_part[warp][row] = amax;
+    }
+    __syncthreads();
+    if (threadIdx.x < p.m) {
+      float amax = amax_part[0][threadIdx.x];
+#pragma unroll
+      for (int w = 1; w < kWarps8; ++w) amax = fmaxf(amax, amax_part[w][threadIdx.x]);
+      const Pow2 ps = pow2_prescale(amax);
+      row_scale[threadIdx.x] = ps.scale;
+      row_inv[threadIdx.x] = ps.inv;
+    }
+    __syncthreads();
+  }
 
   float acc[kRB][kTiles][4];  // MMA accumulators over the whole K range of this CTA
   float csum[kTiles][kCorrPerTile];
@@ -222,7 +251,7 @@ qgemv_i8_kernel(const Gemv8Params p) {
   for (uint32_t done = 0; done < nch;) {
     const uint32_t slab_n = min(p.slab_chunks, nch - done);
     if (done != 0) __syncthreads();
-    stage_x8<XT, kHasLo, kCorrStride>(x, p.m, p.k, cbeg + done, slab_n, xs, xs_stride, corr, p.error_flag);
+    stage_x8<XT, kHasLo, kCorrStride>(x, p.m, p.k, cbeg + done, slab_n, xs, xs_stride, corr, row_scale);
     __syncthreads();
     uint32_t xs_addr = xs_lane, corr_addr = corr_lane;
     uint32_t i = 0;
@@ -271,7 +300,8 @@ qgemv_i8_kernel(const Gemv8Params p) {
         const float ca = kHasLo ? acc[r][tile_m][0] + acc[r][tile_m][1] : acc[r][tile_m][j];
         const float cb = kHasLo ? acc[r][tile_m][2] + acc[r][tile_m][3] : acc[r][tile_m][2 + j];
         const float off = -128.0f * csum[tile_m][kHasLo ? 0 : j];
-        const float va = fmaf(ca, kUnscale, off), vb = fmaf(cb, kUnscale, off);
+        const float inv = row_inv[mm];  // undo the row's power-of-two pre-scale (exact)
+        const float va = fmaf(ca, kUnscale, off) * inv, vb = fmaf(cb, kUnscale, off) * inv;
         if (p.splits == 1) {
           p.out[static_cast<size_t>(mm) * p.n + row_a] = fmaf(s_a, va, bias_a);
           p.out[static_cast<size_t>(mm) * p.n + row_a + 8] = fmaf(s_b, vb, bias_b);
@@ -376,7 +406,6 @@ cudaError_t launch_qgemv_i8(const LaunchEnv& env, const LinearTarget& target, co
   p.m = m;
   p.n = w.n;
   p.k = w.k;
-  p.error_flag = env.error_flag;
   const bool f16s = w.scale_dtype == KQ_F16;
   switch (x_dtype) {
     case KQ_F32: return launch_x8<float>(env, p, f16s);

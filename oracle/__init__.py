@@ -76,6 +76,14 @@ def _declare(l: ctypes.CDLL) -> None:
     l.kqo_linear_w8a8.restype = None
     l.kqo_linear_w4a8.argtypes = [_P, _P, _P, _P, _Z, _Z, _Z, _Z, _P, _P, _P]
     l.kqo_linear_w4a8.restype = None
+    l.kqo_rms_norm.argtypes = [_P, _P, _Z, _Z, ctypes.c_double, _P]
+    l.kqo_rms_norm.restype = None
+    l.kqo_sigmoid.argtypes = [_P, _Z, _P]
+    l.kqo_sigmoid.restype = None
+    l.kqo_silu_mul.argtypes = [_P, _P, _Z, _P]
+    l.kqo_silu_mul.restype = None
+    l.kqo_add.argtypes = [_P, _P, _Z, _P]
+    l.kqo_add.restype = None
     l.kqo_max_threads.argtypes = []
     l.kqo_max_threads.restype = ctypes.c_int
 
@@ -280,6 +288,44 @@ def linear_w4a8(x, wq, wscale, bias, group_size) -> np.ndarray:
     b = _c(bias, np.float32)
     lib().kqo_linear_w4a8(_p(x), _p(wq), _p(ws), _p(b), m, n, k, group_size, _p(xq), _p(xs),
                           _p(out))
+    return out
+
+
+# ---- the matmul's neighbours in a decoder layer -------------------------------
+
+def rms_norm(x, weight, eps) -> np.ndarray:
+    x = _c(x, np.float32)
+    w = _c(weight, np.float32).reshape(-1)
+    dim = x.shape[-1]
+    if w.size != dim:
+        raise OracleError(f"rms_norm weight of {w.size} elements against a last dimension of {dim}")
+    out = np.empty_like(x)
+    lib().kqo_rms_norm(_p(x), _p(w), x.size // dim if dim else 0, dim, float(eps), _p(out))
+    return out
+
+
+def sigmoid(x) -> np.ndarray:
+    x = _c(x, np.float32)
+    out = np.empty_like(x)
+    lib().kqo_sigmoid(_p(x), x.size, _p(out))
+    return out
+
+
+def silu_mul(gate, up) -> np.ndarray:
+    g, u = _c(gate, np.float32), _c(up, np.float32)
+    if g.shape != u.shape:
+        raise OracleError("silu_mul operands differ in shape")
+    out = np.empty_like(g)
+    lib().kqo_silu_mul(_p(g), _p(u), g.size, _p(out))
+    return out
+
+
+def add(a, b) -> np.ndarray:
+    a, b = _c(a, np.float32), _c(b, np.float32)
+    if a.shape != b.shape:
+        raise OracleError("add operands differ in shape")
+    out = np.empty_like(a)
+    lib().kqo_add(_p(a), _p(b), a.size, _p(out))
     return out
 
 

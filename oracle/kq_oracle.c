@@ -433,6 +433,48 @@ KQO_API void kqo_linear_w4a8(const float* x, const int8_t* wq, const float* wsca
     }
 }
 
+/* ---------------------------------------------------------------------------
+ * The matmul's neighbours in a decoder layer (rms_norm, SiLU gate, residual add)
+ * ------------------------------------------------------------------------- */
+
+/* rms_norm over the last dimension, weight only.
+ * Follows packages/runtime/src/reference/ops.ts:948-972 (referenceRmsNorm): the squares are
+ * summed in f64, inv = 1 / sqrt(mean + eps) (the mean is NOT subtracted, eps sits inside
+ * the root), and each output is x * inv * weight evaluated in f64 and rounded to f32 once. */
+KQO_API void kqo_rms_norm(const float* x, const float* weight, size_t rows, size_t dim, double eps, float* out) {
+  for (size_t row = 0; row < rows; ++row) {
+    const float* xr = x + row * dim;
+    double squares = 0.0;
+    for (size_t i = 0; i < dim; ++i) squares += (double)xr[i] * (double)xr[i];
+    const double inv = 1.0 / sqrt(squares / (double)dim + eps);
+    for (size_t i = 0; i < dim; ++i) out[row * dim + i] = (float)((double)xr[i] * inv * (double)weight[i]);
+  }
+}
+
+/* sigmoid, the reference's unary table entry: f32(1 / (1 + exp(-x))) with the exponential in
+ * f64 (packages/runtime/src/reference/ops.ts:150). */
+KQO_API void kqo_sigmoid(const float* x, size_t n, float* out) {
+  for (size_t i = 0; i < n; ++i) out[i] = (float)(1.0 / (1.0 + exp(-(double)x[i])));
+}
+
+/* SwiGLU as the reference's graph spells it: sigmoid(gate) -> mul(gate, sigmoid) -> mul(.., up),
+ * three f32 nodes, each result rounded to f32 (the SiLU pair is what the fusion rule `silu`
+ * of packages/runtime/src/runtime/fusion.ts:453-511 replaces; it keeps the intermediate
+ * f32 rounding of the sigmoid, packages/runtime/src/kernels/silu.ts:1-20). */
+KQO_API void kqo_silu_mul(const float* gate, const float* up, size_t n, float* out) {
+  for (size_t i = 0; i < n; ++i) {
+    const float s = (float)(1.0 / (1.0 + exp(-(double)gate[i])));
+    const float a = (float)((double)gate[i] * (double)s);
+    out[i] = (float)((double)a * (double)up[i]);
+  }
+}
+
+/* residual add: one f32 addition per element (the `add` node). */
+KQO_API void kqo_add(const float* a, const float* b, size_t n, float* out) {
+  for (size_t i = 0; i < n; ++i) out[i] = (float)((double)a[i] + (double)b[i]);
+}
+
+
 KQO_API int kqo_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

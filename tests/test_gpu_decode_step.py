@@ -35,8 +35,9 @@ def test_small_decoder_step_matches_oracle(batch, fused):
     step = DecodeStep(gpu, SMALL, batch, seed=3, keep_host_weights=True, fused=fused)
     step.record()
     ops = SMALL.layers * 4 + 1
-    # per-launch replay: with more than four f32 rows each linear is a conversion launch + the GEMV
-    assert step.kernels_per_step == (1 if fused else ops * (2 if batch > 4 else 1))
+    # per-launch replay: with more than four f32 rows each linear is two conversion launches (row
+    # scales, staged activations) + the GEMV
+    assert step.kernels_per_step == (1 if fused else ops * (3 if batch > 4 else 1))
     x = np.random.default_rng(batch).standard_normal((batch, SMALL.hidden)).astype(np.float32)
     ref = reference_step(step, x)
     # device-resident replay

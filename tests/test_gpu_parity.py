@@ -518,18 +518,3 @@ def test_linear_argument_errors(gpu):
     w.free()
     with pytest.raises(kb.KqError):
         gpu.linear(torch.zeros(1, 64, device="cuda"), w, torch.zeros(16, device="cuda"))  # stale handle
-
-
-def test_out_of_domain_activation_is_reported(gpu):
-    import torch
-    import karume_b200 as kb
-    data, scale = cases.synth_i4(16, 64, seed=1)
-    w = gpu.upload_weight("i4", data, scale, (16, 64), 32)
-    x = torch.ones(1, 64, device="cuda")
-    x[0, 5] = 1e6
-    gpu.linear(x, w, torch.zeros(16, device="cuda"))
-    with pytest.raises(kb.KqError) as err:
-        gpu.sync()
-    assert err.value.status == "KQ_ERR_RANGE"
-    gpu.sync()  # the flag is cleared once reported
-    w.free()

@@ -276,3 +276,107 @@ def test_w8a8_and_w4a8_against_plain_python_loops():
                 accf = np.float32(np.float64(np.float32(acci)) * np.float64(s4[c, gi]) + np.float64(accf))
             want[r, c] = np.float32(np.float64(accf) * np.float64(xs[r]) + np.float64(bias[c]))
     assert np.array_equal(bits(oracle.linear_w4a8(x, w4, s4, bias, g)), bits(want))
+
+
+# ---- the reference's own known-answer tests for the integer-dot contracts -----------------
+# packages/runtime/tests/i8a8_reference_test.ts:42-183, restated value for value.  The expected
+# numbers are the literals that file holds (written down from the contract, not from the
+# implementation), so they pin kqo_quantize_rows / kqo_linear_w8a8 / kqo_linear_w4a8 to
+# something the reference itself commits to.
+
+def test_reference_kat_zero_row_scale_is_f32_tiny():
+    # i8a8_reference_test.ts:42-48
+    q, s = oracle.quantize_rows(np.zeros((1, 4), np.float32), 1, 4)
+    assert float(s[0]) == 1.1754943508222875e-38
+    assert q.tolist() == [[0, 0, 0, 0]]
+
+
+def test_reference_kat_non_finite_rows_propagate_and_stay_in_their_row():
+    # i8a8_reference_test.ts:54-78
+    x = np.array([[1, np.nan, -3], [2, np.inf, 1], [2, -np.inf, 1], [1, 2, 3]], np.float32)
+    q, s = oracle.quantize_rows(x, 4, 3)
+    assert np.isnan(s[0])
+    assert s[1] == np.inf and s[2] == np.inf
+    assert float(s[3]) == 0.023622047156095505
+    assert q[3].tolist() == [42, 85, 127]
+
+
+def test_reference_kat_absolute_maximum_lands_on_127():
+    # i8a8_reference_test.ts:85-91
+    q, s = oracle.quantize_rows(np.array([[127, -127, 3, 0]], np.float32), 1, 4)
+    assert float(s[0]) == 1.0
+    assert q.tolist() == [[127, -127, 3, 0]]
+
+
+def test_reference_kat_w8a8_linear_known_values():
+    # i8a8_reference_test.ts:98-116
+    x = np.array([[8, 3]], np.float32)
+    q, s = oracle.quantize_rows(x, 1, 2)
+    assert q.tolist() == [[127, 48]] and float(s[0]) == 0.06299212574958801
+    out = oracle.linear_w8a8(x, np.array([[1, 2], [-3, 4]], np.int8), np.array([0.5, 0.25], np.float32),
+                             np.array([1, -1], np.float32))
+    assert [float(v) for v in out[0]] == [8.023621559143066, -3.9763779640197754]
+
+
+def test_reference_kat_w8a8_folds_the_two_scales_first():
+    # i8a8_reference_test.ts:119-133: f32(127 * f32(s * w)), not f32(f32(127 * s) * w)
+    out = oracle.linear_w8a8(np.array([[0.001, 0]], np.float32), np.array([[1, 0]], np.int8),
+                             np.array([0.001], np.float32), np.array([0], np.float32))
+    assert float(out[0, 0]) == 9.999999974752427e-7
+    assert float(out[0, 0]) != 1.0000001111620804e-6
+
+
+def test_reference_kat_w4a8_linear_known_values():
+    # i8a8_reference_test.ts:141-162 (group size 2)
+    out = oracle.linear_w4a8(np.array([[8, 3, -2, 5]], np.float32), np.array([[1, 2, -3, 4], [7, -7, 5, -6]], np.int8),
+                             np.array([[0.5, 0.25], [0.125, 2]], np.float32), np.array([1, -1], np.float32), 2)
+    assert [float(v) for v in out[0]] == [14.511811256408691, -76.51968383789062]
+
+
+def test_reference_kat_w4a8_flushes_every_group_to_f32():
+    # i8a8_reference_test.ts:165-183: one rounding per group, not one for the whole row
+    scale = np.float32(0.017009999603033066)
+    out = oracle.linear_w4a8(np.array([[127, 37, 121, 20]], np.float32), np.array([[-7, -3, -7, -6]], np.int8),
+                             np.array([[scale, scale]], np.float32), np.array([0], np.float32), 2)
+    assert float(out[0, 0]) == -33.45867156982422
+    assert float(out[0, 0]) != -33.45866775512695
+
+
+# ---- the matmul's neighbours: rms_norm, sigmoid / SiLU gate, residual add ------------------
+# Known answers of packages/runtime/tests/reference_ops_test.ts:73-74 (sigmoid) and :646-680
+# (rms_norm), restated with the same hand-computed expectations.
+
+def test_reference_kat_sigmoid():
+    out = oracle.sigmoid(np.array([0.0, 2.0], np.float32))
+    assert float(out[0]) == 0.5
+    assert abs(float(out[1]) - 0.8807970779778823) <= 1e-6
+
+
+def test_reference_kat_rms_norm_does_not_subtract_the_mean():
+    x = np.array([[1, 2, 3, 4]], np.float32)
+    inv = 1 / np.sqrt(7.5)  # mean(x^2) = 7.5
+    out = oracle.rms_norm(x, np.ones(4, np.float32), 1e-12)
+    assert abs(out[0, 0] - 1 * inv) <= 1e-6 and abs(out[0, 3] - 4 * inv) <= 1e-6
+    assert np.all(out > 0)  # a layer norm would have made the first entries negative
+    scaled = oracle.rms_norm(x, np.array([2, 0, -1, 0.5], np.float32), 1e-12)
+    assert abs(scaled[0, 0] - 2 * inv) <= 1e-6 and scaled[0, 1] == 0 and abs(scaled[0, 2] + 3 * inv) <= 1e-6
+    rows = oracle.rms_norm(np.array([[3, 4], [6, 8]], np.float32), np.ones(2, np.float32), 1e-12)
+    assert abs(rows[0, 0] - 3 / np.sqrt(12.5)) <= 1e-6 and abs(rows[1, 0] - 6 / np.sqrt(50)) <= 1e-6
+
+
+def test_reference_kat_rms_norm_eps_sits_inside_the_root():
+    zeros = oracle.rms_norm(np.zeros((1, 3), np.float32), np.full(3, 5, np.float32), 1e-6)
+    assert zeros.tolist() == [[0, 0, 0]]
+    epsy = oracle.rms_norm(np.array([[1]], np.float32), np.ones(1, np.float32), 0.5)
+    assert abs(float(epsy[0, 0]) - 1 / np.sqrt(1.5)) <= 1e-6
+    with pytest.raises(oracle.OracleError):
+        oracle.rms_norm(np.ones((1, 4), np.float32), np.ones(3, np.float32), 1e-6)
+
+
+def test_silu_mul_and_add_round_every_node_to_f32():
+    g = np.array([-3.0, -0.5, 0.0, 0.25, 4.0], np.float32)
+    u = np.array([2.0, -1.5, 7.0, 0.125, -0.75], np.float32)
+    s = (1.0 / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32)
+    want = ((g * s).astype(np.float32) * u).astype(np.float32)
+    assert np.array_equal(bits(oracle.silu_mul(g, u)), bits(want))
+    assert np.array_equal(bits(oracle.add(g, u)), bits((g + u).astype(np.float32)))
