@@ -3,18 +3,19 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
 
 A "step" is one pass over every weight matmul of a Llama-8B-shaped decoder (32 layers
-x {q,k,v,o,gate,up,down} + LM head, int4 / group 32, binary16 scales) for a batch of B
-token rows: 4.22 GB of packed weights stream from HBM once per step, which makes the
-inputs larger than L2 by construction (no flush needed).  With N > 1 (launched by
-torch.distributed.run, one rank per GPU) the matmuls are tensor-parallel, column- then
-row-sharded with an all-reduce after each row-parallel matmul; the total work is fixed,
-so scaling is "strong".
+x {q,k,v,o,gate,up,down} + LM head, int4 / group 32, binary16 scales) with the norms, the
+SiLU gate and the residual adds between them, for a batch of B token rows (bench_workload.py):
+4.22 GB of packed weights stream from HBM once per step, which makes the inputs larger than L2
+by construction (no flush needed).  With N > 1 (launched by torch.distributed.run, one rank per
+GPU) the matmuls are tensor-parallel, column- then row-sharded with a sum over the ranks after
+each row-parallel matmul; the total work is fixed, so scaling is "strong".
 
 Prints ONE JSON line.  `value` is tok/s with inputs resident in HBM (device-timed);
-`e2e` is the same metric through host buffers (x copied in, logits copied out every
-step); `roofline` relates the GEMV kernel's algorithmic bytes to its measured time;
-`cpu_baseline` is the CPU oracle (the reference's shader arithmetic restated in C)
-timed on this machine's host cores on a bounded sample.
+`e2e` is the same metric through host buffers with a fence after every step (x copied in,
+logits copied out, the host waits, as a decode loop must before it can pick the next token);
+`roofline` relates the kernel's algorithmic bytes to its measured time; `parity` is a check of
+this very run's outputs against the CPU oracle; `cpu_baseline` is the CPU oracle (the
+reference's shader arithmetic restated in C) timed on this machine's host cores.
 
 `--impl reference` times that CPU restatement alone.  The reference's own WGSL path
 needs Deno + a WebGPU adapter, neither of which exists on these machines.
@@ -35,6 +36,8 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
+from bench_workload import DecodeConfig, reference_step, synth_norm, synth_weight  # noqa: E402
+
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -44,6 +47,30 @@ def measured_peaks():
         except Exception:
             pass
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def host_threads() -> int:
+    """Cores this process may use.  torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm
+    passes this count to the oracle explicitly so that it always uses the whole machine."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def workload_config(cfg: DecodeConfig, batch: int, world: int, **extra):
+    """The `config` object: the same keys in the CUDA arm and in the CPU arm."""
+    out = {
+        "workload": f"{cfg.name}: {cfg.layers} layers x (rms_norm, q|k|v, o + residual, rms_norm, silu(gate)*up, "
+                    f"down + residual) + rms_norm + lm_head, int4 g32, fp16 scales, batch {batch}"
+                    + ("" if cfg.layers == 32 else " (REDUCED layer count: a profiling case, not the benchmark)"),
+        "batch": batch, "activations": "f32", "parallelism": f"tp{world}",
+        "weight_bytes": cfg.weight_bytes(),
+        "l2": f"inputs larger than L2 ({cfg.weight_bytes() / 1e9:.1f} GB of weights per step)",
+        "exchange": None, "replay": None,
+    }
+    out.update(extra)
+    return out
 
 
 class ClockSampler:
@@ -99,61 +126,79 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sample(batch: int, threads: int, steps: int):
-    """Times the CPU restatement of the shader arithmetic (f32, sequential K, one f32
-    multiply per weight for the dequant) on full decode steps: one layer's seven matmuls
-    run 32 times (the same host weights stand in for every layer) plus the LM head.
-    Returns (tok/s, seconds per step, sample description, threads used)."""
+def cpu_sample(cfg: DecodeConfig, batch: int, threads: int, steps: int):
+    """Times the CPU restatement of the shader arithmetic (f32, sequential K, one f32 multiply
+    per weight for the dequant) on full decode steps: one layer's seven matmuls and its norms,
+    gate and adds run `layers` times (the same host weights stand in for every layer) plus the
+    final norm and the LM head.  Returns (tok/s, seconds per step, sample description)."""
     import oracle
-    from karume_b200.decode_step import DecodeConfig, synth_weight
-    cfg = DecodeConfig()
-    rng = np.random.default_rng(0)
-    mats = []
-    for _, k, n, _ in cfg.layer_matmuls() + [("lm_head", cfg.hidden, cfg.vocab, "col")]:
-        payload, scale = synth_weight(rng, n, k)
-        x = rng.standard_normal((batch, k)).astype(np.float32)
-        mats.append((x, payload, scale.astype(np.float32), np.zeros(n, np.float32), n, k))
-    cores = threads if threads > 0 else oracle.max_threads()
-    oracle.linear_i4(*mats[1][:4], mats[1][4], mats[1][5], 32, threads, f64=False)  # warm the thread pool
+    mats = {}
+    for name, k, n, _ in cfg.layer_matmuls() + [("lm_head", cfg.hidden, cfg.vocab, "col")]:
+        payload, scale = synth_weight(0, "l0." + name if name != "lm_head" else name, n, k, cfg.group_size)
+        mats[name] = (payload, scale.astype(np.float32), np.zeros(n, np.float32), n, k)
+    gamma = synth_norm(0, "l0.norm1", cfg.hidden)
+    x = np.random.default_rng(1).standard_normal((batch, cfg.hidden)).astype(np.float32)
+
+    def lin(name, inp):
+        payload, scale, bias, n, k = mats[name]
+        return oracle.linear_i4(inp, payload, scale, bias, n, k, cfg.group_size, threads, f64=False)
+
+    lin("k", x)  # warm the thread pool
     times = []
     for _ in range(steps):
         t0 = time.perf_counter()
+        h = x
         for _layer in range(cfg.layers):
-            for x, payload, scale, bias, n, k in mats[:-1]:
-                oracle.linear_i4(x, payload, scale, bias, n, k, 32, threads, f64=False)
-        x, payload, scale, bias, n, k = mats[-1]
-        oracle.linear_i4(x, payload, scale, bias, n, k, 32, threads, f64=False)
+            xn = oracle.rms_norm(h, gamma, cfg.eps)
+            q = lin("q", xn)
+            lin("k", xn)
+            lin("v", xn)
+            h = oracle.add(lin("o", q), h)
+            xn = oracle.rms_norm(h, gamma, cfg.eps)
+            act = oracle.silu_mul(lin("gate", xn), lin("up", xn))
+            h = oracle.add(lin("down", act), h)
+        lin("lm_head", oracle.rms_norm(h, gamma, cfg.eps))
         times.append(time.perf_counter() - t0)
     step_s = float(np.median(times))
-    desc = (f"{steps} full decode steps (32 x 7 layer matmuls + lm_head, 7505M weights each; one layer's host "
-            f"weights reused for all 32 layers) on {cores} threads, f32 sequential-K shader arithmetic")
-    return batch / step_s, step_s, desc, cores
+    desc = (f"{steps} full decode steps ({cfg.layers} x 7 layer matmuls with norms, gate and adds + lm_head, "
+            f"{cfg.weight_bytes() / 0.5625 / 1e6:.0f}M weights each; one layer's host weights reused for every layer) "
+            f"on {threads} threads, f32 sequential-K shader arithmetic")
+    return batch / step_s, step_s, desc
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from karume_b200.decode_step import DecodeConfig
-    cfg = DecodeConfig()
+    cfg = DecodeConfig(layers=args.layers)
     steps, warm = max(1, args.steps), max(0, args.warmup)
     import oracle
     oracle.build()
+    threads = host_threads()
     if warm:
-        cpu_sample(args.batch, 0, 1)
-    tok_s, step_s, desc, cores = cpu_sample(args.batch, 0, min(steps, 20))
+        cpu_sample(cfg, args.batch, threads, 1)
+    timed_steps = min(steps, 10)  # each step is seconds of CPU work
+    tok_s, step_s, desc = cpu_sample(cfg, args.batch, threads, timed_steps)
     line = {
         "impl": "reference", "metric": "decode_matmul_tok_per_s", "value": tok_s, "unit": "tok/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": f"{cfg.name}: 32 layers x (q,k,v,o,gate,up,down) + lm_head, int4 g32, fp16 scales, batch {args.batch}",
-                   "batch": args.batch, "note": "CPU restatement of the reference's WGSL arithmetic (Deno/WebGPU unavailable on this box)"},
-        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc},
+        "config": workload_config(cfg, args.batch, args.gpus,
+                                  note="CPU restatement of the reference's WGSL arithmetic (Deno/WebGPU unavailable on this box)"),
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def synth_i8(n, k, seed):
+    rng = np.random.default_rng(seed)
+    q = rng.integers(-127, 128, size=(n, k), dtype=np.int16).astype(np.int8)
+    s = (np.abs(rng.standard_normal(n).astype(np.float32)) * np.float32(0.02 / 127)).astype(np.float16)
+    s[s == 0] = np.float16(6e-8)
+    return q, s
 
 
 def kernel_sweep(gpu):
@@ -161,14 +206,13 @@ def kernel_sweep(gpu):
     (N = 1 only): the int4 / int8 GEMV on single matrices (graph replay over distinct weight
     copies totalling more than L2, so every launch streams from HBM) and the prefill GEMM."""
     import torch
-    from tests import cases
     out = {}
 
     def gemv(storage, k, n, m, dtype, a8=False):
         if storage == "i4":
-            data, scale = cases.synth_i4(n, k, seed=1)
+            data, scale = synth_weight(1, f"sweep.{n}x{k}", n, k)
         else:
-            data, scale = cases.synth_i8(n, k, seed=1)
+            data, scale = synth_i8(n, k, 1)
         wbytes = data.nbytes + scale.nbytes
         copies = max(2, min(48, int(400e6 // wbytes) + 1))
         ws = [gpu.upload_weight(storage, data, scale, (n, k), 32 if storage == "i4" else 0) for _ in range(copies)]
@@ -204,13 +248,14 @@ def kernel_sweep(gpu):
     out["gemv_i4_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i4", 1536, 151936, 1, torch.float32)
     out["gemv_i8_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i8", 1536, 151936, 1, torch.float32)
     out["gemv_i4_m8_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 8, torch.float16)
+    out["gemv_i4_m16_4096x11008_f32 (config 2 shape, f32 rows)"] = gemv("i4", 4096, 11008, 16, torch.float32)
     out["gemv_i4_m1_4096x128256_f32 (config 4 lm head)"] = gemv("i4", 4096, 128256, 1, torch.float32)
     out["w8a8_m1_1536x151936 (integer dot, config 1 lm head)"] = gemv("i8", 1536, 151936, 1, torch.float32, a8=True)
     out["w4a8_m1_4096x128256 (integer dot, config 4 lm head)"] = gemv("i4", 4096, 128256, 1, torch.float32, a8=True)
     out["w4a8_m8_4096x11008 (integer dot, config 2 shape)"] = gemv("i4", 4096, 11008, 8, torch.float32, a8=True)
 
     def gemm(m, k, n):
-        data, scale = cases.synth_i4(n, k, seed=1)
+        data, scale = synth_weight(1, f"sweep.{n}x{k}", n, k)
         w = gpu.upload_weight("i4", data, scale, (n, k), 32)
         x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
         bias = torch.zeros(n, device="cuda")
@@ -231,12 +276,66 @@ def kernel_sweep(gpu):
     return out
 
 
+def parity_gate(step, cfg, rank, world, dist, rows_per_rank=48):
+    """This run's outputs against the CPU oracle: the hidden state after the last layer (the same
+    on every rank) and a sample of each rank's logit columns.  Rank 0 runs the oracle chain
+    (f64 accumulation, every weight re-made from its seed) and shares the expected values.
+    Tolerance: |got - ref| <= 1e-5 * max(1, rms(ref)) + 1e-3 * |ref|."""
+    import torch
+    import oracle
+    x = np.random.default_rng(7).standard_normal(step.host_x.shape).astype(np.float32)
+    step.host_x[...] = x
+    step.host_logits[...] = 0
+    if world > 1:
+        dist.barrier()
+    step.run_host()
+    step.sync()
+    shard = cfg.vocab // world
+    rows = np.concatenate([r * shard + np.sort(np.random.default_rng(11 + r).choice(shard, min(rows_per_rank, shard), replace=False))
+                           for r in range(world)])
+    t0 = time.time()
+    if rank == 0:
+        h_ref, logit_ref = reference_step(cfg, step.seed, x, rows, threads=host_threads())
+        packed = np.concatenate([h_ref.reshape(-1), logit_ref.reshape(-1)]).astype(np.float32)
+    else:
+        packed = np.zeros(x.shape[0] * (cfg.hidden + len(rows)), np.float32)
+    if world > 1:
+        t = torch.from_numpy(packed).cuda()
+        dist.broadcast(t, 0)
+        packed = t.cpu().numpy()
+    h_ref = packed[:x.shape[0] * cfg.hidden].reshape(x.shape[0], cfg.hidden)
+    logit_ref = packed[x.shape[0] * cfg.hidden:].reshape(x.shape[0], len(rows))
+    per = len(rows) // world
+    mine = rows[rank * per:(rank + 1) * per] - rank * shard
+    got_l = step.host_logits[:, mine]
+    want_l = logit_ref[:, rank * per:(rank + 1) * per]
+    got_h = step.h.cpu().numpy()
+
+    def cmp(got, want):
+        mag = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+        rep = oracle.allclose(got, want, atol=1e-5 * max(1.0, mag), rtol=1e-3)
+        return rep["pass"], rep["max_abs"], rep["max_rel"], mag
+
+    ok_h, abs_h, rel_h, mag_h = cmp(got_h, h_ref)
+    ok_l, abs_l, rel_l, mag_l = cmp(got_l, want_l)
+    stats = np.array([float(ok_h and ok_l), -abs_h / max(mag_h, 1e-30), -abs_l / max(mag_l, 1e-30)], np.float64)
+    if world > 1:
+        t = torch.from_numpy(stats).cuda()
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        stats = t.cpu().numpy()
+    return {"checked": int(got_h.size + got_l.size * world), "hidden_max_abs_over_rms": float(-stats[1]),
+            "logits_max_abs_over_rms": float(-stats[2]), "logit_columns_per_rank": int(per),
+            "max_abs": float(max(abs_h, abs_l)), "max_rel": float(max(rel_h, rel_l)),
+            "tolerance": "1e-5 * max(1, rms(ref)) + 1e-3 * |ref| against the f64-accumulate CPU oracle, all ranks",
+            "oracle_seconds": round(time.time() - t0, 1), "pass": bool(stats[0] > 0.5)}
+
+
 def run_cuda(args):
     import torch
     import torch.distributed as dist
 
     import karume_b200 as kb
-    from karume_b200.decode_step import DecodeConfig, DecodeStep
+    from bench_workload import DecodeStep
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -249,7 +348,8 @@ def run_cuda(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = DecodeConfig(layers=args.layers)
     gpu = kb.acquire_gpu(local)
-    step = DecodeStep(gpu, cfg, args.batch, rank=rank, world=world, seed=0, fused=args.replay == "fused", exchange=args.exchange)
+    fused = args.replay == "fused" and args.batch <= 2
+    step = DecodeStep(gpu, cfg, args.batch, rank=rank, world=world, seed=0, fused=fused, exchange=args.exchange)
     step.record()
     rng = np.random.default_rng(1)
     step.host_x[...] = rng.standard_normal(step.host_x.shape).astype(np.float32)
@@ -261,7 +361,7 @@ def run_cuda(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(run, steps):
+    def timed(run, steps, fence_each=False):
         ev0 = torch.cuda.Event(enable_timing=True)
         ev1 = torch.cuda.Event(enable_timing=True)
         barrier()
@@ -269,6 +369,8 @@ def run_cuda(args):
             ev0.record()
         for _ in range(steps):
             run()
+            if fence_each:
+                step.sync()
         with torch.cuda.stream(step._stream):
             ev1.record()
         step.sync()
@@ -296,10 +398,18 @@ def run_cuda(args):
     launches = gpu.launch_count - launches_before
     if world > 1 and args.exchange == "nccl":  # a torch CUDA graph replays the launches; the library does not see them
         launches = step.kernels_per_step * args.steps
-    ms_e2e = timed(step.run_host, args.steps)
+    ms_e2e = timed(step.run_host, args.steps, fence_each=True)
+    ms_e2e_pipelined = timed(step.run_host, args.steps)
+    # spread: repeat the K-step region until half a second has been timed
+    rounds, spent = [], 0.0
+    while spent < 500.0 and len(rounds) < 40:
+        ms = timed(step.run_device, args.steps)
+        rounds.append(ms / args.steps)
+        spent += ms
     t1 = time.time()
     clocks = sampler.stop(t0, t1) if rank == 0 else None
 
+    parity = None if args.no_parity else parity_gate(step, cfg, rank, world, dist)
     logits_ok = bool(np.all(np.isfinite(step.host_logits)))
     per_step_ms = ms_dev / args.steps
     per_step_e2e = ms_e2e / args.steps
@@ -324,8 +434,8 @@ def run_cuda(args):
             for _ in range(5):
                 step16.run_device()
             ms16 = gpu.timer_stop() / 5
-            other_batch = {"batch": 16, "replay": "cuda graph", "ms_per_step": ms16, "tok_per_s": 16 / (ms16 * 1e-3),
-                           "GB/s": cfg.algorithmic_bytes(16, 1) / (ms16 * 1e-3) / 1e9}
+            other_batch = {"batch": 16, "replay": "cuda graph of separate launches", "ms_per_step": ms16,
+                           "tok_per_s": 16 / (ms16 * 1e-3), "GB/s": cfg.algorithmic_bytes(16, 1) / (ms16 * 1e-3) / 1e9}
             step16.close()
         sweep = None
         if world == 1 and not args.no_sweep:
@@ -333,30 +443,36 @@ def run_cuda(args):
             sweep = kernel_sweep(gpu)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            tok_cpu, _, desc, cores = cpu_sample(args.batch, 0, 5)
-            cpu = {"value": tok_cpu, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc}
+            import oracle
+            oracle.build()
+            threads = host_threads()
+            tok_cpu, _, desc = cpu_sample(cfg, args.batch, threads, 3)
+            cpu = {"value": tok_cpu, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc}
         line = {
             "metric": "decode_matmul_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm, "ms_per_step": per_step_ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {
-                "workload": f"{cfg.name}: {cfg.layers} layers x (q,k,v,o,gate,up,down) + lm_head, int4 g32, fp16 scales, batch {args.batch}"
-                            + ("" if cfg.layers == 32 else " (REDUCED layer count: a profiling case, not the benchmark)"),
-                "batch": args.batch, "activations": "f32", "parallelism": f"tp{world}", "exchange": (args.exchange if world > 1 else None), "replay": "fused plan kernel" if step.fused else "cuda graph, one launch per linear",
-                "weight_bytes": cfg.weight_bytes(), "l2": f"inputs larger than L2 ({cfg.weight_bytes() / 1e9:.1f} GB of weights per step)"},
+            "config": workload_config(cfg, args.batch, world, exchange=(args.exchange if world > 1 else None),
+                                      replay="fused plan kernel" if step.fused else "cuda graph of separate launches"),
             "e2e": {"value": tok_s_e2e, "unit": "tok/s", "ms_per_step": per_step_e2e,
+                    "fence": "host waits for the logits after every step",
+                    "pipelined_tok_per_s": args.batch / (ms_e2e_pipelined / args.steps * 1e-3),
                     "h2d_bytes_per_step": int(step.x.numel() * 4),
                     "d2h_bytes_per_step": int(step.logits.numel() * 4)},
+            "spread": {"rounds": len(rounds), "steps_per_round": args.steps, "ms_per_step_median": float(np.median(rounds)),
+                       "ms_per_step_min": float(np.min(rounds)), "ms_per_step_max": float(np.max(rounds))},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "plan_pair_kernel" if step.fused else "qgemv_i4_gp_kernel", "achieved": achieved,
-                         "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "plan_pair_kernel" if step.fused else "qgemv_i4 per-launch kernels",
+                         "achieved": achieved, "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "frac_of_8tbs": achieved / 8000.0,
                          "launches_per_step": launches_per_step,
                          "algorithmic_bytes_per_launch": bytes_rank / max(1, launches_per_step),
-                         # dram read+write of one launch: measured with ncu on a 2-layer case of the same
-                         # kernel (traffic = 1.002 x algorithmic bytes, all of it weights) and scaled
+                         # dram read+write of one launch: measured with ncu on a 2-layer, 1-GPU case of the
+                         # same kernel (all of it weights, so it scales with the rank's weight bytes)
                          "traffic": (bytes_rank * 1.002) if step.fused else None,
-                         "traffic_source": "ncu capture of the 2-layer case scaled by weight bytes" if step.fused else None},
+                         "traffic_source": "ncu capture of the 2-layer 1-GPU case of the same kernel, scaled by this rank's weight bytes"
+                                           if step.fused else None},
+            "parity": parity,
             "cpu_baseline": cpu,
             "kernel_sweep": sweep,
             "other_batch": other_batch,
@@ -385,11 +501,13 @@ def main():
     ap.add_argument("--impl", default="kq", choices=["kq", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the single-kernel GEMV / GEMM numbers")
-    ap.add_argument("--exchange", default="kq", choices=["kq", "nccl"], help="all-reduce used when --gpus > 1")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of this run's outputs")
+    ap.add_argument("--exchange", default="kq", choices=["kq", "nccl"], help="sum over ranks used when --gpus > 1")
     ap.add_argument("--layers", type=int, default=32,
                     help="decoder layers; anything but 32 is a small case for profiler captures, not the benchmark")
     ap.add_argument("--replay", default="fused", choices=["fused", "graph"],
-                    help="one GPU: replay the step as one persistent plan kernel (default) or as a CUDA graph of 129 launches")
+                    help="replay the step as one persistent plan kernel per rank (default, batch <= 2) or as a CUDA graph "
+                         "of separate launches")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

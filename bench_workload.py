@@ -1,43 +1,38 @@
-"""The matmuls of one Llama-style decode step, tensor-parallel over the ranks of a box.
+"""The workload bench.py measures and tests/test_gpu_decode_step.py checks: the weight matmuls
+of one Llama-style decode step with their direct neighbours, tensor-parallel over the ranks of
+one box.
 
-This is the workload the headline metric is quoted on: 32 layers x {q, k, v, o, gate,
-up, down} + LM head, every weight int4 / group 32 with binary16 scales, a batch of
-1..16 token rows.  Only the weight matmuls run (no attention, norms or activation
-functions), chained so that each launch depends on the previous one the way the real
-layer does:
+    32 layers x {q, k, v, o, gate, up, down} + LM head, every weight int4 / group 32 with
+    binary16 scales (nibbles uniform over 0..15, scales |N(0, 0.02)| / 7), a batch of 1..16
+    token rows.  One layer is four fused linears (kq_linear_fused):
 
-    x -> [q | k | v]          one launch, three weights, column-parallel
-    q -> o                    row-parallel        (+ all-reduce when world > 1)
-    o -> [gate | up]          one launch, two weights, column-parallel
-    gate -> down = h          row-parallel        (+ all-reduce when world > 1)
-    ... 32 times, every layer starting again from x ...
-    h of the last layer -> LM head (column-parallel over the vocabulary)
+        rms_norm(h) -> [q | k | v]                    column-parallel, three weights
+        q -> o, + h            -> h                   row-parallel (+ sum over ranks)
+        rms_norm(h) -> silu(gate) * up -> act         column-parallel, two weights, one output
+        act -> down, + h       -> h                   row-parallel (+ sum over ranks)
 
-Every layer reads the step's input x rather than the previous layer's h.  Random
-weights with the benchmark's distribution (nibbles uniform in [-8, 7], positive scales)
-have mean -0.5 * scale, and that rank-one component has a gain of 5 to 16 per matmul:
-chained through 32 layers without the norms of a real model it overflows f32 within a
-few layers.  Inside a layer the four launches still depend on one another, and the
-launches of consecutive layers are ordered by the stream, so the timing is that of the
-fully chained step.
+    and rms_norm(h) -> LM head (column-parallel over the vocabulary) ends the step.  Attention
+    itself is not part of the workload (the metric is the decode step's matmul path): o takes q
+    as its input.  The norms keep a 32-layer chain of random matrices bounded, so every layer
+    consumes the previous layer's output, as in the real model.
 
-karume itself is single-device (packages/runtime/src/gpu/device.ts:1182-1218); the
-sharding follows the usual column-then-row scheme so that one exchange per row-parallel
-matmul is the only communication.  With world == 1 the step is recorded as a fused plan
-(kq_plan_*: one persistent kernel for all 129 linears) or, with fused=False, as a CUDA
-graph of one launch per linear (kq_graph_*).  With world > 1 the exchange is libkq's own
-one-shot all-reduce over NVLink peer memory (kq_all_reduce, recorded in the same CUDA graph)
-or, with exchange="nccl", torch.distributed.all_reduce captured in a torch CUDA graph.
+karume is single-device (packages/runtime/src/gpu/device.ts:1182-1218); the sharding follows
+the usual column-then-row scheme, so one exchange per row-parallel matmul is the only
+communication.  The step is recorded once and replayed: as a fused plan (kq_plan_*: one
+persistent kernel per rank, the exchange inside it) or, with fused=False, as a CUDA graph of
+separate launches (kq_graph_*; exchange="nccl" swaps libkq's exchange for
+torch.distributed.all_reduce in a torch CUDA graph).
+
+This module does not load libkq at import time: the CPU arm of the benchmark imports the
+configuration and the weight generator from here without touching the CUDA library.
 """
 from __future__ import annotations
 
 import ctypes
+import zlib
 from dataclasses import dataclass
 
 import numpy as np
-
-from . import _lib
-from .runtime import KQ_SHARD_COLUMN, KQ_SHARD_NONE, KQ_SHARD_ROW, Gpu
 
 
 @dataclass(frozen=True)
@@ -51,6 +46,7 @@ class DecodeConfig:
     ffn: int = 14336
     vocab: int = 128256
     group_size: int = 32
+    eps: float = 1e-5
 
     @property
     def q_dim(self) -> int:
@@ -90,61 +86,106 @@ class DecodeConfig:
 
 SMALL = DecodeConfig(name="tiny-decoder", layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=64,
                      ffn=512, vocab=1024)
+# shards eight ways: every column shard keeps whole 32-row pairs, every row shard whole 64-k chunks
+SMALL_TP = DecodeConfig(name="tiny-tp-decoder", layers=2, hidden=512, q_heads=8, kv_heads=4, head_dim=64,
+                        ffn=1024, vocab=2048)
 
 
-def synth_weight(rng: np.random.Generator, n: int, k: int, group_size: int = 32):
+def _rng(seed: int, name: str) -> np.random.Generator:
+    """Every tensor has a generator of its own, so any of them can be re-made alone."""
+    return np.random.default_rng([seed, zlib.crc32(name.encode())])
+
+
+def synth_weight(seed: int, name: str, n: int, k: int, group_size: int = 32):
     """Nibbles uniform over 0..15, scales |N(0, 0.02)| / 7 in binary16, never zero."""
+    rng = _rng(seed, name)
     payload = rng.integers(0, 256, size=n * k // 2, dtype=np.uint8)
     scale = (np.abs(rng.standard_normal((n, k // group_size), dtype=np.float32)) * np.float32(0.02 / 7)).astype(np.float16)
     scale[scale == 0] = np.float16(6e-8)
     return payload, scale
 
 
+def synth_norm(seed: int, name: str, dim: int) -> np.ndarray:
+    """rms_norm weights around one."""
+    return (1.0 + 0.1 * _rng(seed, name).standard_normal(dim)).astype(np.float32)
+
+
+def norm_names(cfg: DecodeConfig):
+    return [f"l{layer}.norm{i}" for layer in range(cfg.layers) for i in (1, 2)] + ["final_norm"]
+
+
+def reference_step(cfg: DecodeConfig, seed: int, x: np.ndarray, logit_rows=None, threads: int = 0):
+    """The step on the CPU oracle (f64 accumulation), every tensor re-made from its seed.
+    Returns (h after the last layer, logits of the vocabulary rows in `logit_rows`, all when
+    None)."""
+    import oracle
+
+    def lin(name, k, n, inp, rows=None):
+        payload, scale = synth_weight(seed, name, n, k, cfg.group_size)
+        if rows is not None:
+            rows = np.asarray(rows)
+            payload = payload.reshape(n, k // 2)[rows].reshape(-1)
+            scale = scale[rows]
+            n = len(rows)
+        return oracle.linear_i4(inp, payload, scale.astype(np.float32), np.zeros(n, np.float32), n, k,
+                                cfg.group_size, threads)
+
+    h = np.ascontiguousarray(x, np.float32)
+    for layer in range(cfg.layers):
+        p = f"l{layer}."
+        xn = oracle.rms_norm(h, synth_norm(seed, p + "norm1", cfg.hidden), cfg.eps)
+        q = lin(p + "q", cfg.hidden, cfg.q_dim, xn)
+        h = oracle.add(lin(p + "o", cfg.q_dim, cfg.hidden, q), h)
+        xn = oracle.rms_norm(h, synth_norm(seed, p + "norm2", cfg.hidden), cfg.eps)
+        act = oracle.silu_mul(lin(p + "gate", cfg.hidden, cfg.ffn, xn), lin(p + "up", cfg.hidden, cfg.ffn, xn))
+        h = oracle.add(lin(p + "down", cfg.ffn, cfg.hidden, act), h)
+    xn = oracle.rms_norm(h, synth_norm(seed, "final_norm", cfg.hidden), cfg.eps)
+    logits = lin("lm_head", cfg.hidden, cfg.vocab, xn, logit_rows)
+    return h, logits
+
+
 class DecodeStep:
     """Resident sharded weights + activation buffers + a recorded plan of one step."""
 
-    def __init__(self, gpu: Gpu, cfg: DecodeConfig, batch: int, rank: int = 0, world: int = 1,
-                 seed: int = 0, keep_host_weights: bool = False, process_group=None, fused: bool = True,
-                 exchange: str = "kq", share_weights_with: "DecodeStep | None" = None):
+    def __init__(self, gpu, cfg: DecodeConfig, batch: int, rank: int = 0, world: int = 1, seed: int = 0,
+                 process_group=None, fused: bool = True, exchange: str = "kq", share_weights_with: "DecodeStep | None" = None):
         import torch
+        from karume_b200.runtime import KQ_SHARD_COLUMN, KQ_SHARD_NONE, KQ_SHARD_ROW
         if not 1 <= batch <= 16:
             raise ValueError("decode batch is 1..16 token rows")
         for dim in (cfg.q_dim, cfg.kv_dim, cfg.ffn, cfg.vocab):
-            if dim % (world * 16) != 0:
-                raise ValueError(f"dimension {dim} does not shard {world} ways on 16-row blocks")
-        self.gpu, self.cfg, self.batch, self.rank, self.world = gpu, cfg, batch, rank, world
+            if dim % (world * 32) != 0:
+                raise ValueError(f"dimension {dim} does not shard {world} ways on 32-row pairs")
+        self.gpu, self.cfg, self.batch, self.rank, self.world, self.seed = gpu, cfg, batch, rank, world, seed
         self.pg = process_group
-        self.fused = fused and world == 1
-        # "kq": libkq's one-shot peer-memory all-reduce; "nccl": torch.distributed.all_reduce
+        # "kq": libkq's exchange over NVLink peer memory; "nccl": torch.distributed.all_reduce
         self.exchange = exchange if world > 1 else "none"
-        if self.exchange == "kq":
-            gpu.connect_ranks(rank, world, batch * cfg.hidden * 4, process_group)
+        self.fused = fused and self.exchange != "nccl"
+        if self.exchange == "kq" and share_weights_with is None:  # a sharing step also shares the connection
+            gpu.connect_ranks(rank, world, 16 * cfg.hidden * 4, process_group)
         self.torch = torch
         dev = gpu.device
-        self.weights = {}
-        self.host_weights = {} if keep_host_weights else None
-        rng = np.random.default_rng(seed)  # every rank draws the same full matrices, then keeps its shard
+        f32 = dict(dtype=torch.float32, device=dev)
         self._shared = share_weights_with is not None
         if share_weights_with is not None:  # same resident weights, another batch size
-            self.weights = share_weights_with.weights
-            self.host_weights = share_weights_with.host_weights
-        for name, k, n, par in (cfg.all_matmuls() if share_weights_with is None else []):
-            payload, scale = synth_weight(rng, n, k, cfg.group_size)
-            shard = KQ_SHARD_NONE if world == 1 else (KQ_SHARD_COLUMN if par == "col" else KQ_SHARD_ROW)
-            self.weights[name] = gpu.upload_weight("i4", payload, scale, (n, k), cfg.group_size,
-                                                   shard=shard, rank=rank, world=world)
-            if keep_host_weights:
-                self.host_weights[name] = (payload, scale, n, k)
-        f32 = dict(dtype=torch.float32, device=dev)
+            self.weights, self.norms = share_weights_with.weights, share_weights_with.norms
+        else:
+            self.weights, self.norms = {}, {}
+            for name, k, n, par in cfg.all_matmuls():  # every rank draws the full matrix, then keeps its shard
+                payload, scale = synth_weight(seed, name, n, k, cfg.group_size)
+                shard = KQ_SHARD_NONE if world == 1 else (KQ_SHARD_COLUMN if par == "col" else KQ_SHARD_ROW)
+                self.weights[name] = gpu.upload_weight("i4", payload, scale, (n, k), cfg.group_size,
+                                                       shard=shard, rank=rank, world=world)
+            for name in norm_names(cfg):
+                self.norms[name] = torch.from_numpy(synth_norm(seed, name, cfg.hidden)).to(dev)
         w = world
         self.x = torch.zeros((batch, cfg.hidden), **f32)
         self.q = torch.empty((batch, cfg.q_dim // w), **f32)
         self.k = torch.empty((batch, cfg.kv_dim // w), **f32)
         self.v = torch.empty((batch, cfg.kv_dim // w), **f32)
-        self.o = torch.empty((batch, cfg.hidden), **f32)
-        self.gate = torch.empty((batch, cfg.ffn // w), **f32)
-        self.up = torch.empty((batch, cfg.ffn // w), **f32)
+        self.act = torch.empty((batch, cfg.ffn // w), **f32)
         self.h = torch.empty((batch, cfg.hidden), **f32)
+        self.tmp = torch.empty((batch, cfg.hidden), **f32)  # the NCCL path's partial sums
         self.logits = torch.empty((batch, cfg.vocab // w), **f32)
         self.zero_bias = torch.zeros((max(cfg.ffn, cfg.vocab, cfg.hidden),), **f32)
         self.plan = None
@@ -158,39 +199,37 @@ class DecodeStep:
     def _bias(self, n):
         return self.zero_bias[:n]
 
-    def _all_reduce(self, t):
-        if self.exchange == "kq":
-            self.gpu.all_reduce(t)
-        elif self.world > 1:
-            self.torch.distributed.all_reduce(t, group=self.pg)
-
-    def _row_parallel(self, x, w, out):
-        """o / down: K-sharded; the ranks' partial sums are added by libkq (inside the GEMV when
-        it can) or by NCCL."""
-        if self.exchange == "kq":
-            self.gpu.linear_reduce(x, w, self._bias(self.cfg.hidden), out=out)
+    def _row_parallel(self, x, w, residual):
+        """o / down: K-sharded; partial sums added over the ranks, then + residual -> h."""
+        g, hidden = self.gpu, self.cfg.hidden
+        if self.exchange == "nccl":
+            g.linear(x, w, self._bias(hidden), out=self.tmp)
+            self.torch.distributed.all_reduce(self.tmp, group=self.pg)
+            g.add(self.tmp, residual, out=self.h)
         else:
-            self.gpu.linear(x, w, self._bias(self.cfg.hidden), out=out)
-            self._all_reduce(out)
+            g.linear_fused(x, [w], [self._bias(hidden)], [self.h], residual=residual, reduce=self.world > 1)
 
     def enqueue(self) -> None:
-        """Enqueues the step's launches on the context's stream (no host sync)."""
-        g, W = self.gpu, self.weights
+        """Enqueues (or records) the step's launches on the context's stream (no host sync)."""
+        g, W, N, cfg = self.gpu, self.weights, self.norms, self.cfg
         cur = self.x
-        for layer in range(self.cfg.layers):
-            cur = self.x
+        for layer in range(cfg.layers):
             p = f"l{layer}."
-            g.linear_multi(cur, [W[p + "q"], W[p + "k"], W[p + "v"]],
+            g.linear_fused(cur, [W[p + "q"], W[p + "k"], W[p + "v"]],
                            [self._bias(self.q.shape[1]), self._bias(self.k.shape[1]), self._bias(self.v.shape[1])],
-                           [self.q, self.k, self.v])
-            self._row_parallel(self.q, W[p + "o"], self.o)
-            g.linear_multi(self.o, [W[p + "gate"], W[p + "up"]],
-                           [self._bias(self.gate.shape[1]), self._bias(self.up.shape[1])], [self.gate, self.up])
-            self._row_parallel(self.gate, W[p + "down"], self.h)
-        g.linear(self.h, W["lm_head"], self._bias(self.logits.shape[1]), out=self.logits)
+                           [self.q, self.k, self.v], norm_weight=N[p + "norm1"], eps=cfg.eps)
+            self._row_parallel(self.q, W[p + "o"], cur)
+            cur = self.h
+            g.linear_fused(cur, [W[p + "gate"], W[p + "up"]],
+                           [self._bias(self.act.shape[1]), self._bias(self.act.shape[1])], [self.act],
+                           norm_weight=N[p + "norm2"], eps=cfg.eps, swiglu=True)
+            self._row_parallel(self.act, W[p + "down"], cur)
+        g.linear_fused(cur, [W["lm_head"]], [self._bias(self.logits.shape[1])], [self.logits],
+                       norm_weight=N["final_norm"], eps=cfg.eps)
 
     # -- recorded plans ---------------------------------------------------------------------
     def _pinned(self, nbytes):
+        from karume_b200 import _lib
         p = ctypes.c_void_p()
         self.gpu._check(_lib.lib.kq_host_alloc(self.gpu._ctx, nbytes, ctypes.byref(p)))
         return p, np.frombuffer((ctypes.c_uint8 * nbytes).from_address(p.value), np.uint8)
@@ -198,6 +237,7 @@ class DecodeStep:
     def record(self) -> None:
         """Records two replayable plans: device-resident (inputs already in HBM) and
         end-to-end (x copied in from page-locked host memory, logits copied back)."""
+        from karume_b200 import _lib
         torch = self.torch
         L = _lib.lib
         self._px, hx = self._pinned(self.x.numel() * 4)
@@ -208,6 +248,9 @@ class DecodeStep:
             stream = torch.cuda.Stream(self.gpu.device)
             self.gpu.use_stream(stream)
             self._stream = stream
+            if not self.fused:
+                self.enqueue()  # grows the context's scratch before the capture
+                self.gpu.sync()
             before = self.gpu.launch_count
             begin, end = (self.gpu.plan_begin, self.gpu.plan_end) if self.fused else (self.gpu.graph_begin, self.gpu.graph_end)
             self._launch = self.gpu.plan_launch if self.fused else self.gpu.graph_launch
@@ -270,7 +313,7 @@ class DecodeStep:
             free(self.plan)
             free(self.plan_host)
             self.plan = self.plan_host = None
-        if not getattr(self, "_shared", False):
+        if not self._shared:
             for w in self.weights.values():
                 w.free()
         self.weights = {}

@@ -198,6 +198,42 @@ KQ_API int kq_linear_host(kq_ctx* ctx, kq_weight w, const void* x_host, int x_dt
 KQ_API int kq_linear_static(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
                             uint64_t out_dptr, uint32_t m);
 
+/* ---- the matmul's neighbours in a decoder layer -------------------------------------------
+ * rms_norm, the SiLU gate and the residual add are separate kernels in the reference
+ * (packages/runtime/src/kernels/rms-norm.ts, packages/runtime/src/kernels/silu.ts fused from
+ * sigmoid -> mul by packages/runtime/src/runtime/fusion.ts:453-511, and the elementwise `mul` /
+ * `add`).  They are exported here with the reference's f32 formulas:
+ *   kq_rms_norm  out[r, i] = x[r, i] * rsqrt(mean_r(x^2) + eps) * weight[i]   (eps > 0, inside the root)
+ *   kq_silu_mul  out[i] = (gate[i] * sigmoid(gate[i])) * up[i], sigmoid(x) = t = exp(-|x|); x < 0 ? t/(1+t) : 1/(1+t)
+ *   kq_add       out[i] = a[i] + b[i]
+ * All tensors f32; out may alias an input of kq_silu_mul / kq_add. */
+KQ_API int kq_rms_norm(kq_ctx* ctx, uint64_t x_dptr, uint64_t weight_dptr, float eps, uint64_t out_dptr, uint32_t rows,
+                       uint32_t dim);
+KQ_API int kq_silu_mul(kq_ctx* ctx, uint64_t gate_dptr, uint64_t up_dptr, uint64_t out_dptr, uint64_t count);
+KQ_API int kq_add(kq_ctx* ctx, uint64_t a_dptr, uint64_t b_dptr, uint64_t out_dptr, uint64_t count);
+
+/* kq_linear_fused: a linear with those neighbours attached, the four shapes a decoder layer
+ * is made of.  The result is that of the node sequence
+ *   [rms_norm(x, norm_weight, eps) ->] linear(s) [-> silu(gate) * up] [-> all-reduce over ranks] [-> + residual]
+ * with every node's output rounded to f32 as the reference rounds it.
+ *   norm_weight_dptr  0, or f32 [k]: x (f32) is normalised first
+ *   flags & KQ_FUSE_SWIGLU  count == 2, weights (gate, up) of equal shape: ONE output
+ *                     out_dptr[0][m, n] = silu(x.Wg^T + bias[0]) * (x.Wu^T + bias[1])
+ *   flags & KQ_FUSE_REDUCE  count == 1: the weight is a KQ_SHARD_ROW shard, x its k slice; the
+ *                     outputs are added across the connected ranks (as kq_linear_reduce), then
+ *                     the bias and the residual are added, the same bits on every rank
+ *   residual_dptr     0, or f32 [m, n] (count == 1); may be the same buffer as out_dptr[0]
+ * out must not alias x.  Called directly it runs as separate kernels (norm, linears, gate or
+ * add).  Recorded into a fused plan (kq_plan_begin .. kq_plan_end) the persistent kernel does
+ * the norm while it stages the activations and the gate / exchange / residual in the epilogue
+ * of the matmul, so gate and up never travel through HBM; that needs the plan's paired kernel
+ * (at most two f32 / bf16 rows or four binary16 rows, n a multiple of 32 except for the gate
+ * pair, at most 8192 outputs per exchanged op), else kq_plan_end returns KQ_ERR_UNSUPPORTED. */
+enum kq_fuse { KQ_FUSE_SWIGLU = 1, KQ_FUSE_REDUCE = 2 };
+KQ_API int kq_linear_fused(kq_ctx* ctx, uint32_t count, const kq_weight* w, uint64_t x_dptr, int x_dtype,
+                           uint64_t norm_weight_dptr, float norm_eps, const uint64_t* bias_dptr,
+                           uint64_t residual_dptr, const uint64_t* out_dptr, uint32_t m, uint32_t flags);
+
 /* ---- embedding gather ----------------------------------------------------------------
  * out[row, :] = dequantised row index[row] of a resident weight [vocab, hidden] (the weight a
  * tied LM head shares), f32.  Replaces the packed-weight variants of the reference's embedding

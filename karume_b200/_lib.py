@@ -51,6 +51,10 @@ SYMBOLS = {
     "kq_linear_multi": (_i32, [_vp, _u32, _pu64, _u64, _i32, _pu64, _pu64, _u32]),
     "kq_linear_host": (_i32, [_vp, _u64, _vp, _i32, _u64, _vp, _u32]),
     "kq_linear_static": (_i32, [_vp, _u64, _u64, _i32, _u64, _u64, _u32]),
+    "kq_rms_norm": (_i32, [_vp, _u64, _u64, ctypes.c_float, _u64, _u32, _u32]),
+    "kq_silu_mul": (_i32, [_vp, _u64, _u64, _u64, _u64]),
+    "kq_add": (_i32, [_vp, _u64, _u64, _u64, _u64]),
+    "kq_linear_fused": (_i32, [_vp, _u32, _pu64, _u64, _i32, _u64, ctypes.c_float, _pu64, _u64, _pu64, _u32, _u32]),
     "kq_graph_begin": (_i32, [_vp]),
     "kq_graph_end": (_i32, [_vp, _pu64]),
     "kq_graph_launch": (_i32, [_vp, _u64]),

@@ -46,6 +46,10 @@ struct kq_ctx {
   uint64_t zero_bias_count = 0;
   int* idot_sums = nullptr;  // integer sums of the quantised activations (kq_linear_a8)
   uint64_t idot_sums_bytes = 0;
+  float* fused_xn = nullptr;  // kq_linear_fused outside a plan: the normalised activations ...
+  uint64_t fused_xn_bytes = 0;
+  float* fused_gu = nullptr;  // ... and the gate / up outputs in front of the SiLU gate
+  uint64_t fused_gu_bytes = 0;
 };
 
 namespace {
@@ -242,7 +246,7 @@ int check_linear_args(kq_ctx* ctx, const Weight* w, uint64_t x, int x_dtype, uin
 }
 
 int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x, int x_dtype,
-               const uint64_t* bias, const uint64_t* out, uint32_t m) {
+               const uint64_t* bias, const uint64_t* out, uint32_t m, const kq::LinearFusion* fusion = nullptr) {
   if (count < 1 || count > (uint32_t)kq::kMaxMulti)
     return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_multi: count %u outside 1..%d", count, kq::kMaxMulti);
   kq::LinearTarget targets[kq::kMaxMulti];
@@ -257,7 +261,8 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
   }
   if (ctx->recording) {
     const char* why = kq::plan_add_linear(ctx->recording, static_cast<int>(count), targets,
-                                          reinterpret_cast<const void*>(x), x_dtype, m);
+                                          reinterpret_cast<const void*>(x), x_dtype, m,
+                                          fusion ? *fusion : kq::LinearFusion{});
     if (why[0] != 0 && ctx->recording_refusal.empty()) ctx->recording_refusal = why;
     return KQ_OK;
   }
@@ -402,6 +407,8 @@ void kq_destroy(kq_ctx* ctx) {
   if (ctx->host_dev_x) cudaFree(ctx->host_dev_x);
   if (ctx->host_dev_out) cudaFree(ctx->host_dev_out);
   if (ctx->idot_sums) cudaFree(ctx->idot_sums);
+  if (ctx->fused_xn) cudaFree(ctx->fused_xn);
+  if (ctx->fused_gu) cudaFree(ctx->fused_gu);
   if (ctx->zero_bias) cudaFree(ctx->zero_bias);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
@@ -895,6 +902,148 @@ int kq_linear_reduce(kq_ctx* ctx, kq_weight h, uint64_t x_dptr, int x_dtype, uin
   return KQ_OK;
 }
 
+// Grows one of the context's lazily allocated scratch buffers (never during a graph capture).
+static int grow_scratch(kq_ctx* ctx, float** buf, uint64_t* have, uint64_t need, const char* who) {
+  if (need <= *have) return KQ_OK;
+  if (ctx->capturing) return fail(ctx, KQ_ERR_STATE, "%s: scratch must grow; call once outside the recording first", who);
+  if (*buf) cudaFree(*buf);
+  *buf = nullptr;
+  *have = 0;
+  KQ_CUDA(ctx, cudaMalloc(reinterpret_cast<void**>(buf), need));
+  *have = need;
+  return KQ_OK;
+}
+
+int kq_rms_norm(kq_ctx* ctx, uint64_t x_dptr, uint64_t weight_dptr, float eps, uint64_t out_dptr, uint32_t rows,
+                uint32_t dim) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_rms_norm cannot be recorded into a fused plan (use kq_linear_fused)");
+  // packages/runtime/src/kernels/rms-norm.ts:100-117: dim >= 1, eps finite and positive
+  if (dim < 1) return fail(ctx, KQ_ERR_SHAPE, "kq_rms_norm: dim must be positive");
+  if (!(eps > 0.0f) || !(eps < __builtin_inff())) return fail(ctx, KQ_ERR_BAD_ARG, "kq_rms_norm: eps must be finite and positive");
+  if (rows == 0) return KQ_OK;
+  if (!x_dptr || !weight_dptr || !out_dptr) return fail(ctx, KQ_ERR_BAD_ARG, "kq_rms_norm: null device pointer");
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = kq::launch_rms_norm(env_of(ctx), reinterpret_cast<const float*>(x_dptr), reinterpret_cast<const float*>(weight_dptr),
+                                      eps, reinterpret_cast<float*>(out_dptr), rows, dim);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "rms_norm launch");
+  ctx->launches += 1;
+  return KQ_OK;
+}
+
+int kq_silu_mul(kq_ctx* ctx, uint64_t gate_dptr, uint64_t up_dptr, uint64_t out_dptr, uint64_t count) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_silu_mul cannot be recorded into a fused plan (use kq_linear_fused)");
+  if (count == 0) return KQ_OK;
+  if (!gate_dptr || !up_dptr || !out_dptr) return fail(ctx, KQ_ERR_BAD_ARG, "kq_silu_mul: null device pointer");
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = kq::launch_silu_mul(env_of(ctx), reinterpret_cast<const float*>(gate_dptr), reinterpret_cast<const float*>(up_dptr),
+                                      reinterpret_cast<float*>(out_dptr), count);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "silu_mul launch");
+  ctx->launches += 1;
+  return KQ_OK;
+}
+
+int kq_add(kq_ctx* ctx, uint64_t a_dptr, uint64_t b_dptr, uint64_t out_dptr, uint64_t count) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_add cannot be recorded into a fused plan (use kq_linear_fused)");
+  if (count == 0) return KQ_OK;
+  if (!a_dptr || !b_dptr || !out_dptr) return fail(ctx, KQ_ERR_BAD_ARG, "kq_add: null device pointer");
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = kq::launch_add(env_of(ctx), reinterpret_cast<const float*>(a_dptr), reinterpret_cast<const float*>(b_dptr),
+                                 reinterpret_cast<float*>(out_dptr), count);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "add launch");
+  ctx->launches += 1;
+  return KQ_OK;
+}
+
+int kq_linear_fused(kq_ctx* ctx, uint32_t count, const kq_weight* w, uint64_t x_dptr, int x_dtype,
+                    uint64_t norm_weight_dptr, float norm_eps, const uint64_t* bias_dptr, uint64_t residual_dptr,
+                    const uint64_t* out_dptr, uint32_t m, uint32_t flags) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (!w || !bias_dptr || !out_dptr) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: null argument");
+  if (flags & ~static_cast<uint32_t>(KQ_FUSE_SWIGLU | KQ_FUSE_REDUCE))
+    return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: unknown flag bits 0x%x", flags);
+  const bool swiglu = (flags & KQ_FUSE_SWIGLU) != 0, reduce = (flags & KQ_FUSE_REDUCE) != 0;
+  if (count < 1 || count > (uint32_t)kq::kMaxMulti)
+    return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: count %u outside 1..%d", count, kq::kMaxMulti);
+  if (swiglu && (count != 2 || reduce || residual_dptr))
+    return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: the SiLU gate takes two weights (gate, up) and combines with a norm only");
+  if ((reduce || residual_dptr) && count != 1)
+    return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: a residual or a cross-rank reduce goes with a single weight");
+  if (norm_weight_dptr) {
+    if (x_dtype != KQ_F32) return fail(ctx, KQ_ERR_UNSUPPORTED, "kq_linear_fused: the norm takes f32 activations (rms_norm is an f32 op)");
+    if (!(norm_eps > 0.0f) || !(norm_eps < __builtin_inff()))
+      return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: eps must be finite and positive");
+    if (norm_weight_dptr & 15u) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: the norm weight must be 16-byte aligned");
+  }
+  const Weight* w0 = find_weight(ctx, w[0]);
+  if (!w0) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: unknown weight handle");
+  if (swiglu) {
+    const Weight* w1 = find_weight(ctx, w[1]);
+    if (!w1 || w1->n != w0->n || w1->k != w0->k)
+      return fail(ctx, KQ_ERR_SHAPE, "kq_linear_fused: gate and up weights differ in shape");
+  }
+  if (reduce && !kq::comm_connected(ctx->comm)) return fail(ctx, KQ_ERR_STATE, "kq_linear_fused: KQ_FUSE_REDUCE before kq_comm_connect");
+  if (residual_dptr && (residual_dptr & 3u)) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: residual must be 4-byte aligned");
+
+  if (ctx->recording) {
+    kq::LinearFusion fusion;
+    fusion.norm_weight = reinterpret_cast<const float*>(norm_weight_dptr);
+    fusion.norm_eps = norm_eps;
+    fusion.residual = reinterpret_cast<const float*>(residual_dptr);
+    fusion.swiglu = swiglu;
+    fusion.reduce = reduce;
+    // the gate pair has one output; the recorder checks one pointer per weight
+    const uint64_t gate_outs[2] = {out_dptr[0], out_dptr[0]};
+    return run_linear(ctx, count, w, x_dptr, x_dtype, bias_dptr, swiglu ? gate_outs : out_dptr, m, &fusion);
+  }
+  if (m == 0) return KQ_OK;
+  DeviceGuard guard(ctx->device);
+  // Outside a plan: the same arithmetic as a sequence of kernels.
+  uint64_t x_eff = x_dptr;
+  if (norm_weight_dptr) {
+    if (!x_dptr) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: x is null");
+    const int rc = grow_scratch(ctx, &ctx->fused_xn, &ctx->fused_xn_bytes, static_cast<uint64_t>(m) * w0->k * sizeof(float), "kq_linear_fused");
+    if (rc != KQ_OK) return rc;
+    cudaError_t e = kq::launch_rms_norm(env_of(ctx), reinterpret_cast<const float*>(x_dptr), reinterpret_cast<const float*>(norm_weight_dptr),
+                                        norm_eps, ctx->fused_xn, m, w0->k);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "rms_norm launch");
+    ctx->launches += 1;
+    x_eff = reinterpret_cast<uint64_t>(ctx->fused_xn);
+  }
+  if (swiglu) {
+    const uint64_t each = static_cast<uint64_t>(m) * w0->n;
+    const int rc = grow_scratch(ctx, &ctx->fused_gu, &ctx->fused_gu_bytes, 2 * each * sizeof(float), "kq_linear_fused");
+    if (rc != KQ_OK) return rc;
+    if (!out_dptr[0]) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: out is null");
+    const uint64_t outs[2] = {reinterpret_cast<uint64_t>(ctx->fused_gu), reinterpret_cast<uint64_t>(ctx->fused_gu + each)};
+    const int rc2 = run_linear(ctx, 2, w, x_eff, x_dtype, bias_dptr, outs, m);
+    if (rc2 != KQ_OK) return rc2;
+    cudaError_t e = kq::launch_silu_mul(env_of(ctx), ctx->fused_gu, ctx->fused_gu + each, reinterpret_cast<float*>(out_dptr[0]), each);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "silu_mul launch");
+    ctx->launches += 1;
+    return KQ_OK;
+  }
+  // With a residual the linear lands in scratch first: the residual may be the output buffer.
+  uint64_t lin_out = out_dptr[0];
+  if (residual_dptr) {
+    const int rc = grow_scratch(ctx, &ctx->fused_gu, &ctx->fused_gu_bytes, static_cast<uint64_t>(m) * w0->n * sizeof(float), "kq_linear_fused");
+    if (rc != KQ_OK) return rc;
+    lin_out = reinterpret_cast<uint64_t>(ctx->fused_gu);
+  }
+  const int rc = reduce ? kq_linear_reduce(ctx, w[0], x_eff, x_dtype, bias_dptr[0], lin_out, m)
+                        : run_linear(ctx, count, w, x_eff, x_dtype, bias_dptr, residual_dptr ? &lin_out : out_dptr, m);
+  if (rc != KQ_OK) return rc;
+  if (residual_dptr) {
+    cudaError_t e = kq::launch_add(env_of(ctx), ctx->fused_gu, reinterpret_cast<const float*>(residual_dptr),
+                                   reinterpret_cast<float*>(out_dptr[0]), static_cast<uint64_t>(m) * w0->n);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "residual add launch");
+    ctx->launches += 1;
+  }
+  return KQ_OK;
+}
+
 int kq_plan_begin(kq_ctx* ctx) {
   if (!ctx) return KQ_ERR_BAD_ARG;
   if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_plan_begin: a recording is already open");
@@ -916,7 +1065,9 @@ int kq_plan_end(kq_ctx* ctx, kq_plan* out) {
                 ctx->recording_refusal.c_str());
   }
   const char* why = "";
-  cudaError_t e = kq::plan_finalize(plan, env_of(ctx), &why);
+  kq::LaunchEnv env = env_of(ctx);
+  env.fused = kq::comm_fused_view(ctx->comm);
+  cudaError_t e = kq::plan_finalize(plan, env, &why);
   if (e != cudaSuccess) {
     kq::plan_destroy(plan);
     if (why[0] != 0) return fail(ctx, KQ_ERR_UNSUPPORTED, "%s", why);

@@ -107,6 +107,18 @@ __host__ __device__ __forceinline__ size_t tiled_i8_locate(uint32_t row, uint32_
   return (static_cast<size_t>(R) * (k / kChunkK8) + J) * 512u + (4u * g + t) * 16u + (half * 2u + upper) * 4u + b;
 }
 
+// ---- SiLU gate -------------------------------------------------------------------
+// sigmoid in the reference's stable form (packages/runtime/src/codegen/elementwise.ts:187-190)
+// and silu(gate) * up with every product rounded to f32, as the reference's sigmoid -> mul -> mul
+// node sequence rounds them (packages/runtime/src/kernels/silu.ts).
+__device__ __forceinline__ float sigmoid_stable(float x) {
+  const float t = expf(-fabsf(x));
+  return x < 0.0f ? __fdiv_rn(t, __fadd_rn(1.0f, t)) : __fdiv_rn(1.0f, __fadd_rn(1.0f, t));
+}
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+  return __fmul_rn(__fmul_rn(gate, sigmoid_stable(gate)), up);
+}
+
 // ---- misc ----------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -104,13 +104,67 @@ __device__ __forceinline__ float absmax8(const float (&v)[8]) {
 // the price of 8 registers per octet held).
 //   lo_offset != 0 selects the split layout: activation row r occupies column r, its hi part at
 //          byte offset 0 of the group and its lo part lo_offset bytes further on.
+// Converts ONE k-octet (8 consecutive activations of one row, already in registers as f32) and
+// stores it; the four threads of a (group, row) call this together (the shuffles below run over
+// whole warps, so every lane of a warp must make the call, `valid` or not).
+template <bool kHasLo, int kCorrStride, bool kPerGroup>
+__device__ __forceinline__ void stage_octet(const float (&v)[8], bool valid, uint32_t q, uint32_t row, uint32_t lg,
+                                            uint8_t* xs, uint32_t xs_stride, float* corr, uint32_t lo_offset,
+                                            const float* row_scale) {
+  Pow2 ps;
+  if constexpr (kPerGroup) {
+    float amax = absmax8(v);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    ps = pow2_prescale(amax);
+  } else {
+    ps.scale = valid ? row_scale[row] : 1.0f;
+    ps.inv = 1.0f;
+  }
+  uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
+  float sum = 0.0f;
+  if (valid) {
+    __half h[8], l[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float staged = v[e] * ((e & 1) ? ps.scale * 0.0625f : ps.scale);
+      const float back = (e & 1) ? 16.0f : 1.0f;
+      h[e] = __float2half_rn(staged);
+      const float hf = __half2float(h[e]);
+      if constexpr (kHasLo) {
+        l[e] = __float2half_rn(staged - hf);
+        sum = fmaf(hf + __half2float(l[e]), back, sum);
+      } else {
+        sum = fmaf(hf, back, sum);
+      }
+    }
+    hi4 = make_uint4(pack_half2(h[0], h[4]), pack_half2(h[1], h[5]), pack_half2(h[2], h[6]), pack_half2(h[3], h[7]));
+    if constexpr (kHasLo)
+      lo4 = make_uint4(pack_half2(l[0], l[4]), pack_half2(l[1], l[5]), pack_half2(l[2], l[6]), pack_half2(l[3], l[7]));
+  }
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  if (valid) {
+    const uint32_t col = (kHasLo && lo_offset == 0) ? 2 * row : row;
+    const uint32_t off = lg * xs_stride + col * 64 + q * 16;
+    *reinterpret_cast<uint4*>(xs + off) = hi4;
+    if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + (lo_offset == 0 ? 64u : lo_offset)) = lo4;
+    if (q == 0) {
+      if constexpr (kPerGroup)
+        reinterpret_cast<float2*>(corr)[lg * kCorrStride + row] = make_float2(sum * (-8.0f / kUnscale), ps.inv);
+      else
+        corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
+    }
+  }
+}
+
 template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2 = false, int kBatch = 1, bool kPerGroup = true>
 __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, uint32_t k,
                                         uint32_t group0, uint32_t groups, uint8_t* xs,
                                         uint32_t xs_stride, float* corr, uint32_t lo_offset = 0,
                                         const float* row_scale = nullptr) {
   const uint32_t items = groups * m * 4;
-  const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles below
+  const uint32_t items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles
   for (uint32_t base = threadIdx.x; base < items_padded; base += blockDim.x * kBatch) {
     float v[kBatch][8];
 #pragma unroll
@@ -129,58 +183,86 @@ __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, ui
     for (int b = 0; b < kBatch; ++b) {
       const uint32_t item = base + b * blockDim.x;
       if (item >= items_padded) break;  // warp-uniform
-      const bool valid = item < items;
-      const uint32_t q = item & 3u;
       const uint32_t rest = item >> 2;
-      const uint32_t row = rest % m;
-      const uint32_t lg = rest / m;
-      Pow2 ps;
-      if constexpr (kPerGroup) {
-        float amax = absmax8(v[b]);
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        ps = pow2_prescale(amax);
-      } else {
-        ps.scale = valid ? row_scale[row] : 1.0f;
-        ps.inv = 1.0f;
-      }
-      uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
-      float sum = 0.0f;
-      if (valid) {
-        __half h[8], l[8];
+      stage_octet<kHasLo, kCorrStride, kPerGroup>(v[b], item < items, item & 3u, rest % m, rest / m, xs, xs_stride,
+                                                  corr, lo_offset, row_scale);
+    }
+  }
+}
+
+// The same with an rms_norm in front (the whole activation block, group0 = 0):
+//   v = (x * rsqrt(mean_row(x^2) + eps)) * weight[k]        (packages/runtime/src/kernels/rms-norm.ts:60-90)
+// is what gets staged.  The sum of squares of a row is taken over the CTA: every thread adds
+// the squares of its own octets in ascending order, a warp adds its lanes with the shuffle
+// tree, and the warps' sums are added in warp order, so every CTA that stages the same x
+// computes the same bits.  `red` is [warps][m] floats of shared memory, `inv` is [m].
+// When the block fits one round (items <= threads * kBatch, every decode shape) the octets
+// stay in registers between the two passes; otherwise x is read a second time.
+template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2, int kBatch>
+__device__ __forceinline__ void stage_x_rms_norm(const XT* __restrict__ x, const float* __restrict__ weight, float eps,
+                                                 uint32_t m, uint32_t k, uint8_t* xs, uint32_t xs_stride, float* corr,
+                                                 float* red, float* inv) {
+  const uint32_t groups = k >> 5;
+  const uint32_t items = groups * m * 4;
+  const uint32_t items_padded = (items + 31u) & ~31u;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
+  const bool one_round = items_padded <= blockDim.x * kBatch;
+  float v[kBatch][8];
+  float sq[16];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float staged = v[b][e] * ((e & 1) ? ps.scale * 0.0625f : ps.scale);
-          const float back = (e & 1) ? 16.0f : 1.0f;
-          h[e] = __float2half_rn(staged);
-          const float hf = __half2float(h[e]);
-          if constexpr (kHasLo) {
-            l[e] = __float2half_rn(staged - hf);
-            sum = fmaf(hf + __half2float(l[e]), back, sum);
-          } else {
-            sum = fmaf(hf, back, sum);
-          }
-        }
-        hi4 = make_uint4(pack_half2(h[0], h[4]), pack_half2(h[1], h[5]), pack_half2(h[2], h[6]),
-                         pack_half2(h[3], h[7]));
-        if constexpr (kHasLo)
-          lo4 = make_uint4(pack_half2(l[0], l[4]), pack_half2(l[1], l[5]), pack_half2(l[2], l[6]),
-                           pack_half2(l[3], l[7]));
+  for (int r = 0; r < 16; ++r) sq[r] = 0.0f;
+  for (uint32_t base = threadIdx.x; base < items_padded; base += blockDim.x * kBatch) {
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const uint32_t item = base + b * blockDim.x;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[b][e] = 0.0f;
+      if (item < items) {
+        const uint32_t rest = item >> 2;
+        const uint32_t row = rest % m, lg = rest / m;
+        load_x8<XT, kFromL2>(x + static_cast<size_t>(row) * k + (static_cast<size_t>(lg) << 5) + ((item & 3u) << 3), v[b]);
+        float s = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s = fmaf(v[b][e], v[b][e], s);
+#pragma unroll
+        for (int r = 0; r < 16; ++r)
+          if (static_cast<uint32_t>(r) == row) sq[r] += s;
       }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    if (static_cast<uint32_t>(r) < m) {  // uniform
+      const float total = warp_sum(sq[r]);
+      if (lane == 0) red[warp * m + r] = total;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < m) {
+    float total = 0.0f;
+    for (uint32_t w = 0; w < warps; ++w) total += red[w * m + threadIdx.x];
+    inv[threadIdx.x] = rsqrtf(total * (1.0f / static_cast<float>(k)) + eps);
+  }
+  __syncthreads();
+  for (uint32_t base = threadIdx.x; base < items_padded; base += blockDim.x * kBatch) {
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const uint32_t item = base + b * blockDim.x;
+      if (item >= items_padded) break;  // warp-uniform
+      const bool valid = item < items;
+      const uint32_t rest = item >> 2;
+      const uint32_t row = rest % m, lg = rest / m, q = item & 3u;
       if (valid) {
-        const uint32_t col = (kHasLo && lo_offset == 0) ? 2 * row : row;
-        const uint32_t off = lg * xs_stride + col * 64 + q * 16;
-        *reinterpret_cast<uint4*>(xs + off) = hi4;
-        if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + (lo_offset == 0 ? 64u : lo_offset)) = lo4;
-        if (q == 0) {
-          if constexpr (kPerGroup)
-            reinterpret_cast<float2*>(corr)[lg * kCorrStride + row] = make_float2(sum * (-8.0f / kUnscale), ps.inv);
-          else
-            corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
-        }
+        if (!one_round)
+          load_x8<XT, kFromL2>(x + static_cast<size_t>(row) * k + (static_cast<size_t>(lg) << 5) + (q << 3), v[b]);
+        const float r_inv = inv[row];
+        const float4 w0 = *reinterpret_cast<const float4*>(weight + (lg << 5) + (q << 3));
+        const float4 w1 = *reinterpret_cast<const float4*>(weight + (lg << 5) + (q << 3) + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[b][e] = __fmul_rn(__fmul_rn(v[b][e], r_inv), wv[e]);
       }
+      stage_octet<kHasLo, kCorrStride, true>(v[b], valid, q, row, lg, xs, xs_stride, corr, 0u, nullptr);
     }
   }
 }

@@ -33,6 +33,15 @@ struct LinearTarget {
   float* out;
 };
 
+// The neighbours of a linear that kq_linear_fused attaches to it.
+struct LinearFusion {
+  const float* norm_weight = nullptr;  // [k] f32: x is rms-normalised first
+  float norm_eps = 0.0f;
+  const float* residual = nullptr;     // [m, n] f32 added to the single output
+  bool swiglu = false;                 // two weights (gate, up) -> one output silu(gate) * up
+  bool reduce = false;                 // row-parallel shard: add the outputs across ranks
+};
+
 // Device-side view of the tensor-parallel exchange area a row-parallel GEMV uses to add its
 // partial sums across ranks inside its own epilogue (kq_comm.cu owns the memory).
 constexpr int kFusedMaxWorld = 8;
@@ -98,7 +107,7 @@ Plan* plan_create();
 void plan_destroy(Plan* plan);
 const char* plan_add_copy(Plan* plan, bool to_device, void* device, void* host, uint64_t bytes);
 const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, const void* x, int x_dtype,
-                            uint32_t m);
+                            uint32_t m, const LinearFusion& fusion);
 uint32_t plan_op_count(const Plan* plan);
 cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why);
 cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches);
@@ -121,6 +130,14 @@ cudaError_t comm_all_reduce(Comm* c, cudaStream_t stream, float* data, uint64_t 
 int comm_take_status(Comm* c);
 const FusedCommDev* comm_fused_view(const Comm* c);
 uint32_t comm_rank(const Comm* c);
+}  // namespace kq
+
+// ---- rms_norm, SiLU gate, residual add as kernels of their own (kq_fused_ops.cu) -----------
+namespace kq {
+cudaError_t launch_rms_norm(const LaunchEnv& env, const float* x, const float* weight, float eps, float* out,
+                            uint32_t rows, uint32_t dim);
+cudaError_t launch_silu_mul(const LaunchEnv& env, const float* gate, const float* up, float* out, uint64_t count);
+cudaError_t launch_add(const LaunchEnv& env, const float* a, const float* b, float* out, uint64_t count);
 }  // namespace kq
 
 // ---- integer-dot linear (kq_idot.cu) ---------------------------------------------------

@@ -36,14 +36,24 @@ constexpr int kSlots = 2;  // ring slots per warp
 constexpr uint32_t kOpWindow = 16;  // op descriptors the paired kernel keeps in shared memory
 constexpr uint32_t kSpinLimit = 1u << 22;
 
+// What an op does besides out = x . W^T + bias (kq_linear_fused): all of it runs inside the
+// paired kernel, in the activation staging (norm) and in the epilogue (the rest).
+constexpr uint32_t kOpSwiglu = 1u;  // weights (gate, up): out[0] = silu(x.Wg^T + bg) * (x.Wu^T + bu)
+constexpr uint32_t kOpReduce = 2u;  // row-parallel shard: the outputs are added across ranks
+
 struct PlanOpDev {
   const uint8_t* w[kMaxMulti];
   const float* bias[kMaxMulti];
   float* out[kMaxMulti];
+  const float* residual[kMaxMulti];  // null, or [m, n] added to the output (may alias it)
   uint32_t n[kMaxMulti];
   uint32_t rb_begin[kMaxMulti + 1];  // prefix sums of n / 16
   uint32_t count;
+  uint32_t flags;
   const void* x;
+  const float* norm_weight;  // null, or [k]: x is rms-normalised with this weight while it is staged
+  float norm_eps;
+  uint32_t reduce_index;     // ordinal of this op among the plan's kOpReduce ops
   uint32_t k;
   uint32_t chunks_per_row;   // k / 64
   uint32_t slabs;            // S: k-slabs a row block is split into across the warps of a CTA
@@ -62,6 +72,8 @@ struct PlanParams {
   uint32_t xs_bytes;       // shared memory reserved for the staged activations of one op
   unsigned int* grid_bar;  // arrivals at the inter-op barrier (zeroed before every launch)
   int* status;             // non-zero: a bounded wait gave up
+  const FusedCommDev* fcomm;  // exchange areas of the ranks (plans with kOpReduce ops)
+  uint32_t reduce_ops;        // how many kOpReduce ops the plan holds
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -84,6 +96,19 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+
+// One exchange entry = {value, epoch} in ONE aligned 64-bit word, written and polled with scalar
+// 64-bit accesses (single-copy atomic: a reader that sees the new epoch sees the value stored
+// with it).  Relaxed, system scope: the entry is its own flag.
+__device__ __forceinline__ void st_exchange_entry(uint2* p, float value, unsigned int epoch) {
+  const unsigned long long word = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(value);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(word) : "memory");
+}
+__device__ __forceinline__ uint2 ld_exchange_entry(const uint2* p) {
+  unsigned long long word;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(p) : "memory");
+  return make_uint2(static_cast<uint32_t>(word), static_cast<uint32_t>(word >> 32));
 }
 
 // One warp's share of one CTA round of an op.
@@ -517,7 +542,7 @@ __device__ __forceinline__ void lds_v2f_if_at(float& a, float& b, uint32_t base,
 
 struct PairItem {
   const uint8_t* src;  // first chunk of the slab of the pair's first row block
-  uint32_t row_stride; // bytes from a chunk of the first block to the same chunk of the second
+  int64_t row_stride;  // bytes from a chunk of the first block to the same chunk of the second
   uint32_t nck;        // chunks in the slab (0: nothing to do)
   uint32_t c0;         // first chunk index inside the row
   uint32_t rb;         // first row block of the pair, inside the op
@@ -542,16 +567,21 @@ __device__ __forceinline__ PairItem pair_item_of(const PlanOpDev& o, uint32_t ro
   if (unit >= o.cta_items) return it;
   const uint32_t sub = warp >> o.slabs_log2, slab = warp & (o.slabs - 1u);
   const uint32_t pair = unit * (static_cast<uint32_t>(kPlanWarps) >> o.slabs_log2) + sub;
-  it.rb = 2u * pair;
+  const bool swiglu = (o.flags & kOpSwiglu) != 0;
+  // plain op: two adjacent row blocks of one weight; SiLU gate: block `pair` of the gate weight
+  // and the same block of the up weight (row_blocks counts the blocks of ONE of them)
+  it.rb = swiglu ? pair : 2u * pair;
   if (it.rb >= o.row_blocks) return it;
   it.valid = true;
+  if (!swiglu) {
 #pragma unroll
-  for (int i = 1; i < kMaxMulti; ++i)
-    if (i < static_cast<int>(o.count) && it.rb >= o.rb_begin[i]) it.wi = i;
+    for (int i = 1; i < kMaxMulti; ++i)
+      if (i < static_cast<int>(o.count) && it.rb >= o.rb_begin[i]) it.wi = i;
+  }
   it.c0 = slab * o.chunks_per_slab;
   if (it.c0 >= o.chunks_per_row) return it;
   it.nck = min(o.chunks_per_slab, o.chunks_per_row - it.c0);
-  it.row_stride = o.chunks_per_row * kCB;
+  it.row_stride = swiglu ? static_cast<int64_t>(o.w[1] - o.w[0]) : static_cast<int64_t>(o.chunks_per_row) * kCB;
   it.src = o.w[it.wi] + (static_cast<size_t>(it.rb - o.rb_begin[it.wi]) * o.chunks_per_row + it.c0) * kCB;
   return it;
 }
@@ -614,7 +644,8 @@ plan_pair_kernel(const PlanParams p) {
   __syncthreads();
 
   // ---- producer -------------------------------------------------------------------------
-  uint32_t prod_op = 0, prod_round = 0, prod_q = 0, prod_left = 0, prod_stride = 0;
+  uint32_t prod_op = 0, prod_round = 0, prod_q = 0, prod_left = 0;
+  int64_t prod_stride = 0;
   const uint8_t* prod_src = nullptr;
   auto produce = [&]() {
     while (prod_left == 0) {  // move to this warp's next item, whatever op it belongs to
@@ -725,6 +756,52 @@ plan_pair_kernel(const PlanParams p) {
     }
   };
 
+  // ---- cross-rank exchange (plans with kOpReduce ops) --------------------------------------
+  // The k-th reduce op of this launch uses epoch base + 1 + k, where base is what the previous
+  // launch (of this plan or of kq_linear_reduce) left in the exchange area; the last CTA to
+  // finish advances it.  Entries of consecutive epochs alternate between two slots, and the
+  // grid barrier between ops keeps every rank within one exchange of its peers.
+  const unsigned int epoch_base = p.fcomm != nullptr ? *reinterpret_cast<volatile unsigned int*>(p.fcomm->epoch) : 0u;
+  constexpr int kMaxOut = 8;  // outputs one lane finishes per round
+  // out = sum over ranks (rank order) of the lane's finished partial sums, in place
+  auto exchange = [&](float (&val)[kMaxOut], const uint32_t (&off)[kMaxOut], int cnt, unsigned int epoch) {
+    const FusedCommDev& fc = *p.fcomm;
+    const uint32_t me = fc.rank, world = fc.world;
+    const uint64_t slot_entries = kFusedSlotBytes / 8;
+    const uint64_t parity_base = static_cast<uint64_t>(epoch & 1u) * kFusedMaxWorld;
+    for (uint32_t r = 0; r < world; ++r) {
+      if (r == me) continue;
+      uint2* dst = reinterpret_cast<uint2*>(fc.base[r] + fc.data_off) + (parity_base + me) * slot_entries;
+#pragma unroll
+      for (int i = 0; i < kMaxOut; ++i)
+        if (i < cnt) st_exchange_entry(dst + off[i], val[i], epoch);
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxOut; ++i) {
+      if (i >= cnt) continue;
+      float sum = 0.0f;
+      for (uint32_t r = 0; r < world; ++r) {
+        if (r == me) {
+          sum += val[i];
+          continue;
+        }
+        const uint2* src = reinterpret_cast<const uint2*>(fc.base[me] + fc.data_off) + (parity_base + r) * slot_entries + off[i];
+        uint2 e;
+        uint32_t spins = 0;
+        while (true) {
+          e = ld_exchange_entry(src);
+          if (e.y == epoch) break;
+          if (++spins > kSpinLimit) {
+            *reinterpret_cast<volatile int*>(p.status) = 3;
+            break;
+          }
+        }
+        sum += __uint_as_float(e.x);
+      }
+      val[i] = sum;
+    }
+  };
+
   uint32_t cons_q = 0, red_buf = 0;
   for (uint32_t op = 0; op < p.op_count; ++op) {
     // Nothing about the first item depends on the previous op: look it up before the wait.
@@ -751,10 +828,19 @@ plan_pair_kernel(const PlanParams p) {
     }
     cur_op = op;
     const PlanOpDev& o = win[op % kOpWindow];
-    stage_x<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr);
+    if (o.norm_weight != nullptr) {
+      // no reduction of the previous op is in flight any more: its buffers serve as scratch
+      float* scratch = red + static_cast<size_t>(red_buf) * kPlanWarps * (2 * p.m * 16);
+      stage_x_rms_norm<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), o.norm_weight, o.norm_eps, p.m, o.k,
+                                                         xs, kXsStride, corr, scratch, scratch + kPlanWarps * p.m);
+    } else {
+      stage_x<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr);
+    }
     __syncthreads();
 
     const uint32_t slabs = o.slabs, rounds = o.rounds;
+    const bool swiglu = (o.flags & kOpSwiglu) != 0, reduce = (o.flags & kOpReduce) != 0;
+    const unsigned int epoch = epoch_base + 1u + o.reduce_index;
     for (uint32_t round = 0; round < rounds; ++round) {
       const PairItem it = round == 0 ? first_item : pair_item_of<kCB>(o, round, warp, grid, cta);
 #pragma unroll
@@ -765,16 +851,17 @@ plan_pair_kernel(const PlanParams p) {
       const uint32_t local_row = (it.rb - o.rb_begin[it.wi]) * 16u;  // first row of the pair inside its weight
       const uint32_t n_i = o.n[it.wi];
       float* out = o.out[it.wi];
+      const float* residual = o.residual[it.wi];
       const float* bias = o.bias[it.wi];
+      const float* bias2 = swiglu ? o.bias[1] : bias + 16;  // bias of the pair's second block
       float bias_pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       if (it.valid) {
         if (o.slabs == 1) {
-#pragma unroll
-          for (int r = 0; r < 2; ++r) {
-            bias_pre[2 * r] = bias[local_row + r * 16 + g];
-            bias_pre[2 * r + 1] = bias[local_row + r * 16 + g + 8];
-          }
-        } else {
+          bias_pre[0] = bias[local_row + g];
+          bias_pre[1] = bias[local_row + g + 8];
+          bias_pre[2] = bias2[local_row + g];
+          bias_pre[3] = bias2[local_row + g + 8];
+        } else if (!swiglu) {
           bias_pre[0] = bias[local_row + lane];  // the reducer's first pass covers rows lane of the pair
         }
       }
@@ -817,48 +904,111 @@ plan_pair_kernel(const PlanParams p) {
           acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 2);
         }
       const bool owner = jl == 0;
+      // A finished value of a plain op: partial sum (scaled back) [+ the other ranks' partial
+      // sums] + bias [+ residual], each addition rounded to f32 like the reference's node
+      // sequence linear -> add.
+      float val[kMaxOut];
+      uint32_t off[kMaxOut];  // mm * n + row
+      float bsv[kMaxOut];
+      int cnt = 0;
       if (slabs == 1) {
         if (it.nck != 0 && owner) {
+#pragma unroll
+          for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
+            const uint32_t mm = kHasLo ? tl : 2 * tl + j;
+            if (mm >= p.m) continue;
+            const float a0 = acc[0][kHasLo ? 0 : j], a1 = acc[0][kHasLo ? 1 : 2 + j];
+            const float b0 = acc[1][kHasLo ? 0 : j], b1 = acc[1][kHasLo ? 1 : 2 + j];
+            if (swiglu) {
+              const uint32_t row = local_row + g;
+              out[static_cast<size_t>(mm) * n_i + row] =
+                  silu_mul(fmaf(a0, kUnscale, bias_pre[0]), fmaf(b0, kUnscale, bias_pre[2]));
+              out[static_cast<size_t>(mm) * n_i + row + 8] =
+                  silu_mul(fmaf(a1, kUnscale, bias_pre[1]), fmaf(b1, kUnscale, bias_pre[3]));
+            } else {
+              const uint32_t base = mm * n_i + local_row + g;
+              val[cnt] = a0; off[cnt] = base;      bsv[cnt] = bias_pre[0]; ++cnt;
+              val[cnt] = a1; off[cnt] = base + 8;  bsv[cnt] = bias_pre[1]; ++cnt;
+              val[cnt] = b0; off[cnt] = base + 16; bsv[cnt] = bias_pre[2]; ++cnt;
+              val[cnt] = b1; off[cnt] = base + 24; bsv[cnt] = bias_pre[3]; ++cnt;
+            }
+          }
+        }
+      } else {
+        // K was split over `slabs` warps of this CTA: meet in shared memory, add in slab order.
+        float* mine = red + (static_cast<size_t>(red_buf) * kPlanWarps + warp) * (2 * p.m * 16);
+        if (owner) {
 #pragma unroll
           for (int r = 0; r < 2; ++r)
 #pragma unroll
             for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
               const uint32_t mm = kHasLo ? tl : 2 * tl + j;
               if (mm >= p.m) continue;
-              const uint32_t row = local_row + r * 16 + g;
-              out[static_cast<size_t>(mm) * n_i + row] = fmaf(acc[r][kHasLo ? 0 : j], kUnscale, bias_pre[2 * r]);
-              out[static_cast<size_t>(mm) * n_i + row + 8] = fmaf(acc[r][kHasLo ? 1 : 2 + j], kUnscale, bias_pre[2 * r + 1]);
+              mine[(r * p.m + mm) * 16 + g] = acc[r][kHasLo ? 0 : j];  // zeros when the warp had no chunks
+              mine[(r * p.m + mm) * 16 + g + 8] = acc[r][kHasLo ? 1 : 2 + j];
             }
         }
-        continue;
-      }
-      // K was split over `slabs` warps of this CTA: meet in shared memory, add in slab order.
-      float* mine = red + (static_cast<size_t>(red_buf) * kPlanWarps + warp) * (2 * p.m * 16);
-      if (owner) {
+        __syncthreads();
+        if ((warp & (slabs - 1u)) == 0 && it.valid) {
+          const float* first_slab = mine;
+          const uint32_t slab_stride = 2 * p.m * 16;
+          if (swiglu) {
+            for (uint32_t idx = lane; idx < 16u * p.m; idx += 32) {
+              const uint32_t mm = idx >> 4, rr = idx & 15u;
+              float tg = 0.0f, tu = 0.0f;
+              for (uint32_t sl = 0; sl < slabs; ++sl) {
+                tg += first_slab[static_cast<size_t>(sl) * slab_stride + mm * 16 + rr];
+                tu += first_slab[static_cast<size_t>(sl) * slab_stride + (p.m + mm) * 16 + rr];
+              }
+              const uint32_t row = local_row + rr;
+              out[static_cast<size_t>(mm) * n_i + row] =
+                  silu_mul(fmaf(tg, kUnscale, bias[row]), fmaf(tu, kUnscale, bias2[row]));
+            }
+          } else {
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
-#pragma unroll
-          for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
-            const uint32_t mm = kHasLo ? tl : 2 * tl + j;
-            if (mm >= p.m) continue;
-            mine[(r * p.m + mm) * 16 + g] = acc[r][kHasLo ? 0 : j];  // zeros when the warp had no chunks
-            mine[(r * p.m + mm) * 16 + g + 8] = acc[r][kHasLo ? 1 : 2 + j];
+            for (int i = 0; i < kMaxOut; ++i) {
+              const uint32_t idx = lane + 32u * i;
+              if (idx >= 32u * p.m) break;
+              float total = 0.0f;
+              for (uint32_t sl = 0; sl < slabs; ++sl) total += first_slab[static_cast<size_t>(sl) * slab_stride + idx];
+              const uint32_t r = idx / (p.m * 16), rem = idx - r * (p.m * 16);
+              const uint32_t mm = rem >> 4, row = local_row + r * 16 + (rem & 15u);
+              // idx == lane in the first pass: row r * 16 + (lane & 15) of activation row 0 when m == 1
+              val[cnt] = total;
+              off[cnt] = mm * n_i + row;
+              bsv[cnt] = (i == 0 && p.m == 1) ? bias_pre[0] : bias[row];
+              ++cnt;
+            }
           }
+        }
+        red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
       }
-      __syncthreads();
-      if ((warp & (slabs - 1u)) == 0 && it.valid) {
-        const float* first_slab = mine;
-        for (uint32_t idx = lane; idx < 32u * p.m; idx += 32) {
-          float total = 0.0f;
-          for (uint32_t s = 0; s < slabs; ++s) total += first_slab[static_cast<size_t>(s) * (2 * p.m * 16) + idx];
-          const uint32_t r = idx / (p.m * 16), rem = idx - r * (p.m * 16);
-          const uint32_t mm = rem >> 4, row = local_row + r * 16 + (rem & 15u);
-          // idx == lane in the first pass: row r * 16 + (lane & 15) of activation row 0 when m == 1
-          const float b = (idx == lane && p.m == 1) ? bias_pre[0] : bias[row];
-          out[static_cast<size_t>(mm) * n_i + row] = fmaf(total, kUnscale, b);
+      if (cnt > 0) {
+#pragma unroll
+        for (int i = 0; i < kMaxOut; ++i)
+          if (i < cnt) val[i] *= kUnscale;
+        if (reduce) exchange(val, off, cnt, epoch);
+#pragma unroll
+        for (int i = 0; i < kMaxOut; ++i) {
+          if (i >= cnt) continue;
+          float v = __fadd_rn(val[i], bsv[i]);
+          if (residual != nullptr) v = __fadd_rn(v, residual[off[i]]);
+          out[off[i]] = v;
         }
       }
-      red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
+    }
+  }
+  if (p.fcomm != nullptr && p.reduce_ops != 0) {
+    // the last CTA to get here advances the epoch for the next launch
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const unsigned int finished = atomicAdd(p.fcomm->done, 1u) + 1u;
+      if (finished == gridDim.x) {
+        *reinterpret_cast<volatile unsigned int*>(p.fcomm->done) = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile unsigned int*>(p.fcomm->epoch) = epoch_base + p.reduce_ops;
+      }
     }
   }
 }
@@ -887,6 +1037,9 @@ struct Plan {
   uint32_t k_max = 0;
   bool all_even_chunks = true;  // every op's k is a multiple of 128
   bool all_even_blocks = true;  // every weight has a whole number of 32-row pairs
+  bool any_fused = false;       // some op carries a norm, a SiLU gate, a residual or a cross-rank reduce
+  uint32_t reduce_ops = 0;      // kOpReduce ops recorded
+  const FusedCommDev* fcomm = nullptr;
   bool paired = false;          // plan_pair_kernel: work items are pairs of row blocks
   uint32_t unit_chunks = 1;     // chunks the kernel consumes at a time (slabs are whole units)
   int grid = 0;
@@ -1016,7 +1169,9 @@ cudaError_t configure_any(Plan& plan, int sm_count, bool* fits) {
 void shape_op(PlanOpDev& o, uint32_t grid, uint32_t unit_chunks, bool paired, uint32_t* rot) {
   uint32_t s = 1, log2 = 0;
   const uint32_t units_per_row = o.chunks_per_row / unit_chunks;
-  const uint32_t items = paired ? o.row_blocks / 2 : o.row_blocks;  // what one warp works on per round
+  // what one warp works on per round: a row block, a pair of adjacent ones, or (SiLU gate) the
+  // same block of the gate and of the up weight
+  const uint32_t items = !paired ? o.row_blocks : ((o.flags & kOpSwiglu) ? o.row_blocks : o.row_blocks / 2);
   while (s < static_cast<uint32_t>(kPlanWarps) && s * 2 <= units_per_row &&
          (items + kPlanWarps / s - 1) / (kPlanWarps / s) < (grid * 3) / 5) {
     s *= 2;
@@ -1031,10 +1186,31 @@ void shape_op(PlanOpDev& o, uint32_t grid, uint32_t unit_chunks, bool paired, ui
   *rot = (*rot + o.cta_items) % grid;  // the next op starts where this one left the grid idle
 }
 
-bool fill_op(PlanOpDev& o, int count, const LinearTarget* targets, const void* x, const char** why) {
+bool fill_op(PlanOpDev& o, int count, const LinearTarget* targets, const void* x, const LinearFusion& fusion,
+             const char** why) {
   o = PlanOpDev{};
   o.count = static_cast<uint32_t>(count);
   const Weight& w0 = *targets[0].w;
+  if (fusion.swiglu) {
+    if (count != 2 || targets[0].w->n != targets[1].w->n) {
+      *why = "the SiLU gate takes exactly two weights (gate, up) with the same number of rows";
+      return false;
+    }
+    if (fusion.reduce || fusion.residual != nullptr) {
+      *why = "the SiLU gate combines with a norm only";
+      return false;
+    }
+    o.flags |= kOpSwiglu;
+  }
+  if (fusion.reduce || fusion.residual != nullptr) {
+    if (count != 1) {
+      *why = "a residual or a cross-rank reduce goes with a single weight";
+      return false;
+    }
+    if (fusion.reduce) o.flags |= kOpReduce;
+  }
+  o.norm_weight = fusion.norm_weight;
+  o.norm_eps = fusion.norm_eps;
   uint32_t rb = 0;
   for (int i = 0; i < count; ++i) {
     const Weight& w = *targets[i].w;
@@ -1049,10 +1225,12 @@ bool fill_op(PlanOpDev& o, int count, const LinearTarget* targets, const void* x
     o.w[i] = static_cast<const uint8_t*>(w.data);
     o.bias[i] = targets[i].bias;
     o.out[i] = targets[i].out;
+    o.residual[i] = i == 0 ? fusion.residual : nullptr;
     o.n[i] = w.n;
     o.rb_begin[i] = rb;
     rb += w.n / 16;
   }
+  if (fusion.swiglu) rb = w0.n / 16;  // items are counted in blocks of ONE of the two weights
   for (int i = count; i <= kMaxMulti; ++i) o.rb_begin[i] = rb;
   o.x = x;
   o.k = w0.k;
@@ -1090,13 +1268,20 @@ const char* plan_add_copy(Plan* plan, bool to_device, void* device, void* host, 
 
 // Returns an empty string when the op was recorded, else why the fused kernel cannot run it.
 const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, const void* x, int x_dtype,
-                            uint32_t m) {
+                            uint32_t m, const LinearFusion& fusion) {
   if (!plan->after.empty()) return "a host read was recorded before this linear; reads must come after the last op";
   if (m < 1 || m > 16) return "the fused plan kernel covers 1..16 activation rows";
   if (count < 1 || count > kMaxMulti) return "too many weights in one op";
   PlanOpDev o;
   const char* why = "";
-  if (!fill_op(o, count, targets, x, &why)) return why;
+  if (!fill_op(o, count, targets, x, fusion, &why)) return why;
+  if (o.flags & kOpReduce) {
+    if (static_cast<uint64_t>(m) * o.n[0] * 8u > kFusedSlotBytes)
+      return "a cross-rank reduce inside a plan exchanges at most 8192 outputs per op";
+    o.reduce_index = plan->reduce_ops;
+    plan->reduce_ops += 1;
+  }
+  if (o.flags != 0 || o.norm_weight != nullptr || o.residual[0] != nullptr) plan->any_fused = true;
   const int scale_dtype = targets[0].w->scale_dtype;
   if (plan->ops.empty()) {
     plan->m = m;
@@ -1107,7 +1292,8 @@ const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, 
   }
   plan->k_max = std::max(plan->k_max, o.k);
   plan->all_even_chunks = plan->all_even_chunks && o.chunks_per_row % 2 == 0;
-  for (int i = 0; i < count; ++i) plan->all_even_blocks = plan->all_even_blocks && targets[i].w->n % 32 == 0;
+  if (!(o.flags & kOpSwiglu))
+    for (int i = 0; i < count; ++i) plan->all_even_blocks = plan->all_even_blocks && targets[i].w->n % 32 == 0;
   plan->ops.push_back(o);
   return "";
 }
@@ -1126,6 +1312,18 @@ cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why) {
   if (!fits) {
     *why = "the staged activations of the widest op (k * columns * 2 bytes) do not fit in shared memory next to the weight rings";
     return cudaErrorInvalidValue;
+  }
+  if (plan->any_fused && !plan->paired) {
+    *why = "ops with a norm, a SiLU gate, a residual or a cross-rank reduce need the paired kernel: at most two "
+           "f32 / bf16 rows (four binary16 rows) and weights with a whole number of 32-row pairs";
+    return cudaErrorInvalidValue;
+  }
+  if (plan->reduce_ops != 0) {
+    if (env.fused == nullptr) {
+      *why = "the plan holds a cross-rank reduce but the context has no connected exchange (kq_comm_connect)";
+      return cudaErrorInvalidValue;
+    }
+    plan->fcomm = env.fused;
   }
   uint32_t rot = 0;
   for (PlanOpDev& o : plan->ops) shape_op(o, static_cast<uint32_t>(plan->grid), plan->unit_chunks, plan->paired, &rot);
@@ -1155,6 +1353,8 @@ cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
   p.xs_bytes = plan->xs_bytes;
   p.grid_bar = plan->grid_bar;
   p.status = plan->status_dev;
+  p.fcomm = plan->fcomm;
+  p.reduce_ops = plan->reduce_ops;
   void* args[] = {&p};
   e = cudaLaunchCooperativeKernel(plan->kernel, dim3(plan->grid), dim3(kPlanWarps * 32), args, plan->smem, env.stream);
   if (e != cudaSuccess) return e;
@@ -1183,7 +1383,7 @@ constexpr size_t kStaticBarOff = 0;
 constexpr size_t kStaticStatusOff = 256;
 constexpr size_t kStaticOpOff = 512;
 constexpr size_t kStaticTotal = 4096;
-static_assert(sizeof(PlanOpDev) <= 512, "op descriptor outgrew its slot");
+static_assert(sizeof(PlanOpDev) <= 512 && sizeof(PlanOpDev) % 4 == 0, "op descriptor outgrew its slot");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticTotal];
 
@@ -1218,7 +1418,7 @@ cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, cons
     return cudaErrorInvalidValue;
   }
   PlanOpDev o;
-  if (!fill_op(o, 1, &target, x, why)) return cudaErrorInvalidValue;
+  if (!fill_op(o, 1, &target, x, LinearFusion{}, why)) return cudaErrorInvalidValue;
   unsigned char* base = nullptr;
   cudaError_t e = static_scratch_for_current_device(&base);
   if (e != cudaSuccess) return e;

@@ -222,6 +222,64 @@ class Gpu:
             arr(*[b.data_ptr() for b in biases]), arr(*[o.data_ptr() for o in outs]), m))
         return outs
 
+    # -- the matmul's neighbours in a decoder layer -------------------------------------------
+    def rms_norm(self, x, weight, eps: float, out=None):
+        """out = x * rsqrt(mean(x^2, last dim) + eps) * weight, f32 (the reference's rms_norm op)."""
+        torch = _torch()
+        if x.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != x.shape[-1]:
+            raise KqError(2, "rms_norm takes f32 x [..., dim] and an f32 weight [dim]")
+        x = x.contiguous()
+        dim = x.shape[-1]
+        if out is None:
+            out = torch.empty_like(x)
+        self._check(L.kq_rms_norm(self._ctx, x.data_ptr(), weight.data_ptr(), float(eps), out.data_ptr(),
+                                  x.numel() // dim if dim else 0, dim))
+        return out
+
+    def silu_mul(self, gate, up, out=None):
+        """out = (gate * sigmoid(gate)) * up, f32 elementwise (the reference's SiLU pair followed by mul)."""
+        torch = _torch()
+        if gate.dtype != torch.float32 or up.dtype != torch.float32 or gate.shape != up.shape:
+            raise KqError(2, "silu_mul takes two f32 tensors of one shape")
+        if out is None:
+            out = torch.empty_like(gate)
+        self._check(L.kq_silu_mul(self._ctx, gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel()))
+        return out
+
+    def add(self, a, b, out=None):
+        torch = _torch()
+        if a.dtype != torch.float32 or b.dtype != torch.float32 or a.shape != b.shape:
+            raise KqError(2, "add takes two f32 tensors of one shape")
+        if out is None:
+            out = torch.empty_like(a)
+        self._check(L.kq_add(self._ctx, a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel()))
+        return out
+
+    def linear_fused(self, x, weights, biases, outs=None, norm_weight=None, eps: float = 0.0, residual=None,
+                     swiglu: bool = False, reduce: bool = False):
+        """[rms_norm ->] linear(s) [-> silu(gate) * up] [-> sum over ranks] [-> + residual] (kq_linear_fused).
+        `weights` / `biases` are lists; with swiglu=True they are (gate, up) and there is one output."""
+        torch = _torch()
+        x = x.contiguous()
+        k = weights[0].k
+        if x.shape[-1] != k:
+            raise KqError(2, f"linear_fused: x[..., {x.shape[-1]}] does not match k={k}")
+        m = x.numel() // k if k else 0
+        n_out = 1 if swiglu else len(weights)
+        if outs is None:
+            outs = [torch.empty(tuple(x.shape[:-1]) + (weights[i].n,), dtype=torch.float32, device=x.device)
+                    for i in range(n_out)]
+        cnt = len(weights)
+        arr = ctypes.c_uint64 * cnt
+        out_ptrs = [outs[i].data_ptr() if i < len(outs) else 0 for i in range(cnt)]
+        flags = (1 if swiglu else 0) | (2 if reduce else 0)
+        self._check(L.kq_linear_fused(
+            self._ctx, cnt, arr(*[w.handle for w in weights]), x.data_ptr(), _tensor_dtype_code(x),
+            norm_weight.data_ptr() if norm_weight is not None else 0, float(eps),
+            arr(*[b.data_ptr() for b in biases]), residual.data_ptr() if residual is not None else 0,
+            arr(*out_ptrs), m, flags))
+        return outs
+
     def linear_host(self, x: np.ndarray, weight: Weight, bias) -> np.ndarray:
         """Host-buffer round trip: numpy x in, numpy f32 out (copies inside the call)."""
         x = np.ascontiguousarray(x)

@@ -27,7 +27,7 @@ def _worker(rank, world, port, out_dir):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     import karume_b200 as kb
     import oracle
-    from karume_b200.decode_step import SMALL, DecodeStep
+    from bench_workload import SMALL_TP as SMALL, DecodeStep, reference_step
     results = []
     gpu = kb.acquire_gpu(rank)
     gpu.connect_ranks(rank, world, 256 * 1024)
@@ -117,20 +117,33 @@ def _worker(rank, world, port, out_dir):
     torch.cuda.synchronize()
     dist.barrier()
     gpu.destroy()
-    # 3. tensor-parallel decode step (column / row shards + libkq all-reduce) vs the oracle
-    from tests.test_gpu_decode_step import reference_step
-    gpu2 = kb.acquire_gpu(rank)
-    step = DecodeStep(gpu2, SMALL, 2, rank=rank, world=world, seed=3, keep_host_weights=True, exchange="kq")
-    step.record()
+    # 3. tensor-parallel decode step vs the oracle: as one fused plan per rank (the exchange
+    # inside the persistent kernel) and as a graph of separate launches (kq_linear_reduce)
     x = np.random.default_rng(0).standard_normal((2, SMALL.hidden)).astype(np.float32)
-    ref = reference_step(step, x)
-    step.host_x[...] = x
-    dist.barrier()
-    step.run_host()
-    step.sync()
+    _, ref = reference_step(SMALL, 3, x)
     shard = SMALL.vocab // world
-    rep = oracle.allclose(step.host_logits, ref[:, rank * shard:(rank + 1) * shard], atol=1e-5, rtol=1e-3)
-    results.append(("tp_decode_step", rep["pass"]))
+    gpu2 = kb.acquire_gpu(rank)
+    first_step = None
+    for name, fused in (("tp_decode_step_plan", True), ("tp_decode_step_graph", False)):
+        step = DecodeStep(gpu2, SMALL, 2, rank=rank, world=world, seed=3, fused=fused, exchange="kq",
+                          share_weights_with=first_step)
+        first_step = first_step or step
+        step.record()
+        good = True
+        for _ in range(3):
+            step.host_x[...] = x
+            step.host_logits[...] = 0
+            dist.barrier()
+            step.run_host()
+            step.sync()
+            want = ref[:, rank * shard:(rank + 1) * shard]
+            mag = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+            good = good and oracle.allclose(step.host_logits, want, atol=1e-5 * max(1.0, mag), rtol=1e-3)["pass"]
+            # every rank holds the same h (the exchange adds in rank order)
+            every = [torch.empty_like(step.h) for _ in range(world)]
+            dist.all_gather(every, step.h)
+            good = good and all(bool(torch.equal(every[0], e)) for e in every[1:])
+        results.append((name, good))
     dist.barrier()
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
         f.write(" ".join(f"{name}={int(v)}" for name, v in results))
@@ -149,4 +162,4 @@ def test_all_reduce_and_tensor_parallel_step(tmp_path, world):
     for rank in range(world):
         path = tmp_path / f"rank{rank}.txt"
         assert path.exists(), f"rank {rank} did not finish"
-        assert open(path).read() == "all_reduce=1 graph_replay=1 linear_reduce=1 tp_decode_step=1"
+        assert open(path).read() == "all_reduce=1 graph_replay=1 linear_reduce=1 tp_decode_step_plan=1 tp_decode_step_graph=1"
