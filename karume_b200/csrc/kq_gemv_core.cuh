@@ -94,9 +94,9 @@ __device__ __forceinline__ float absmax8(const float (&v)[8]) {
 //          k-octet are stored in the order 0,4,1,5,2,6,3,7, and the odd ones (1,3,5,7)
 //          are stored divided by 16: their nibbles reach the MMA as u * 2^-20 instead
 //          of u * 2^-24.  Every value is pre-scaled by the 2^e of its (row, group), see above.
-//   corr : kPerGroup  : [local group][kCorrStride] float2; entry r =
-//                       { -8 * 2^-24 * (sum of the group's x of activation row r, as staged),
-//                         2^-e of that (row, group) }
+//   corr : kPerGroup  : [local group][kCorrStride] float2; entry r = { c, 2^-e } of that
+//                       (row, group), c = -8 * 2^-24 * 2^-e * (sum of the group's x of activation
+//                       row r, as staged): a group's partial sum is fma(mma sum, 2^-e, c)
 //          !kPerGroup : [local group][kCorrStride] f32, the first of the two only; the
 //                       caller passes one scale per activation row in row_scale
 // Four consecutive threads share one (group, row): each converts one octet.
@@ -151,7 +151,7 @@ __device__ __forceinline__ void stage_octet(const float (&v)[8], bool valid, uin
     if constexpr (kHasLo) *reinterpret_cast<uint4*>(xs + off + (lo_offset == 0 ? 64u : lo_offset)) = lo4;
     if (q == 0) {
       if constexpr (kPerGroup)
-        reinterpret_cast<float2*>(corr)[lg * kCorrStride + row] = make_float2(sum * (-8.0f / kUnscale), ps.inv);
+        reinterpret_cast<float2*>(corr)[lg * kCorrStride + row] = make_float2(sum * (-8.0f / kUnscale) * ps.inv, ps.inv);
       else
         corr[lg * kCorrStride + row] = sum * (-8.0f / kUnscale);
     }
@@ -195,10 +195,10 @@ __device__ __forceinline__ void stage_x(const XT* __restrict__ x, uint32_t m, ui
 // is what gets staged.  The sum of squares of a row is taken over the CTA: every thread adds
 // the squares of its own octets in ascending order, a warp adds its lanes with the shuffle
 // tree, and the warps' sums are added in warp order, so every CTA that stages the same x
-// computes the same bits.  `red` is [warps][m] floats of shared memory, `inv` is [m].
+// computes the same bits.  `red` is [warps][m] floats of shared memory (`inv` is unused).
 // When the block fits one round (items <= threads * kBatch, every decode shape) the octets
 // stay in registers between the two passes; otherwise x is read a second time.
-template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2, int kBatch>
+template <typename XT, bool kHasLo, int kCorrStride, bool kFromL2, int kBatch, int kMaxRows>
 __device__ __forceinline__ void stage_x_rms_norm(const XT* __restrict__ x, const float* __restrict__ weight, float eps,
                                                  uint32_t m, uint32_t k, uint8_t* xs, uint32_t xs_stride, float* corr,
                                                  float* red, float* inv) {
@@ -208,9 +208,9 @@ __device__ __forceinline__ void stage_x_rms_norm(const XT* __restrict__ x, const
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
   const bool one_round = items_padded <= blockDim.x * kBatch;
   float v[kBatch][8];
-  float sq[16];
+  float sq[kMaxRows];  // m <= kMaxRows
 #pragma unroll
-  for (int r = 0; r < 16; ++r) sq[r] = 0.0f;
+  for (int r = 0; r < kMaxRows; ++r) sq[r] = 0.0f;
   for (uint32_t base = threadIdx.x; base < items_padded; base += blockDim.x * kBatch) {
 #pragma unroll
     for (int b = 0; b < kBatch; ++b) {
@@ -225,25 +225,29 @@ __device__ __forceinline__ void stage_x_rms_norm(const XT* __restrict__ x, const
 #pragma unroll
         for (int e = 0; e < 8; ++e) s = fmaf(v[b][e], v[b][e], s);
 #pragma unroll
-        for (int r = 0; r < 16; ++r)
+        for (int r = 0; r < kMaxRows; ++r)
           if (static_cast<uint32_t>(r) == row) sq[r] += s;
       }
     }
   }
+  // the norm weights of the thread's first octet travel while the sums of squares meet
+  float wv0[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (threadIdx.x < items) {
+    const uint32_t lg0 = (threadIdx.x >> 2) / m, q0 = threadIdx.x & 3u;
+    const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + (lg0 << 5) + (q0 << 3)));
+    const float4 w1 = __ldg(reinterpret_cast<const float4*>(weight + (lg0 << 5) + (q0 << 3) + 4));
+    wv0[0] = w0.x; wv0[1] = w0.y; wv0[2] = w0.z; wv0[3] = w0.w;
+    wv0[4] = w1.x; wv0[5] = w1.y; wv0[6] = w1.z; wv0[7] = w1.w;
+  }
 #pragma unroll
-  for (int r = 0; r < 16; ++r) {
+  for (int r = 0; r < kMaxRows; ++r) {
     if (static_cast<uint32_t>(r) < m) {  // uniform
       const float total = warp_sum(sq[r]);
       if (lane == 0) red[warp * m + r] = total;
     }
   }
   __syncthreads();
-  if (threadIdx.x < m) {
-    float total = 0.0f;
-    for (uint32_t w = 0; w < warps; ++w) total += red[w * m + threadIdx.x];
-    inv[threadIdx.x] = rsqrtf(total * (1.0f / static_cast<float>(k)) + eps);
-  }
-  __syncthreads();
+  (void)inv;
   for (uint32_t base = threadIdx.x; base < items_padded; base += blockDim.x * kBatch) {
 #pragma unroll
     for (int b = 0; b < kBatch; ++b) {
@@ -255,10 +259,21 @@ __device__ __forceinline__ void stage_x_rms_norm(const XT* __restrict__ x, const
       if (valid) {
         if (!one_round)
           load_x8<XT, kFromL2>(x + static_cast<size_t>(row) * k + (static_cast<size_t>(lg) << 5) + (q << 3), v[b]);
-        const float r_inv = inv[row];
-        const float4 w0 = *reinterpret_cast<const float4*>(weight + (lg << 5) + (q << 3));
-        const float4 w1 = *reinterpret_cast<const float4*>(weight + (lg << 5) + (q << 3) + 4);
-        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        // every thread adds the warps' sums of its row itself, in warp order: the same bits in
+        // every thread and in every CTA
+        float total = 0.0f;
+        for (uint32_t w = 0; w < warps; ++w) total += red[w * m + row];
+        const float r_inv = rsqrtf(total * (1.0f / static_cast<float>(k)) + eps);
+        float wv[8];
+        if (item == threadIdx.x) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) wv[e] = wv0[e];
+        } else {
+          const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + (lg << 5) + (q << 3)));
+          const float4 w1 = __ldg(reinterpret_cast<const float4*>(weight + (lg << 5) + (q << 3) + 4));
+          wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w;
+          wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[b][e] = __fmul_rn(__fmul_rn(v[b][e], r_inv), wv[e]);
       }

@@ -21,6 +21,7 @@
 //     launch).  Every wait in this file is bounded: if one gives up, the kernel records a
 //     status word, keeps going without blocking, and the host reports KQ_ERR_TIMEOUT.
 #include <algorithm>
+#include <climits>
 #include <type_traits>
 #include <utility>
 #include <vector>
@@ -358,13 +359,13 @@ plan_kernel(const PlanParams p) {
               mma_f16(cf, a1, bset[j].z, bset[j].w);
             }
             if constexpr (kHasLo) {
-              acc[0][0] = fmaf(s.x, ((cf[0] + cf[1]) + gterm[0]) * ginv[0], acc[0][0]);
-              acc[0][1] = fmaf(s.y, ((cf[2] + cf[3]) + gterm[0]) * ginv[0], acc[0][1]);
+              acc[0][0] = fmaf(s.x, fmaf(cf[0] + cf[1], ginv[0], gterm[0]), acc[0][0]);
+              acc[0][1] = fmaf(s.y, fmaf(cf[2] + cf[3], ginv[0], gterm[0]), acc[0][1]);
             } else {
-              acc[0][0] = fmaf(s.x, (cf[0] + gterm[0]) * ginv[0], acc[0][0]);
-              acc[0][1] = fmaf(s.x, (cf[1] + gterm[1]) * ginv[1], acc[0][1]);
-              acc[0][2] = fmaf(s.y, (cf[2] + gterm[0]) * ginv[0], acc[0][2]);
-              acc[0][3] = fmaf(s.y, (cf[3] + gterm[1]) * ginv[1], acc[0][3]);
+              acc[0][0] = fmaf(s.x, fmaf(cf[0], ginv[0], gterm[0]), acc[0][0]);
+              acc[0][1] = fmaf(s.x, fmaf(cf[1], ginv[1], gterm[1]), acc[0][1]);
+              acc[0][2] = fmaf(s.y, fmaf(cf[2], ginv[0], gterm[0]), acc[0][2]);
+              acc[0][3] = fmaf(s.y, fmaf(cf[3], ginv[1], gterm[1]), acc[0][3]);
             }
           }
         } else {
@@ -412,13 +413,13 @@ plan_kernel(const PlanParams p) {
               mma_f16_zero(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y);
               mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
               if constexpr (kHasLo) {
-                acc[tile_m][0] = fmaf(s.x, ((cf[0] + cf[1]) + cterm[tile_m][0]) * cinv[tile_m][0], acc[tile_m][0]);
-                acc[tile_m][1] = fmaf(s.y, ((cf[2] + cf[3]) + cterm[tile_m][0]) * cinv[tile_m][0], acc[tile_m][1]);
+                acc[tile_m][0] = fmaf(s.x, fmaf(cf[0] + cf[1], cinv[tile_m][0], cterm[tile_m][0]), acc[tile_m][0]);
+                acc[tile_m][1] = fmaf(s.y, fmaf(cf[2] + cf[3], cinv[tile_m][0], cterm[tile_m][0]), acc[tile_m][1]);
               } else {
-                acc[tile_m][0] = fmaf(s.x, (cf[0] + cterm[tile_m][0]) * cinv[tile_m][0], acc[tile_m][0]);
-                acc[tile_m][1] = fmaf(s.x, (cf[1] + cterm[tile_m][1]) * cinv[tile_m][1], acc[tile_m][1]);
-                acc[tile_m][2] = fmaf(s.y, (cf[2] + cterm[tile_m][0]) * cinv[tile_m][0], acc[tile_m][2]);
-                acc[tile_m][3] = fmaf(s.y, (cf[3] + cterm[tile_m][1]) * cinv[tile_m][1], acc[tile_m][3]);
+                acc[tile_m][0] = fmaf(s.x, fmaf(cf[0], cinv[tile_m][0], cterm[tile_m][0]), acc[tile_m][0]);
+                acc[tile_m][1] = fmaf(s.x, fmaf(cf[1], cinv[tile_m][1], cterm[tile_m][1]), acc[tile_m][1]);
+                acc[tile_m][2] = fmaf(s.y, fmaf(cf[2], cinv[tile_m][0], cterm[tile_m][0]), acc[tile_m][2]);
+                acc[tile_m][3] = fmaf(s.y, fmaf(cf[3], cinv[tile_m][1], cterm[tile_m][1]), acc[tile_m][3]);
               }
             }
           }
@@ -540,9 +541,152 @@ __device__ __forceinline__ void lds_v2f_if_at(float& a, float& b, uint32_t base,
                : "+f"(a), "+f"(b) : "r"(base), "r"(static_cast<uint32_t>(pred)), "n"(kOff));
 }
 
+// ---- finishing the outputs of ops with fused neighbours ---------------------------------
+// out = partial sum (scaled back) [summed over the ranks] + bias [+ residual], each addition
+// rounded to f32 like the reference's node sequence linear -> add; or silu(gate) * up.
+//
+// Cross-rank sum (kOpReduce): every lane PUSHES its finished partial sums into the exchange
+// area of every peer as {value, epoch} entries (slot = epoch parity, source = this rank), then
+// polls (bounded) its own area until the peers' entries carry this epoch and adds the ranks'
+// values in rank order, so all ranks hold the same bits.  The k-th reduce op of a launch uses
+// epoch base + 1 + k, where base is what the previous launch (of a plan or of kq_linear_reduce)
+// left in the exchange area; the last CTA of a launch advances it.  Entries of consecutive
+// epochs alternate between two slots, and the grid barrier between ops keeps every rank within
+// one exchange of its peers, so an unread entry is never overwritten.
+constexpr int kFinish = 4;  // outputs finished per call
+__device__ __forceinline__ void exchange_sum(const FusedCommDev* fcp, int* status, unsigned int epoch,
+                                             float (&val)[kFinish], const uint32_t (&off)[kFinish], uint32_t vmask) {
+  const FusedCommDev& fc = *fcp;
+  const uint32_t me = fc.rank, world = fc.world;
+  const uint64_t slot_entries = kFusedSlotBytes / 8;
+  const uint64_t parity_base = static_cast<uint64_t>(epoch & 1u) * kFusedMaxWorld;
+  for (uint32_t r = 0; r < world; ++r) {
+    if (r == me) continue;
+    uint2* dst = reinterpret_cast<uint2*>(fc.base[r] + fc.data_off) + (parity_base + me) * slot_entries;
+#pragma unroll
+    for (int i = 0; i < kFinish; ++i)
+      if (vmask & (1u << i)) st_exchange_entry(dst + off[i], val[i], epoch);
+  }
+#pragma unroll
+  for (int i = 0; i < kFinish; ++i) {
+    if (!(vmask & (1u << i))) continue;
+    float sum = 0.0f;
+    for (uint32_t r = 0; r < world; ++r) {
+      if (r == me) {
+        sum += val[i];
+        continue;
+      }
+      const uint2* src = reinterpret_cast<const uint2*>(fc.base[me] + fc.data_off) + (parity_base + r) * slot_entries + off[i];
+      uint2 e;
+      uint32_t spins = 0;
+      while (true) {
+        e = ld_exchange_entry(src);
+        if (e.y == epoch) break;
+        if (++spins > kSpinLimit) {
+          *reinterpret_cast<volatile int*>(status) = 3;
+          break;
+        }
+      }
+      sum += __uint_as_float(e.x);
+    }
+    val[i] = sum;
+  }
+}
+
+__device__ __forceinline__ void finish_values(const PlanOpDev* o, uint32_t wi, float (&val)[kFinish],
+                                              const uint32_t (&off)[kFinish], const float (&bsv)[kFinish], uint32_t vmask,
+                                              const FusedCommDev* fc, int* status, bool have_residual0 = false,
+                                              float residual0 = 0.0f) {
+  if (vmask == 0) return;
+#pragma unroll
+  for (int i = 0; i < kFinish; ++i) val[i] *= kUnscale;
+  if (o->flags & kOpReduce) {
+    // the epoch word keeps the launch's base until the last CTA of the launch has finished
+    const unsigned int epoch_base = *reinterpret_cast<volatile unsigned int*>(fc->epoch);
+    exchange_sum(fc, status, epoch_base + 1u + o->reduce_index, val, off, vmask);
+  }
+  const float* residual = o->residual[wi];
+  float* out = o->out[wi];
+#pragma unroll
+  for (int i = 0; i < kFinish; ++i) {
+    if (!(vmask & (1u << i))) continue;
+    float v = __fadd_rn(val[i], bsv[i]);
+    if (residual != nullptr) v = __fadd_rn(v, (i == 0 && have_residual0) ? residual0 : residual[off[i]]);
+    out[off[i]] = v;
+  }
+}
+
+// One lane's outputs of an unsplit pair: rows `row`, row + 8 of the first block (a0, a1) and of
+// the second block (b0, b1) for activation row mm.  For the SiLU gate the first block is the
+// gate and the second the up projection of the same 16 output rows.
+__device__ __noinline__ void finish_fused_lane(const PlanOpDev* o, uint32_t wi, uint32_t mm, uint32_t row, float a0, float a1,
+                                               float b0, float b1, float bias0, float bias1, float bias2, float bias3,
+                                               const FusedCommDev* fc, int* status) {
+  const uint32_t n_i = o->n[wi];
+  if (o->flags & kOpSwiglu) {
+    float* dst = o->out[0] + static_cast<size_t>(mm) * n_i + row;
+    dst[0] = silu_mul(fmaf(a0, kUnscale, bias0), fmaf(b0, kUnscale, bias2));
+    dst[8] = silu_mul(fmaf(a1, kUnscale, bias1), fmaf(b1, kUnscale, bias3));
+    return;
+  }
+  const uint32_t base = mm * n_i + row;
+  float val[kFinish] = {a0, a1, b0, b1};
+  const uint32_t off[kFinish] = {base, base + 8, base + 16, base + 24};
+  const float bsv[kFinish] = {bias0, bias1, bias2, bias3};
+  finish_values(o, wi, val, off, bsv, 0xFu, fc, status);
+}
+
+// The reducing warp of a pair whose K range was split over `slabs` warps: adds the slabs' partial
+// sums ([slab][block][m][16] in shared memory) in slab order and finishes the 32 (SiLU gate: 16)
+// output rows x m.
+__device__ __noinline__ void finish_fused_slabs(const PlanOpDev* o, uint32_t wi, const float* first_slab, uint32_t slabs,
+                                                uint32_t m, uint32_t local_row, uint32_t lane, float bias_lane,
+                                                float residual_lane, const FusedCommDev* fc, int* status) {
+  const uint32_t n_i = o->n[wi], slab_stride = 2 * m * 16;
+  if (o->flags & kOpSwiglu) {
+    const float* bias_g = o->bias[0];
+    const float* bias_u = o->bias[1];
+    for (uint32_t idx = lane; idx < 16u * m; idx += 32) {
+      const uint32_t mm = idx >> 4, rr = idx & 15u;
+      float tg = 0.0f, tu = 0.0f;
+      for (uint32_t sl = 0; sl < slabs; ++sl) {
+        tg += first_slab[static_cast<size_t>(sl) * slab_stride + mm * 16 + rr];
+        tu += first_slab[static_cast<size_t>(sl) * slab_stride + (m + mm) * 16 + rr];
+      }
+      const uint32_t row = local_row + rr;
+      o->out[0][static_cast<size_t>(mm) * n_i + row] = silu_mul(fmaf(tg, kUnscale, bias_g[row]), fmaf(tu, kUnscale, bias_u[row]));
+    }
+    return;
+  }
+  const float* bias = o->bias[wi];
+  for (uint32_t first = 0; first < 32u * m; first += 32u * kFinish) {
+    float val[kFinish], bsv[kFinish];
+    uint32_t off[kFinish];
+    uint32_t vmask = 0;
+#pragma unroll
+    for (int i = 0; i < kFinish; ++i) {
+      const uint32_t idx = first + lane + 32u * i;
+      val[i] = 0.0f;
+      bsv[i] = 0.0f;
+      off[i] = 0u;
+      if (idx < 32u * m) {
+        float total = 0.0f;
+        for (uint32_t sl = 0; sl < slabs; ++sl) total += first_slab[static_cast<size_t>(sl) * slab_stride + idx];
+        const uint32_t r = idx / (m * 16), rem = idx - r * (m * 16);
+        const uint32_t mm = rem >> 4, row = local_row + r * 16 + (rem & 15u);
+        val[i] = total;
+        off[i] = mm * n_i + row;
+        bsv[i] = (m == 1 && idx == lane) ? bias_lane : bias[row];  // fetched before the weights were consumed
+        vmask |= 1u << i;
+      }
+    }
+    finish_values(o, wi, val, off, bsv, vmask, fc, status, m == 1 && first == 0, residual_lane);
+  }
+}
+
 struct PairItem {
   const uint8_t* src;  // first chunk of the slab of the pair's first row block
-  int64_t row_stride;  // bytes from a chunk of the first block to the same chunk of the second
+  int32_t row_stride16;  // 16-byte units from a chunk of the first block to the same chunk of the second
   uint32_t nck;        // chunks in the slab (0: nothing to do)
   uint32_t c0;         // first chunk index inside the row
   uint32_t rb;         // first row block of the pair, inside the op
@@ -555,7 +699,7 @@ __device__ __forceinline__ PairItem pair_item_of(const PlanOpDev& o, uint32_t ro
                                                  uint32_t cta) {
   PairItem it;
   it.src = nullptr;
-  it.row_stride = 0;
+  it.row_stride16 = 0;
   it.nck = 0;
   it.c0 = 0;
   it.rb = 0;
@@ -581,7 +725,9 @@ __device__ __forceinline__ PairItem pair_item_of(const PlanOpDev& o, uint32_t ro
   it.c0 = slab * o.chunks_per_slab;
   if (it.c0 >= o.chunks_per_row) return it;
   it.nck = min(o.chunks_per_slab, o.chunks_per_row - it.c0);
-  it.row_stride = swiglu ? static_cast<int64_t>(o.w[1] - o.w[0]) : static_cast<int64_t>(o.chunks_per_row) * kCB;
+  // (device allocations are 256-byte aligned and chunks are multiples of 16 bytes; the host
+  // checks that the distance between a gate and an up weight fits 32 bits of such units)
+  it.row_stride16 = swiglu ? static_cast<int32_t>((o.w[1] - o.w[0]) / 16) : static_cast<int32_t>(o.chunks_per_row * (kCB / 16));
   it.src = o.w[it.wi] + (static_cast<size_t>(it.rb - o.rb_begin[it.wi]) * o.chunks_per_row + it.c0) * kCB;
   return it;
 }
@@ -645,7 +791,7 @@ plan_pair_kernel(const PlanParams p) {
 
   // ---- producer -------------------------------------------------------------------------
   uint32_t prod_op = 0, prod_round = 0, prod_q = 0, prod_left = 0;
-  int64_t prod_stride = 0;
+  int32_t prod_stride16 = 0;
   const uint8_t* prod_src = nullptr;
   auto produce = [&]() {
     while (prod_left == 0) {  // move to this warp's next item, whatever op it belongs to
@@ -660,14 +806,15 @@ plan_pair_kernel(const PlanParams p) {
       prod_round += 1;
       prod_left = it.nck;
       prod_src = it.src;
-      prod_stride = it.row_stride;
+      prod_stride16 = it.row_stride16;
     }
     const uint32_t nc = min(static_cast<uint32_t>(kPiece), prod_left);
     const uint32_t slot = prod_q & 1u;
     if (lane == 0) {
       mbar_expect_tx(bars + slot * 8, 2u * nc * kCB);
       bulk_copy_g2s(ring + slot * kSlotBytes, prod_src, nc * kCB, bars + slot * 8);
-      bulk_copy_g2s(ring + slot * kSlotBytes + kPiece * kCB, prod_src + prod_stride, nc * kCB, bars + slot * 8);
+      bulk_copy_g2s(ring + slot * kSlotBytes + kPiece * kCB, prod_src + static_cast<int64_t>(prod_stride16) * 16, nc * kCB,
+                    bars + slot * 8);
     }
     prod_src += nc * kCB;
     prod_left -= nc;
@@ -745,60 +892,14 @@ plan_pair_kernel(const PlanParams p) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       if constexpr (kHasLo) {
-        acc[r][0] = fmaf(sc[r].x, ((cf[r][0] + cf[r][1]) + gterm[0]) * ginv[0], acc[r][0]);
-        acc[r][1] = fmaf(sc[r].y, ((cf[r][2] + cf[r][3]) + gterm[0]) * ginv[0], acc[r][1]);
+        acc[r][0] = fmaf(sc[r].x, fmaf(cf[r][0] + cf[r][1], ginv[0], gterm[0]), acc[r][0]);
+        acc[r][1] = fmaf(sc[r].y, fmaf(cf[r][2] + cf[r][3], ginv[0], gterm[0]), acc[r][1]);
       } else {
-        acc[r][0] = fmaf(sc[r].x, (cf[r][0] + gterm[0]) * ginv[0], acc[r][0]);
-        acc[r][1] = fmaf(sc[r].x, (cf[r][1] + gterm[1]) * ginv[1], acc[r][1]);
-        acc[r][2] = fmaf(sc[r].y, (cf[r][2] + gterm[0]) * ginv[0], acc[r][2]);
-        acc[r][3] = fmaf(sc[r].y, (cf[r][3] + gterm[1]) * ginv[1], acc[r][3]);
+        acc[r][0] = fmaf(sc[r].x, fmaf(cf[r][0], ginv[0], gterm[0]), acc[r][0]);
+        acc[r][1] = fmaf(sc[r].x, fmaf(cf[r][1], ginv[1], gterm[1]), acc[r][1]);
+        acc[r][2] = fmaf(sc[r].y, fmaf(cf[r][2], ginv[0], gterm[0]), acc[r][2]);
+        acc[r][3] = fmaf(sc[r].y, fmaf(cf[r][3], ginv[1], gterm[1]), acc[r][3]);
       }
-    }
-  };
-
-  // ---- cross-rank exchange (plans with kOpReduce ops) --------------------------------------
-  // The k-th reduce op of this launch uses epoch base + 1 + k, where base is what the previous
-  // launch (of this plan or of kq_linear_reduce) left in the exchange area; the last CTA to
-  // finish advances it.  Entries of consecutive epochs alternate between two slots, and the
-  // grid barrier between ops keeps every rank within one exchange of its peers.
-  const unsigned int epoch_base = p.fcomm != nullptr ? *reinterpret_cast<volatile unsigned int*>(p.fcomm->epoch) : 0u;
-  constexpr int kMaxOut = 8;  // outputs one lane finishes per round
-  // out = sum over ranks (rank order) of the lane's finished partial sums, in place
-  auto exchange = [&](float (&val)[kMaxOut], const uint32_t (&off)[kMaxOut], int cnt, unsigned int epoch) {
-    const FusedCommDev& fc = *p.fcomm;
-    const uint32_t me = fc.rank, world = fc.world;
-    const uint64_t slot_entries = kFusedSlotBytes / 8;
-    const uint64_t parity_base = static_cast<uint64_t>(epoch & 1u) * kFusedMaxWorld;
-    for (uint32_t r = 0; r < world; ++r) {
-      if (r == me) continue;
-      uint2* dst = reinterpret_cast<uint2*>(fc.base[r] + fc.data_off) + (parity_base + me) * slot_entries;
-#pragma unroll
-      for (int i = 0; i < kMaxOut; ++i)
-        if (i < cnt) st_exchange_entry(dst + off[i], val[i], epoch);
-    }
-#pragma unroll
-    for (int i = 0; i < kMaxOut; ++i) {
-      if (i >= cnt) continue;
-      float sum = 0.0f;
-      for (uint32_t r = 0; r < world; ++r) {
-        if (r == me) {
-          sum += val[i];
-          continue;
-        }
-        const uint2* src = reinterpret_cast<const uint2*>(fc.base[me] + fc.data_off) + (parity_base + r) * slot_entries + off[i];
-        uint2 e;
-        uint32_t spins = 0;
-        while (true) {
-          e = ld_exchange_entry(src);
-          if (e.y == epoch) break;
-          if (++spins > kSpinLimit) {
-            *reinterpret_cast<volatile int*>(p.status) = 3;
-            break;
-          }
-        }
-        sum += __uint_as_float(e.x);
-      }
-      val[i] = sum;
     }
   };
 
@@ -831,16 +932,14 @@ plan_pair_kernel(const PlanParams p) {
     if (o.norm_weight != nullptr) {
       // no reduction of the previous op is in flight any more: its buffers serve as scratch
       float* scratch = red + static_cast<size_t>(red_buf) * kPlanWarps * (2 * p.m * 16);
-      stage_x_rms_norm<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), o.norm_weight, o.norm_eps, p.m, o.k,
-                                                         xs, kXsStride, corr, scratch, scratch + kPlanWarps * p.m);
+      stage_x_rms_norm<XT, kHasLo, kCorrStride, true, 4, 4>(static_cast<const XT*>(o.x), o.norm_weight, o.norm_eps, p.m, o.k,
+                                                            xs, kXsStride, corr, scratch, scratch + kPlanWarps * p.m);
     } else {
       stage_x<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr);
     }
     __syncthreads();
 
     const uint32_t slabs = o.slabs, rounds = o.rounds;
-    const bool swiglu = (o.flags & kOpSwiglu) != 0, reduce = (o.flags & kOpReduce) != 0;
-    const unsigned int epoch = epoch_base + 1u + o.reduce_index;
     for (uint32_t round = 0; round < rounds; ++round) {
       const PairItem it = round == 0 ? first_item : pair_item_of<kCB>(o, round, warp, grid, cta);
 #pragma unroll
@@ -849,20 +948,19 @@ plan_pair_kernel(const PlanParams p) {
         for (int j = 0; j < kAcc; ++j) acc[r][j] = 0.0f;
       // (1) the bias of the rows this lane will store, fetched while the weights are consumed
       const uint32_t local_row = (it.rb - o.rb_begin[it.wi]) * 16u;  // first row of the pair inside its weight
-      const uint32_t n_i = o.n[it.wi];
-      float* out = o.out[it.wi];
-      const float* residual = o.residual[it.wi];
-      const float* bias = o.bias[it.wi];
-      const float* bias2 = swiglu ? o.bias[1] : bias + 16;  // bias of the pair's second block
       float bias_pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       if (it.valid) {
+        const float* bias = o.bias[it.wi];
+        const float* bias2 = (o.flags & kOpSwiglu) ? o.bias[1] : bias + 16;  // bias of the pair's second block
         if (o.slabs == 1) {
           bias_pre[0] = bias[local_row + g];
           bias_pre[1] = bias[local_row + g + 8];
           bias_pre[2] = bias2[local_row + g];
           bias_pre[3] = bias2[local_row + g + 8];
-        } else if (!swiglu) {
+        } else if (!(o.flags & kOpSwiglu)) {
           bias_pre[0] = bias[local_row + lane];  // the reducer's first pass covers rows lane of the pair
+          // ... and so does its residual (one activation row: output index == row)
+          if (p.m == 1 && o.residual[it.wi] != nullptr) bias_pre[1] = o.residual[it.wi][local_row + lane];
         }
       }
 
@@ -904,13 +1002,9 @@ plan_pair_kernel(const PlanParams p) {
           acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 2);
         }
       const bool owner = jl == 0;
-      // A finished value of a plain op: partial sum (scaled back) [+ the other ranks' partial
-      // sums] + bias [+ residual], each addition rounded to f32 like the reference's node
-      // sequence linear -> add.
-      float val[kMaxOut];
-      uint32_t off[kMaxOut];  // mm * n + row
-      float bsv[kMaxOut];
-      int cnt = 0;
+      // Ops with a SiLU gate, a residual or a cross-rank reduce finish in functions of their own
+      // (not inlined: their registers must not weigh on the loop above); plain ops store here.
+      const bool plain = o.flags == 0 && o.residual[it.wi] == nullptr;
       if (slabs == 1) {
         if (it.nck != 0 && owner) {
 #pragma unroll
@@ -919,83 +1013,54 @@ plan_pair_kernel(const PlanParams p) {
             if (mm >= p.m) continue;
             const float a0 = acc[0][kHasLo ? 0 : j], a1 = acc[0][kHasLo ? 1 : 2 + j];
             const float b0 = acc[1][kHasLo ? 0 : j], b1 = acc[1][kHasLo ? 1 : 2 + j];
-            if (swiglu) {
-              const uint32_t row = local_row + g;
-              out[static_cast<size_t>(mm) * n_i + row] =
-                  silu_mul(fmaf(a0, kUnscale, bias_pre[0]), fmaf(b0, kUnscale, bias_pre[2]));
-              out[static_cast<size_t>(mm) * n_i + row + 8] =
-                  silu_mul(fmaf(a1, kUnscale, bias_pre[1]), fmaf(b1, kUnscale, bias_pre[3]));
+            if (plain) {
+              float* dst = o.out[it.wi] + static_cast<size_t>(mm) * o.n[it.wi] + local_row + g;
+              dst[0] = fmaf(a0, kUnscale, bias_pre[0]);
+              dst[8] = fmaf(a1, kUnscale, bias_pre[1]);
+              dst[16] = fmaf(b0, kUnscale, bias_pre[2]);
+              dst[24] = fmaf(b1, kUnscale, bias_pre[3]);
             } else {
-              const uint32_t base = mm * n_i + local_row + g;
-              val[cnt] = a0; off[cnt] = base;      bsv[cnt] = bias_pre[0]; ++cnt;
-              val[cnt] = a1; off[cnt] = base + 8;  bsv[cnt] = bias_pre[1]; ++cnt;
-              val[cnt] = b0; off[cnt] = base + 16; bsv[cnt] = bias_pre[2]; ++cnt;
-              val[cnt] = b1; off[cnt] = base + 24; bsv[cnt] = bias_pre[3]; ++cnt;
+              finish_fused_lane(&o, it.wi, mm, local_row + g, a0, a1, b0, b1, bias_pre[0], bias_pre[1], bias_pre[2],
+                                bias_pre[3], p.fcomm, p.status);
             }
           }
         }
-      } else {
-        // K was split over `slabs` warps of this CTA: meet in shared memory, add in slab order.
-        float* mine = red + (static_cast<size_t>(red_buf) * kPlanWarps + warp) * (2 * p.m * 16);
-        if (owner) {
+        continue;
+      }
+      // K was split over `slabs` warps of this CTA: meet in shared memory, add in slab order.
+      float* mine = red + (static_cast<size_t>(red_buf) * kPlanWarps + warp) * (2 * p.m * 16);
+      if (owner) {
 #pragma unroll
-          for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < 2; ++r)
 #pragma unroll
-            for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
-              const uint32_t mm = kHasLo ? tl : 2 * tl + j;
-              if (mm >= p.m) continue;
-              mine[(r * p.m + mm) * 16 + g] = acc[r][kHasLo ? 0 : j];  // zeros when the warp had no chunks
-              mine[(r * p.m + mm) * 16 + g + 8] = acc[r][kHasLo ? 1 : 2 + j];
-            }
-        }
-        __syncthreads();
-        if ((warp & (slabs - 1u)) == 0 && it.valid) {
-          const float* first_slab = mine;
-          const uint32_t slab_stride = 2 * p.m * 16;
-          if (swiglu) {
-            for (uint32_t idx = lane; idx < 16u * p.m; idx += 32) {
-              const uint32_t mm = idx >> 4, rr = idx & 15u;
-              float tg = 0.0f, tu = 0.0f;
-              for (uint32_t sl = 0; sl < slabs; ++sl) {
-                tg += first_slab[static_cast<size_t>(sl) * slab_stride + mm * 16 + rr];
-                tu += first_slab[static_cast<size_t>(sl) * slab_stride + (p.m + mm) * 16 + rr];
-              }
-              const uint32_t row = local_row + rr;
-              out[static_cast<size_t>(mm) * n_i + row] =
-                  silu_mul(fmaf(tg, kUnscale, bias[row]), fmaf(tu, kUnscale, bias2[row]));
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < kMaxOut; ++i) {
-              const uint32_t idx = lane + 32u * i;
-              if (idx >= 32u * p.m) break;
-              float total = 0.0f;
-              for (uint32_t sl = 0; sl < slabs; ++sl) total += first_slab[static_cast<size_t>(sl) * slab_stride + idx];
-              const uint32_t r = idx / (p.m * 16), rem = idx - r * (p.m * 16);
-              const uint32_t mm = rem >> 4, row = local_row + r * 16 + (rem & 15u);
-              // idx == lane in the first pass: row r * 16 + (lane & 15) of activation row 0 when m == 1
-              val[cnt] = total;
-              off[cnt] = mm * n_i + row;
-              bsv[cnt] = (i == 0 && p.m == 1) ? bias_pre[0] : bias[row];
-              ++cnt;
-            }
+          for (int j = 0; j < (kHasLo ? 1 : 2); ++j) {
+            const uint32_t mm = kHasLo ? tl : 2 * tl + j;
+            if (mm >= p.m) continue;
+            mine[(r * p.m + mm) * 16 + g] = acc[r][kHasLo ? 0 : j];  // zeros when the warp had no chunks
+            mine[(r * p.m + mm) * 16 + g + 8] = acc[r][kHasLo ? 1 : 2 + j];
           }
-        }
-        red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
       }
-      if (cnt > 0) {
-#pragma unroll
-        for (int i = 0; i < kMaxOut; ++i)
-          if (i < cnt) val[i] *= kUnscale;
-        if (reduce) exchange(val, off, cnt, epoch);
-#pragma unroll
-        for (int i = 0; i < kMaxOut; ++i) {
-          if (i >= cnt) continue;
-          float v = __fadd_rn(val[i], bsv[i]);
-          if (residual != nullptr) v = __fadd_rn(v, residual[off[i]]);
-          out[off[i]] = v;
+      __syncthreads();
+      if ((warp & (slabs - 1u)) == 0 && it.valid) {
+        const float* first_slab = mine;
+        if (plain) {
+          const uint32_t n_i = o.n[it.wi];
+          float* out = o.out[it.wi];
+          const float* bias = o.bias[it.wi];
+          for (uint32_t idx = lane; idx < 32u * p.m; idx += 32) {
+            float total = 0.0f;
+            for (uint32_t sl = 0; sl < slabs; ++sl) total += first_slab[static_cast<size_t>(sl) * (2 * p.m * 16) + idx];
+            const uint32_t r = idx / (p.m * 16), rem = idx - r * (p.m * 16);
+            const uint32_t mm = rem >> 4, row = local_row + r * 16 + (rem & 15u);
+            // idx == lane in the first pass: row r * 16 + (lane & 15) of activation row 0 when m == 1
+            const float b = (idx == lane && p.m == 1) ? bias_pre[0] : bias[row];
+            out[static_cast<size_t>(mm) * n_i + row] = fmaf(total, kUnscale, b);
+          }
+        } else {
+          finish_fused_slabs(&o, it.wi, first_slab, slabs, p.m, local_row, lane, bias_pre[0], bias_pre[1], p.fcomm, p.status);
         }
       }
+      red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
     }
   }
   if (p.fcomm != nullptr && p.reduce_ops != 0) {
@@ -1007,6 +1072,8 @@ plan_pair_kernel(const PlanParams p) {
       if (finished == gridDim.x) {
         *reinterpret_cast<volatile unsigned int*>(p.fcomm->done) = 0u;
         __threadfence();
+        // (nobody writes the epoch before this point, so it still holds the launch's base)
+        const unsigned int epoch_base = *reinterpret_cast<volatile unsigned int*>(p.fcomm->epoch);
         *reinterpret_cast<volatile unsigned int*>(p.fcomm->epoch) = epoch_base + p.reduce_ops;
       }
     }
@@ -1198,6 +1265,11 @@ bool fill_op(PlanOpDev& o, int count, const LinearTarget* targets, const void* x
     }
     if (fusion.reduce || fusion.residual != nullptr) {
       *why = "the SiLU gate combines with a norm only";
+      return false;
+    }
+    const int64_t apart = (static_cast<const uint8_t*>(targets[1].w->data) - static_cast<const uint8_t*>(targets[0].w->data)) / 16;
+    if (apart > INT32_MAX || apart < INT32_MIN) {
+      *why = "the gate and the up weight lie more than 32 GiB apart in device memory";
       return false;
     }
     o.flags |= kOpSwiglu;

@@ -388,13 +388,13 @@ qgemv_i4_kernel(const GemvParams p) {
           mma_f16_zero(cf, a0, bfrag[tile_m].x, bfrag[tile_m].y);
           mma_f16(cf, a1, bfrag[tile_m].z, bfrag[tile_m].w);
           if constexpr (kHasLo) {
-            acc[r][tile_m][0] = fmaf(s.x, ((cf[0] + cf[1]) + cterm[tile_m][0]) * cinv[tile_m][0], acc[r][tile_m][0]);
-            acc[r][tile_m][1] = fmaf(s.y, ((cf[2] + cf[3]) + cterm[tile_m][0]) * cinv[tile_m][0], acc[r][tile_m][1]);
+            acc[r][tile_m][0] = fmaf(s.x, fmaf(cf[0] + cf[1], cinv[tile_m][0], cterm[tile_m][0]), acc[r][tile_m][0]);
+            acc[r][tile_m][1] = fmaf(s.y, fmaf(cf[2] + cf[3], cinv[tile_m][0], cterm[tile_m][0]), acc[r][tile_m][1]);
           } else {
-            acc[r][tile_m][0] = fmaf(s.x, (cf[0] + cterm[tile_m][0]) * cinv[tile_m][0], acc[r][tile_m][0]);
-            acc[r][tile_m][1] = fmaf(s.x, (cf[1] + cterm[tile_m][1]) * cinv[tile_m][1], acc[r][tile_m][1]);
-            acc[r][tile_m][2] = fmaf(s.y, (cf[2] + cterm[tile_m][0]) * cinv[tile_m][0], acc[r][tile_m][2]);
-            acc[r][tile_m][3] = fmaf(s.y, (cf[3] + cterm[tile_m][1]) * cinv[tile_m][1], acc[r][tile_m][3]);
+            acc[r][tile_m][0] = fmaf(s.x, fmaf(cf[0], cinv[tile_m][0], cterm[tile_m][0]), acc[r][tile_m][0]);
+            acc[r][tile_m][1] = fmaf(s.x, fmaf(cf[1], cinv[tile_m][1], cterm[tile_m][1]), acc[r][tile_m][1]);
+            acc[r][tile_m][2] = fmaf(s.y, fmaf(cf[2], cinv[tile_m][0], cterm[tile_m][0]), acc[r][tile_m][2]);
+            acc[r][tile_m][3] = fmaf(s.y, fmaf(cf[3], cinv[tile_m][1], cterm[tile_m][1]), acc[r][tile_m][3]);
           }
         }
       }
@@ -619,13 +619,13 @@ qgemv_i4_gp_kernel(const GemvParams p) {
     if constexpr (kScaleF16) s = __half22float2(*reinterpret_cast<const __half2*>(&ring_s[u].v));
     else s = make_float2(__uint_as_float(ring_s[u].v.x), __uint_as_float(ring_s[u].v.y));
     if constexpr (kHasLo) {
-      acc[0] = fmaf(s.x, ((cf[0] + cf[1]) + cterm[0]) * cinv[0], acc[0]);
-      acc[1] = fmaf(s.y, ((cf[2] + cf[3]) + cterm[0]) * cinv[0], acc[1]);
+      acc[0] = fmaf(s.x, fmaf(cf[0] + cf[1], cinv[0], cterm[0]), acc[0]);
+      acc[1] = fmaf(s.y, fmaf(cf[2] + cf[3], cinv[0], cterm[0]), acc[1]);
     } else {
-      acc[0] = fmaf(s.x, (cf[0] + cterm[0]) * cinv[0], acc[0]);
-      acc[1] = fmaf(s.x, (cf[1] + cterm[1]) * cinv[1], acc[1]);
-      acc[2] = fmaf(s.y, (cf[2] + cterm[0]) * cinv[0], acc[2]);
-      acc[3] = fmaf(s.y, (cf[3] + cterm[1]) * cinv[1], acc[3]);
+      acc[0] = fmaf(s.x, fmaf(cf[0], cinv[0], cterm[0]), acc[0]);
+      acc[1] = fmaf(s.x, fmaf(cf[1], cinv[1], cterm[1]), acc[1]);
+      acc[2] = fmaf(s.y, fmaf(cf[2], cinv[0], cterm[0]), acc[2]);
+      acc[3] = fmaf(s.y, fmaf(cf[3], cinv[1], cterm[1]), acc[3]);
     }
     if (refill && active) fetch(u, next + u * (kCU * kCB));
   };
