@@ -146,6 +146,45 @@ KQ_API int kq_weight_shape(kq_ctx* ctx, kq_weight w, uint32_t* out_n, uint32_t* 
  *       packages/runtime/tests/gpu_i8_weights_test.ts:612-660). */
 KQ_API int kq_weight_dequant(kq_ctx* ctx, kq_weight w, uint64_t out_f32_dptr);
 
+/* ---- models in karume's distribution format ----------------------------------------------
+ * A model is ONE .safetensors file (8-byte little-endian header length, header JSON, data
+ * section) whose __metadata__.karume_ir holds the graph JSON (docs/ir-v1.md).  kq_model_open
+ * reads it with the reference's own checks and refuses what the reference refuses:
+ *   - header: known dtypes, integer shapes, byte size == numel * bits / 8 (I4 = 4 bits; an odd
+ *     number of I4 elements is refused), the data section covered exactly (no overlap, gap or
+ *     tail), every tensor start aligned (I4: 4 bytes)
+ *     (packages/runtime/src/format/safetensors.ts:25-50, :107-160, :187-262);
+ *   - initializers: storage { dtype, scale, group_size } with scale required for i8 / i4,
+ *     group_size required for i4 (a power of two >= 16 dividing numel / shape[0]) and refused
+ *     on any other storage (packages/runtime/src/format/ir.ts:268-306, :617-646;
+ *     packages/runtime/src/format/container.ts:468-506);
+ *   - against the file: tensor present, dtype == the storage's encoding, shape == the declared
+ *     one; scale tensors F32, [shape[0], row / group_size] for i4 and the keepdim broadcast form
+ *     for i8; no tensor without a referring initializer
+ *     (packages/runtime/src/format/container.ts:180-232, :309-320, :337-400).
+ * The graph's nodes stay the host's business.  These calls need no GPU and no context; their
+ * error text is read with kq_last_error(NULL).  kq_model_weight uploads one packed i4 / i8
+ * initializer (rank >= 2, rows = shape[0], k = numel / shape[0]) as a resident weight. */
+typedef uint64_t kq_model; /* opaque handle, 0 is never valid */
+KQ_API int kq_model_open(const char* path, kq_model* out);
+KQ_API int kq_model_open_memory(const void* bytes, uint64_t size, kq_model* out); /* the bytes are copied */
+KQ_API void kq_model_close(kq_model model);
+KQ_API uint32_t kq_model_initializer_count(kq_model model);
+KQ_API const char* kq_model_initializer_name(kq_model model, uint32_t index);
+/* Any out-pointer may be NULL.  storage_bits: 4 (i4), 8 (i8), 16 (f16 / bf16), 32 (f32 / i32);
+ * shape8 receives up to 8 dimensions (the rest 0); payload / scale point into the model's copy
+ * of the file and stay valid until kq_model_close. */
+KQ_API int kq_model_initializer_info(kq_model model, const char* name, uint32_t* storage_bits, uint32_t* rank,
+                                     uint64_t* shape8, uint32_t* group_size, const void** payload,
+                                     uint64_t* payload_bytes, const void** scale, uint64_t* scale_bytes);
+KQ_API int kq_model_weight(kq_ctx* ctx, kq_model model, const char* name, kq_weight* out);
+/* A .safetensors file without a graph (the reference's golden io files): the header checks
+ * only.  kq_model_tensor_info looks a tensor up by its safetensors key in either kind of
+ * handle; dtype8 receives the dtype name ("F32", "I8", "I4", ...), NUL-terminated. */
+KQ_API int kq_tensors_open(const char* path, kq_model* out);
+KQ_API int kq_model_tensor_info(kq_model model, const char* key, char* dtype8, uint32_t* rank, uint64_t* shape8,
+                                const void** data, uint64_t* bytes);
+
 /* ---- the op ---------------------------------------------------------------------
  * out[m, n] = sum_k x[m, k] * W[n, k] + bias[n], f32 accumulate, f32 output.
  * Replaces RecipeBuilder.#buildLinear's pipeline lookup + dispatch

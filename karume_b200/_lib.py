@@ -46,6 +46,16 @@ SYMBOLS = {
     "kq_embedding": (_i32, [_vp, _u64, _u64, _u32, _u64]),
     "kq_quantize_rows": (_i32, [_vp, _u64, _u32, _u32, _u64, _u64]),
     "kq_linear_a8": (_i32, [_vp, _u64, _u64, _u64, _u64, _u64, _u32]),
+    "kq_model_open": (_i32, [ctypes.c_char_p, _pu64]),
+    "kq_model_open_memory": (_i32, [_vp, _u64, _pu64]),
+    "kq_model_close": (None, [_u64]),
+    "kq_model_initializer_count": (_u32, [_u64]),
+    "kq_model_initializer_name": (ctypes.c_char_p, [_u64, _u32]),
+    "kq_model_initializer_info": (_i32, [_u64, ctypes.c_char_p, _pu32, _pu32, _pu64, _pu32, ctypes.POINTER(_vp), _pu64,
+                                         ctypes.POINTER(_vp), _pu64]),
+    "kq_model_weight": (_i32, [_vp, _u64, ctypes.c_char_p, _pu64]),
+    "kq_tensors_open": (_i32, [ctypes.c_char_p, _pu64]),
+    "kq_model_tensor_info": (_i32, [_u64, ctypes.c_char_p, ctypes.c_char_p, _pu32, _pu64, ctypes.POINTER(_vp), _pu64]),
     "kq_weight_dequant": (_i32, [_vp, _u64, _u64]),
     "kq_linear": (_i32, [_vp, _u64, _u64, _i32, _u64, _u64, _u32]),
     "kq_linear_multi": (_i32, [_vp, _u32, _pu64, _u64, _i32, _pu64, _pu64, _u32]),

@@ -341,6 +341,11 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
 
 }  // namespace
 
+namespace kq {
+void set_global_error(const std::string& message) { g_init_error = message; }
+int ctx_fail(kq_ctx* ctx, int code, const std::string& message) { return fail(ctx, code, "%s", message.c_str()); }
+}  // namespace kq
+
 extern "C" {
 
 const char* kq_version(void) { return "kq 0.1 sm_100a"; }

@@ -100,6 +100,13 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
                             int* status_word, int* extra_launches);
 }  // namespace kq
 
+// ---- error reporting shared with kq_container.cu (kq_api.cu) ------------------------------
+#include <string>
+namespace kq {
+void set_global_error(const std::string& message);              // read back by kq_last_error(NULL)
+int ctx_fail(kq_ctx* ctx, int code, const std::string& message);  // stores the message, returns the code
+}  // namespace kq
+
 // ---- fused plans (kq_plan.cu) -------------------------------------------------------
 namespace kq {
 struct Plan;

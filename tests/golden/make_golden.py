@@ -24,6 +24,14 @@ Two fixtures are written next to this script:
     [7,5], int8 dense weight [3,5] + bias, index[6], expected output [6,3]); the
     reference checks it at atol 1e-6 / rtol 1e-5
     (packages/runtime/tests/e2e_golden_test.ts:43).
+
+``exporter_linear_i4_g32.safetensors``, ``exporter_linear_i4_g16.safetensors``,
+``exporter_linear_i8.safetensors`` and ``exporter_models.npz``
+    Whole model files written by the reference's exporter (``karume.pipeline.export_to_file``
+    after ``karume.quantize.fake_quant_int4 / fake_quant_int8``) for a single ``nn.Linear``,
+    with an input and the torch module's output on it.  They pin the container loader
+    (kq_model_open) to files the reference itself produces, I4 payload order and scale layout
+    included.
 """
 import json
 import os
@@ -36,18 +44,17 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def read_safetensors(path):
+def read_tensors(path, graph):
+    """Every tensor of a .safetensors file through libkq's own loader (kq_model_open for a model
+    with its graph, kq_tensors_open for the golden io file), by safetensors key."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from karume_b200.container import Model
     blob = open(path, "rb").read()
     (hlen,) = struct.unpack("<Q", blob[:8])
-    header = json.loads(blob[8:8 + hlen])
-    base = 8 + hlen
-    dtypes = {"F32": np.float32, "I8": np.int8, "I32": np.int32}
-    out = {}
-    for key, meta in header.items():
-        if key == "__metadata__":
-            continue
-        lo, hi = meta["data_offsets"]
-        out[key] = np.frombuffer(blob[base + lo:base + hi], dtypes[meta["dtype"]]).reshape(meta["shape"]).copy()
+    keys = [k for k in json.loads(blob[8:8 + hlen]) if k != "__metadata__"]
+    model = Model(path, graph=graph)
+    out = {key: model.tensor(key) for key in keys}
+    model.close()
     return out
 
 
@@ -86,13 +93,36 @@ def main(ref_root):
     np.savez_compressed(os.path.join(HERE, "exporter_vectors.npz"), **vec)
 
     gold = os.path.join(ref_root, "packages", "runtime", "tests", "fixtures", "golden", "i8_weights")
-    model = read_safetensors(os.path.join(gold, "model.safetensors"))
-    io = read_safetensors(os.path.join(gold, "io.safetensors"))
+    model = read_tensors(os.path.join(gold, "model.safetensors"), graph=True)
+    io = read_tensors(os.path.join(gold, "io.safetensors"), graph=False)
     np.savez_compressed(
         os.path.join(HERE, "i8_weights_golden.npz"),
         table_q=model["table.weight"], table_scale=model["karume.scale.table.weight"],
         dense_q=model["dense.weight"], dense_scale=model["karume.scale.dense.weight"],
         dense_bias=model["dense.bias"], index=io["input.index"], expected=io["output.0"])
+    models = {}
+    from karume import pipeline
+
+    class One(torch.nn.Module):
+        def __init__(self, k, n):
+            super().__init__()
+            self.dense = torch.nn.Linear(k, n)
+
+        def forward(self, x):
+            return self.dense(x)
+
+    torch.manual_seed(69)
+    for tag, k, n, kind, group in [("i4_g32", 128, 64, "i4", 32), ("i4_g16", 64, 48, "i4", 16), ("i8", 20, 19, "i8", 0)]:
+        module = One(k, n).eval()
+        report = quantize.fake_quant_int4(module, group_size=group) if kind == "i4" else quantize.fake_quant_int8(module)
+        x = torch.randn(5, k)
+        with torch.no_grad():
+            y = module(x)
+        pipeline.export_to_file(module, (x,), os.path.join(HERE, f"exporter_linear_{tag}.safetensors"),
+                                weight_dtype=kind, weight_scales=report.scales)
+        models[f"{tag}_x"] = x.numpy()
+        models[f"{tag}_y"] = y.numpy()
+    np.savez_compressed(os.path.join(HERE, "exporter_models.npz"), **models)
     print("wrote", sorted(os.listdir(HERE)))
 
 
