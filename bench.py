@@ -330,6 +330,32 @@ def parity_gate(step, cfg, rank, world, dist, rows_per_rank=48):
             "oracle_seconds": round(time.time() - t0, 1), "pass": bool(stats[0] > 0.5)}
 
 
+def phase_table(gpu, step, cfg):
+    """One profiled launch of the fused plan (kq_plan_profile): per kind of op, the median over
+    CTAs and layers of the time spent in each phase, in microseconds."""
+    stamps = gpu.plan_profile(step.plan).astype(np.float64)  # [cta, op, slot] ns
+    names = ["q|k|v", "o", "gate*up", "down"]
+    kinds = [names[i % 4] for i in range(4 * cfg.layers)] + ["lm_head"]
+    begin, barrier, staged, first, consumed, end = (stamps[:, :, i] for i in range(6))
+    last_arrival = begin.max(axis=0, keepdims=True)
+    phases = {
+        "wait_for_last_cta": np.maximum(last_arrival - begin, 0.0),
+        "barrier_after_last_arrival": np.maximum(barrier - np.maximum(last_arrival, begin), 0.0),
+        "stage_x": staged - barrier,
+        "first_piece_wait": np.maximum(first - staged, 0.0),
+        "weights": consumed - np.maximum(first, staged),
+        "outputs": end - consumed,
+        "op_total": end - begin,
+    }
+    table = {}
+    for kind in names + ["lm_head"]:
+        cols = [i for i, k in enumerate(kinds) if k == kind and i > 0]
+        table[kind] = {name: round(float(np.median(val[:, cols])) / 1e3, 2) for name, val in phases.items()}
+        table[kind]["ops"] = len(cols)
+    span = float(end.max() - begin.min()) / 1e6
+    return {"unit": "us (median over CTAs and ops of a kind; warp 0 of every CTA)", "kernel_ms": round(span, 4), "phases": table}
+
+
 def run_cuda(args):
     import torch
     import torch.distributed as dist
@@ -448,6 +474,7 @@ def run_cuda(args):
             threads = host_threads()
             tok_cpu, _, desc = cpu_sample(cfg, args.batch, threads, 3)
             cpu = {"value": tok_cpu, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc}
+        phases = phase_table(gpu, step, cfg) if (args.phases and step.fused and world == 1) else None
         line = {
             "metric": "decode_matmul_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm, "ms_per_step": per_step_ms, "higher_is_better": True,
@@ -473,6 +500,7 @@ def run_cuda(args):
                          "traffic_source": "ncu capture of the 2-layer 1-GPU case of the same kernel, scaled by this rank's weight bytes"
                                            if step.fused else None},
             "parity": parity,
+            "plan_phases": phases,
             "cpu_baseline": cpu,
             "kernel_sweep": sweep,
             "other_batch": other_batch,
@@ -502,6 +530,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the single-kernel GEMV / GEMM numbers")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of this run's outputs")
+    ap.add_argument("--phases", action="store_true",
+                    help="add a per-op phase table from one profiled launch of the fused plan (kq_plan_profile)")
     ap.add_argument("--exchange", default="kq", choices=["kq", "nccl"], help="sum over ranks used when --gpus > 1")
     ap.add_argument("--layers", type=int, default=32,
                     help="decoder layers; anything but 32 is a small case for profiler captures, not the benchmark")

@@ -325,6 +325,17 @@ KQ_API int kq_plan_begin(kq_ctx* ctx);
 KQ_API int kq_plan_end(kq_ctx* ctx, kq_plan* out);
 KQ_API int kq_plan_launch(kq_ctx* ctx, kq_plan plan);
 KQ_API int kq_plan_free(kq_ctx* ctx, kq_plan plan);
+/* Runs the plan once (copies included) with phase stamps switched on and returns them: the
+ * fused kernel's counterpart of the reference's per-pipeline timestamp queries
+ * (packages/runtime/src/gpu/submit.ts:180-194, docs/decisions/0021-gpu-timing-diagnostics.md).
+ * stamps[(cta * ops + op) * slots + s] is the GPU's nanosecond timer when CTA `cta` reached point
+ * s of op `op`: 0 done with the previous op, 1 through the grid barrier, 2 activations staged,
+ * 3 first weight piece landed (warp 0), 4 weights of the first round consumed (warp 0), 5 outputs
+ * stored; the other slots are zero.  With stamps == NULL only the three sizes are returned.
+ * Plans that run on the paired kernel only (at most two f32 rows); allocates and frees its
+ * buffer, so not for the serving path. */
+KQ_API int kq_plan_profile(kq_ctx* ctx, kq_plan plan, uint64_t* stamps, uint64_t capacity, uint32_t* out_ctas,
+                           uint32_t* out_ops, uint32_t* out_slots);
 
 /* ---- tensor-parallel exchange --------------------------------------------------------
  * No reference counterpart (karume is single-device).  One process per GPU: every rank

@@ -73,6 +73,7 @@ SYMBOLS = {
     "kq_plan_end": (_i32, [_vp, _pu64]),
     "kq_plan_launch": (_i32, [_vp, _u64]),
     "kq_plan_free": (_i32, [_vp, _u64]),
+    "kq_plan_profile": (_i32, [_vp, _u64, _pu64, _u64, _pu32, _pu32, _pu32]),
     "kq_comm_create": (_i32, [_vp, _u32, _u32, _u64, _vp]),
     "kq_comm_connect": (_i32, [_vp, _vp]),
     "kq_all_reduce": (_i32, [_vp, _u64, _u64]),

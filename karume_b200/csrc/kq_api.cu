@@ -1097,6 +1097,36 @@ int kq_plan_launch(kq_ctx* ctx, kq_plan plan) {
   return KQ_OK;
 }
 
+int kq_plan_profile(kq_ctx* ctx, kq_plan plan, uint64_t* stamps, uint64_t capacity, uint32_t* out_ctas, uint32_t* out_ops,
+                    uint32_t* out_slots) {
+  if (!ctx || !out_ctas || !out_ops || !out_slots) return fail(ctx, KQ_ERR_BAD_ARG, "kq_plan_profile: null argument");
+  auto it = ctx->plans.find(plan);
+  if (it == ctx->plans.end()) return fail(ctx, KQ_ERR_BAD_ARG, "kq_plan_profile: unknown plan handle");
+  if (ctx->capturing || ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_plan_profile during a recording");
+  if (!kq::plan_is_paired(it->second))
+    return fail(ctx, KQ_ERR_UNSUPPORTED, "kq_plan_profile: only the paired kernel (one or two rows) leaves phase stamps");
+  const uint32_t ctas = kq::plan_grid(it->second), ops = kq::plan_op_count(it->second), slots = kq::plan_trace_slots();
+  *out_ctas = ctas;
+  *out_ops = ops;
+  *out_slots = slots;
+  const uint64_t need = static_cast<uint64_t>(ctas) * ops * slots;
+  if (!stamps) return KQ_OK;  // size query
+  if (capacity < need) return fail(ctx, KQ_ERR_SHAPE, "kq_plan_profile: %llu stamps needed, room for %llu", (unsigned long long)need,
+                                   (unsigned long long)capacity);
+  DeviceGuard guard(ctx->device);
+  unsigned long long* dev = nullptr;
+  KQ_CUDA(ctx, cudaMalloc(reinterpret_cast<void**>(&dev), need * sizeof(unsigned long long)));
+  cudaError_t e = cudaMemsetAsync(dev, 0, need * sizeof(unsigned long long), ctx->stream);
+  int launched = 0;
+  if (e == cudaSuccess) e = kq::plan_launch(it->second, env_of(ctx), &launched, dev);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(stamps, dev, need * sizeof(unsigned long long), cudaMemcpyDeviceToHost, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  cudaFree(dev);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "kq_plan_profile");
+  ctx->launches += launched;
+  return KQ_OK;
+}
+
 int kq_plan_free(kq_ctx* ctx, kq_plan plan) {
   if (!ctx) return KQ_ERR_BAD_ARG;
   auto it = ctx->plans.find(plan);

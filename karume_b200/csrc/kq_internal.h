@@ -117,7 +117,10 @@ const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, 
                             uint32_t m, const LinearFusion& fusion);
 uint32_t plan_op_count(const Plan* plan);
 cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why);
-cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches);
+cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches, unsigned long long* trace = nullptr);
+uint32_t plan_grid(const Plan* plan);
+bool plan_is_paired(const Plan* plan);
+uint32_t plan_trace_slots();
 int plan_take_status(Plan* plan);
 // One linear through the fused kernel with every scratch byte in a static device array.
 cudaError_t linear_static(const LaunchEnv& env, const LinearTarget& target, const void* x, int x_dtype,

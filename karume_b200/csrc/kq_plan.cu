@@ -55,6 +55,7 @@ struct PlanOpDev {
   const float* norm_weight;  // null, or [k]: x is rms-normalised with this weight while it is staged
   float norm_eps;
   uint32_t reduce_index;     // ordinal of this op among the plan's kOpReduce ops
+  long long gate_up_delta;   // kOpSwiglu: bytes from the gate weight to the up weight (any distance)
   uint32_t k;
   uint32_t chunks_per_row;   // k / 64
   uint32_t slabs;            // S: k-slabs a row block is split into across the warps of a CTA
@@ -75,7 +76,26 @@ struct PlanParams {
   int* status;             // non-zero: a bounded wait gave up
   const FusedCommDev* fcomm;  // exchange areas of the ranks (plans with kOpReduce ops)
   uint32_t reduce_ops;        // how many kOpReduce ops the plan holds
+  unsigned long long* trace;  // null, or [cta][op][kTraceSlots] %globaltimer stamps (kq_plan_profile)
 };
+
+// Phase stamps one CTA (its thread 0) leaves per op when a plan is profiled.
+constexpr uint32_t kTraceSlots = 8;
+enum : uint32_t {
+  kTraceOpBegin = 0,    // the CTA is done with the previous op
+  kTraceBarrier = 1,    // the grid barrier has let it through
+  kTraceStaged = 2,     // the activations are staged
+  kTraceFirstPiece = 3, // warp 0's first weight piece of the op has landed
+  kTraceConsumed = 4,   // warp 0 has consumed the weights of its first round
+  kTraceOpEnd = 5       // outputs of the last round stored
+};
+__device__ __forceinline__ void trace_stamp(const PlanParams& p, uint32_t op, uint32_t slot) {
+  if (p.trace != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[(static_cast<size_t>(blockIdx.x) * p.op_count + op) * kTraceSlots + slot] = t;
+  }
+}
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -541,6 +561,20 @@ __device__ __forceinline__ void lds_v2f_if_at(float& a, float& b, uint32_t base,
                : "+f"(a), "+f"(b) : "r"(base), "r"(static_cast<uint32_t>(pred)), "n"(kOff));
 }
 
+// Sum over the k-slabs of one output, slab order fixed: ((s0 + s1) + (s2 + s3)) + ... per group of
+// four, groups in ascending order (slabs is a power of two >= 2).  Four independent loads per
+// step instead of a chain of dependent load-add pairs.
+__device__ __forceinline__ float sum_slabs(const float* first, uint32_t slabs, uint32_t stride) {
+  if (slabs == 2) return first[0] + first[stride];
+  float total = 0.0f;
+  for (uint32_t sl = 0; sl < slabs; sl += 4) {
+    const float a = first[static_cast<size_t>(sl) * stride], b = first[static_cast<size_t>(sl + 1) * stride];
+    const float c = first[static_cast<size_t>(sl + 2) * stride], d = first[static_cast<size_t>(sl + 3) * stride];
+    total += (a + b) + (c + d);
+  }
+  return total;
+}
+
 // ---- finishing the outputs of ops with fused neighbours ---------------------------------
 // out = partial sum (scaled back) [summed over the ranks] + bias [+ residual], each addition
 // rounded to f32 like the reference's node sequence linear -> add; or silu(gate) * up.
@@ -648,11 +682,8 @@ __device__ __noinline__ void finish_fused_slabs(const PlanOpDev* o, uint32_t wi,
     const float* bias_u = o->bias[1];
     for (uint32_t idx = lane; idx < 16u * m; idx += 32) {
       const uint32_t mm = idx >> 4, rr = idx & 15u;
-      float tg = 0.0f, tu = 0.0f;
-      for (uint32_t sl = 0; sl < slabs; ++sl) {
-        tg += first_slab[static_cast<size_t>(sl) * slab_stride + mm * 16 + rr];
-        tu += first_slab[static_cast<size_t>(sl) * slab_stride + (m + mm) * 16 + rr];
-      }
+      const float tg = sum_slabs(first_slab + mm * 16 + rr, slabs, slab_stride);
+      const float tu = sum_slabs(first_slab + (m + mm) * 16 + rr, slabs, slab_stride);
       const uint32_t row = local_row + rr;
       o->out[0][static_cast<size_t>(mm) * n_i + row] = silu_mul(fmaf(tg, kUnscale, bias_g[row]), fmaf(tu, kUnscale, bias_u[row]));
     }
@@ -670,8 +701,7 @@ __device__ __noinline__ void finish_fused_slabs(const PlanOpDev* o, uint32_t wi,
       bsv[i] = 0.0f;
       off[i] = 0u;
       if (idx < 32u * m) {
-        float total = 0.0f;
-        for (uint32_t sl = 0; sl < slabs; ++sl) total += first_slab[static_cast<size_t>(sl) * slab_stride + idx];
+        const float total = sum_slabs(first_slab + idx, slabs, slab_stride);
         const uint32_t r = idx / (m * 16), rem = idx - r * (m * 16);
         const uint32_t mm = rem >> 4, row = local_row + r * 16 + (rem & 15u);
         val[i] = total;
@@ -683,6 +713,8 @@ __device__ __noinline__ void finish_fused_slabs(const PlanOpDev* o, uint32_t wi,
     finish_values(o, wi, val, off, bsv, vmask, fc, status, m == 1 && first == 0, residual_lane);
   }
 }
+
+constexpr int32_t kStrideInDescriptor = INT32_MIN;  // PairItem::row_stride16: see PlanOpDev::gate_up_delta
 
 struct PairItem {
   const uint8_t* src;  // first chunk of the slab of the pair's first row block
@@ -725,9 +757,9 @@ __device__ __forceinline__ PairItem pair_item_of(const PlanOpDev& o, uint32_t ro
   it.c0 = slab * o.chunks_per_slab;
   if (it.c0 >= o.chunks_per_row) return it;
   it.nck = min(o.chunks_per_slab, o.chunks_per_row - it.c0);
-  // (device allocations are 256-byte aligned and chunks are multiples of 16 bytes; the host
-  // checks that the distance between a gate and an up weight fits 32 bits of such units)
-  it.row_stride16 = swiglu ? static_cast<int32_t>((o.w[1] - o.w[0]) / 16) : static_cast<int32_t>(o.chunks_per_row * (kCB / 16));
+  // (the gate and the up weight are separate allocations, any distance apart: the producer
+  // reads that distance from the descriptor instead of carrying 64 bits of it in a register)
+  it.row_stride16 = swiglu ? kStrideInDescriptor : static_cast<int32_t>(o.chunks_per_row * (kCB / 16));
   it.src = o.w[it.wi] + (static_cast<size_t>(it.rb - o.rb_begin[it.wi]) * o.chunks_per_row + it.c0) * kCB;
   return it;
 }
@@ -813,8 +845,9 @@ plan_pair_kernel(const PlanParams p) {
     if (lane == 0) {
       mbar_expect_tx(bars + slot * 8, 2u * nc * kCB);
       bulk_copy_g2s(ring + slot * kSlotBytes, prod_src, nc * kCB, bars + slot * 8);
-      bulk_copy_g2s(ring + slot * kSlotBytes + kPiece * kCB, prod_src + static_cast<int64_t>(prod_stride16) * 16, nc * kCB,
-                    bars + slot * 8);
+      const long long delta = prod_stride16 != kStrideInDescriptor ? static_cast<long long>(prod_stride16) * 16
+                                                                   : desc(prod_op).gate_up_delta;
+      bulk_copy_g2s(ring + slot * kSlotBytes + kPiece * kCB, prod_src + delta, nc * kCB, bars + slot * 8);
     }
     prod_src += nc * kCB;
     prod_left -= nc;
@@ -907,6 +940,7 @@ plan_pair_kernel(const PlanParams p) {
   for (uint32_t op = 0; op < p.op_count; ++op) {
     // Nothing about the first item depends on the previous op: look it up before the wait.
     const PairItem first_item = pair_item_of<kCB>(win[op % kOpWindow], 0, warp, grid, cta);
+    trace_stamp(p, op, kTraceOpBegin);
     if (op > 0) {
       // Slot (op - 2) % kOpWindow is dead: every warp passed the barrier of op - 1.
       fill_window(op + kOpWindow - 2);
@@ -929,6 +963,7 @@ plan_pair_kernel(const PlanParams p) {
     }
     cur_op = op;
     const PlanOpDev& o = win[op % kOpWindow];
+    trace_stamp(p, op, kTraceBarrier);
     if (o.norm_weight != nullptr) {
       // no reduction of the previous op is in flight any more: its buffers serve as scratch
       float* scratch = red + static_cast<size_t>(red_buf) * kPlanWarps * (2 * p.m * 16);
@@ -938,6 +973,7 @@ plan_pair_kernel(const PlanParams p) {
       stage_x<XT, kHasLo, kCorrStride, true, 4>(static_cast<const XT*>(o.x), p.m, o.k, 0, o.k >> 5, xs, kXsStride, corr);
     }
     __syncthreads();
+    trace_stamp(p, op, kTraceStaged);
 
     const uint32_t slabs = o.slabs, rounds = o.rounds;
     for (uint32_t round = 0; round < rounds; ++round) {
@@ -976,6 +1012,7 @@ plan_pair_kernel(const PlanParams p) {
             }
           }
         }
+        if (first == 0 && round == 0) trace_stamp(p, op, kTraceFirstPiece);
         const uint32_t slot_addr = ring + slot * kSlotBytes;
         const uint32_t unit0 = (it.c0 + first) / kCU;
         const uint32_t w_base = slot_addr + lane * 16, s_base = slot_addr + scale_lane;
@@ -993,6 +1030,7 @@ plan_pair_kernel(const PlanParams p) {
       }
 
       // ---- this round's outputs ------------------------------------------------------
+      if (round == 0) trace_stamp(p, op, kTraceConsumed);
       // lanes whose C columns belong to different groups hold partial sums of the same outputs
 #pragma unroll
       for (int r = 0; r < 2; ++r)
@@ -1062,6 +1100,7 @@ plan_pair_kernel(const PlanParams p) {
       }
       red_buf ^= 1u;  // the next round writes the other buffer; this one is re-used two rounds on
     }
+    trace_stamp(p, op, kTraceOpEnd);
   }
   if (p.fcomm != nullptr && p.reduce_ops != 0) {
     // the last CTA to get here advances the epoch for the next launch
@@ -1267,11 +1306,7 @@ bool fill_op(PlanOpDev& o, int count, const LinearTarget* targets, const void* x
       *why = "the SiLU gate combines with a norm only";
       return false;
     }
-    const int64_t apart = (static_cast<const uint8_t*>(targets[1].w->data) - static_cast<const uint8_t*>(targets[0].w->data)) / 16;
-    if (apart > INT32_MAX || apart < INT32_MIN) {
-      *why = "the gate and the up weight lie more than 32 GiB apart in device memory";
-      return false;
-    }
+    o.gate_up_delta = static_cast<const uint8_t*>(targets[1].w->data) - static_cast<const uint8_t*>(targets[0].w->data);
     o.flags |= kOpSwiglu;
   }
   if (fusion.reduce || fusion.residual != nullptr) {
@@ -1371,6 +1406,9 @@ const char* plan_add_linear(Plan* plan, int count, const LinearTarget* targets, 
 }
 
 uint32_t plan_op_count(const Plan* plan) { return static_cast<uint32_t>(plan->ops.size()); }
+uint32_t plan_grid(const Plan* plan) { return static_cast<uint32_t>(plan->grid); }
+bool plan_is_paired(const Plan* plan) { return plan->paired; }
+uint32_t plan_trace_slots() { return kTraceSlots; }
 
 cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why) {
   *why = "";
@@ -1410,7 +1448,7 @@ cudaError_t plan_finalize(Plan* plan, const LaunchEnv& env, const char** why) {
   return e;
 }
 
-cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
+cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches, unsigned long long* trace) {
   cudaError_t e = cudaSuccess;
   for (const PlanCopy& c : plan->before) {
     e = cudaMemcpyAsync(c.device, c.host, c.bytes, cudaMemcpyHostToDevice, env.stream);
@@ -1427,6 +1465,7 @@ cudaError_t plan_launch(Plan* plan, const LaunchEnv& env, int* launches) {
   p.status = plan->status_dev;
   p.fcomm = plan->fcomm;
   p.reduce_ops = plan->reduce_ops;
+  p.trace = plan->paired ? trace : nullptr;  // the paired kernel is the one that leaves stamps
   void* args[] = {&p};
   e = cudaLaunchCooperativeKernel(plan->kernel, dim3(plan->grid), dim3(kPlanWarps * 32), args, plan->smem, env.stream);
   if (e != cudaSuccess) return e;

@@ -320,6 +320,16 @@ class Gpu:
     def plan_launch(self, plan: int) -> None:
         self._check(L.kq_plan_launch(self._ctx, plan))
 
+    def plan_profile(self, plan: int) -> np.ndarray:
+        """One profiled launch of a fused plan: uint64 [ctas, ops, slots] of GPU-timer stamps (ns);
+        see kq_plan_profile for the meaning of the slots."""
+        ctas, ops, slots = ctypes.c_uint32(), ctypes.c_uint32(), ctypes.c_uint32()
+        self._check(L.kq_plan_profile(self._ctx, plan, None, 0, ctypes.byref(ctas), ctypes.byref(ops), ctypes.byref(slots)))
+        out = np.zeros((ctas.value, ops.value, slots.value), np.uint64)
+        self._check(L.kq_plan_profile(self._ctx, plan, out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint64)), out.size,
+                                      ctypes.byref(ctas), ctypes.byref(ops), ctypes.byref(slots)))
+        return out
+
     def plan_free(self, plan: int) -> None:
         self._check(L.kq_plan_free(self._ctx, plan))
 
