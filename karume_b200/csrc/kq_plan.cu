@@ -764,7 +764,7 @@ __device__ __forceinline__ PairItem pair_item_of(const PlanOpDev& o, uint32_t ro
   return it;
 }
 
-template <typename XT, bool kScaleF16, int kG, int kPiece>
+template <typename XT, bool kScaleF16, int kG, int kPiece, int kNS>
 __global__ void __launch_bounds__(kPlanWarps * 32, 1)
 plan_pair_kernel(const PlanParams p) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
@@ -788,9 +788,9 @@ plan_pair_kernel(const PlanParams p) {
 
   // shared memory: [warp rings][mbarriers][staged x][corr][reduction buffers x2]
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-  const uint32_t ring = smem_base + warp * (kSlots * kSlotBytes);
-  const uint32_t bars = smem_base + kPlanWarps * kSlots * kSlotBytes + warp * (kSlots * 8);
-  uint8_t* xs = smem + kPlanWarps * kSlots * kSlotBytes + kPlanWarps * kSlots * 8;
+  const uint32_t ring = smem_base + warp * (kNS * kSlotBytes);
+  const uint32_t bars = smem_base + kPlanWarps * kNS * kSlotBytes + warp * (kNS * 8);
+  uint8_t* xs = smem + kPlanWarps * kNS * kSlotBytes + kPlanWarps * kNS * 8;
   const uint32_t active_cols = kHasLo ? 2 * p.m : p.m;
   constexpr uint32_t kXsStride = kCpg * 64u;
   const uint32_t groups_max = p.xs_bytes / kXsStride;
@@ -815,7 +815,7 @@ plan_pair_kernel(const PlanParams p) {
 
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) mbar_init(bars + s * 8, 1);
+    for (int s = 0; s < kNS; ++s) mbar_init(bars + s * 8, 1);
   }
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -841,7 +841,7 @@ plan_pair_kernel(const PlanParams p) {
       prod_stride16 = it.row_stride16;
     }
     const uint32_t nc = min(static_cast<uint32_t>(kPiece), prod_left);
-    const uint32_t slot = prod_q & 1u;
+    const uint32_t slot = prod_q & (kNS - 1);
     if (lane == 0) {
       mbar_expect_tx(bars + slot * 8, 2u * nc * kCB);
       bulk_copy_g2s(ring + slot * kSlotBytes, prod_src, nc * kCB, bars + slot * 8);
@@ -854,7 +854,7 @@ plan_pair_kernel(const PlanParams p) {
     prod_q += 1;
   };
 #pragma unroll
-  for (int s = 0; s < kSlots; ++s) produce();
+  for (int s = 0; s < kNS; ++s) produce();
 
   // ---- per-lane constants of the packed MMA tile -----------------------------------------
   const uint32_t jl = (2u * t) / kCpg;      // group (inside a unit) of this lane's two C columns
@@ -1002,7 +1002,7 @@ plan_pair_kernel(const PlanParams p) {
 
       for (uint32_t first = 0; first < it.nck; first += kPiece) {
         const uint32_t nc = min(static_cast<uint32_t>(kPiece), it.nck - first);
-        const uint32_t slot = cons_q & 1u, parity = (cons_q >> 1) & 1u;
+        const uint32_t slot = cons_q & (kNS - 1), parity = (cons_q / kNS) & 1u;
         {
           uint32_t spins = 0;
           while (!mbar_try_wait(bars + slot * 8, parity)) {
@@ -1187,15 +1187,16 @@ cudaError_t configure(Plan& plan, int sm_count, bool* fits) {
   return cudaSuccess;
 }
 
-template <typename XT, bool kScaleF16, int kG, int kPiece>
+template <typename XT, bool kScaleF16, int kG, int kPiece, int kNS>
 cudaError_t configure_pair(Plan& plan, int sm_count, bool* fits) {
-  auto kernel = plan_pair_kernel<XT, kScaleF16, kG, kPiece>;
+  static_assert((kNS & (kNS - 1)) == 0, "the slot of a piece is its sequence number modulo a power of two");
+  auto kernel = plan_pair_kernel<XT, kScaleF16, kG, kPiece, kNS>;
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kCpg = 8 / kG;
   const uint32_t cb = kChunkWeightBytes + 32u * (kScaleF16 ? 2u : 4u);
   const uint32_t groups = plan.k_max / 32;
   const size_t xs_bytes = static_cast<size_t>(groups) * kCpg * 64;
-  const size_t smem = static_cast<size_t>(kPlanWarps) * kSlots * 2 * kPiece * cb + kPlanWarps * kSlots * 8 + xs_bytes +
+  const size_t smem = static_cast<size_t>(kPlanWarps) * kNS * 2 * kPiece * cb + kPlanWarps * kNS * 8 + xs_bytes +
                       static_cast<size_t>(groups) * (kHasLo ? kCpg / 2 : kCpg) * 8 +
                       static_cast<size_t>(2) * kPlanWarps * 2 * plan.m * 16 * sizeof(float) + 16 +
                       kOpWindow * sizeof(PlanOpDev);
@@ -1218,9 +1219,11 @@ cudaError_t configure_pair(Plan& plan, int sm_count, bool* fits) {
 
 template <typename XT, bool kScaleF16, int kG>
 cudaError_t configure_pair_slots(Plan& plan, int sm_count, bool* fits) {
-  cudaError_t e = configure_pair<XT, kScaleF16, kG, 4>(plan, sm_count, fits);
+  // Four slots of two chunks time the same as two slots of four (measured): what counts is the
+  // number of bytes a warp keeps in flight, and shared memory bounds that.
+  cudaError_t e = configure_pair<XT, kScaleF16, kG, 4, 2>(plan, sm_count, fits);
   if (e != cudaSuccess || *fits) return e;
-  return configure_pair<XT, kScaleF16, kG, 2>(plan, sm_count, fits);
+  return configure_pair<XT, kScaleF16, kG, 2, 2>(plan, sm_count, fits);
 }
 
 // Deep weight rings when the staged activations leave room for them, shallower ones otherwise.

@@ -341,7 +341,8 @@ class Gpu:
         import torch.distributed as dist
         handle = (ctypes.c_uint8 * 64)()
         self._check(L.kq_comm_create(self._ctx, rank, world, int(max_bytes), handle))
-        mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
+        on_device = dist.get_backend(process_group) == "nccl"  # a gloo group moves host tensors
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device if on_device else "cpu")
         gathered = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine, group=process_group)
         blob = bytes(torch.cat(gathered).cpu().numpy().tobytes())

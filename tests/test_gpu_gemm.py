@@ -69,7 +69,7 @@ def test_gemm_matches_oracle_on_prerounded_inputs(gpu, m, n, k):
     w.free()
 
 
-@pytest.mark.parametrize("m,k,n", [(512, 4096, 14336), (2048, 14336, 4096)])
+@pytest.mark.parametrize("m,k,n", [(512, 4096, 14336), (2048, 4096, 14336), (2048, 14336, 4096)])
 def test_prefill_benchmark_shapes_on_sampled_rows_and_columns(gpu, m, k, n):
     import torch
     data, scale = cases.synth_i4(n, k, seed=k)

@@ -1,7 +1,9 @@
 """Multi-GPU tests (one process per GPU, world = 2, 4 and 8 as far as the box has GPUs): libkq's
 peer-memory all-reduce against NCCL, the row-parallel linear with the exchange in its epilogue
 and the tensor-parallel decode step against the single-device oracle.  Skipped on boxes with
-fewer than two GPUs.  Nothing here makes a rank fail or hang on purpose."""
+fewer than two GPUs.  The one failure exercised is made on the host: a rank that does not join an
+exchange, so the other rank's bounded wait runs out and reports KQ_ERR_TIMEOUT; no GPU is made
+to fault or hang."""
 import os
 import sys
 
@@ -163,3 +165,59 @@ def test_all_reduce_and_tensor_parallel_step(tmp_path, world):
         path = tmp_path / f"rank{rank}.txt"
         assert path.exists(), f"rank {rank} did not finish"
         assert open(path).read() == "all_reduce=1 graph_replay=1 linear_reduce=1 tp_decode_step_plan=1 tp_decode_step_graph=1"
+
+
+def _late_rank_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)  # host-side rendezvous only
+    import karume_b200 as kb
+    gpu = kb.acquire_gpu(rank)
+    gpu.connect_ranks(rank, world, 64 * 1024)
+    notes = []
+    first = torch.full((1024,), float(rank + 1), device="cuda")
+    if rank == 0:
+        # rank 1 stays away from this exchange: the wait for its arrival flag gives up after its
+        # spin limit (a few seconds at most) and the kernel returns with the status word set
+        gpu.all_reduce(first)
+        try:
+            gpu.sync()
+            notes.append("timeout=0")
+        except kb.KqError as err:
+            notes.append("timeout=%d" % int(err.status == "KQ_ERR_TIMEOUT"))
+        gpu.sync()  # the status is reported once; the context answers again
+    dist.barrier()
+    if rank == 1:
+        # the late rank catches up alone: rank 0's contribution of that exchange is still in its slot
+        gpu.all_reduce(first)
+        gpu.sync()
+        notes.append("late=%d" % int(bool(torch.all(first == 3.0))))
+    dist.barrier()
+    ok = True
+    for i in range(3):  # and both ranks are in step again
+        t = torch.full((4096,), float(rank + 1 + i), device="cuda")
+        gpu.all_reduce(t)
+        gpu.sync()
+        ok = ok and bool(torch.all(t == float(3 + 2 * i)))
+        dist.barrier()
+    notes.append("after=%d" % int(ok))
+    with open(os.path.join(out_dir, f"late{rank}.txt"), "w") as f:
+        f.write(" ".join(notes))
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+def test_a_rank_that_stays_away_makes_the_wait_give_up_and_the_context_survives(tmp_path):
+    import torch.multiprocessing as mp
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    port = 29950 + os.getpid() % 40
+    ctx = mp.spawn(_late_rank_worker, args=(2, port, str(tmp_path)), nprocs=2, join=False, daemon=True)
+    ctx.join(timeout=120)
+    assert open(tmp_path / "late0.txt").read() == "timeout=1 after=1"
+    assert open(tmp_path / "late1.txt").read() == "late=1 after=1"

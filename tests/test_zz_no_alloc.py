@@ -1,10 +1,9 @@
 """kq_linear_static: the entry point for hosts that cannot allocate device memory while
 serving (all of HBM already belongs to their own pool, or a cudaMalloc's device-wide
 synchronisation does not fit their latency budget).  It must give the same answer as
-kq_linear while taking its scratch from the library's static device array.
-
-The file name sorts last on purpose: a run that stops at the first failure has already
-been through every other test when it gets here.
+kq_linear while taking its scratch from the library's static device array: the result is
+checked against the CPU oracle and against kq_linear, and the device's free memory
+(cudaMemGetInfo) must read the same before and after the calls.
 """
 import ctypes
 
@@ -33,11 +32,20 @@ def test_static_scratch_linear_matches_the_allocating_entry_point_twice_in_a_row
             bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
             want = gpu.linear(x, w, bias)  # the existing entry point (kq_linear)
             gpu.sync()
+            truth = oracle.linear_i4(x.cpu().numpy(), data, scale, bias.cpu().numpy(), n, k, 32)
+            outs = [torch.full((m, n), float("nan"), device="cuda") for _ in range(2)]
+            torch.cuda.synchronize()
+            free_before, _ = torch.cuda.mem_get_info()  # cudaMemGetInfo
             for repeat in range(2):  # two calls in a row share the static array
-                got = torch.full((m, n), float("nan"), device="cuda")
                 rc = L.kq_linear_static(gpu._ctx, w.handle, x.data_ptr(), kb.KQ_F32, bias.data_ptr(),
-                                        got.data_ptr(), m)
+                                        outs[repeat].data_ptr(), m)
                 assert rc == 0, (L.kq_last_error(gpu._ctx) or b"").decode()
+            gpu.sync()
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before, (free_before, free_after)  # nothing allocated, nothing freed
+            for repeat, got in enumerate(outs):
+                rep = oracle.allclose(got.cpu().numpy(), truth, atol=ATOL, rtol=RTOL)
+                assert rep["pass"], (call, repeat, rep)
                 rep = oracle.allclose(got.cpu().numpy(), want.cpu().numpy(), atol=ATOL, rtol=RTOL)
                 assert rep["pass"], (call, repeat, rep)
             w.free()
