@@ -208,7 +208,7 @@ def kernel_sweep(gpu):
     import torch
     out = {}
 
-    def gemv(storage, k, n, m, dtype, a8=False):
+    def gemv(storage, k, n, m, dtype, a8=False, tc=False):
         if storage == "i4":
             data, scale = synth_weight(1, f"sweep.{n}x{k}", n, k)
         else:
@@ -226,6 +226,8 @@ def kernel_sweep(gpu):
         for w in ws:
             if a8:
                 gpu.linear_a8(xq, xs, w, bias, out=y)
+            elif tc:  # the same linear through the tcgen05 entry point (kq_linear_tc)
+                gpu.linear_tc(x, [w], [bias], [y])
             else:
                 gpu.linear(x, w, bias, out=y)
         g = gpu.graph_end()
@@ -248,7 +250,10 @@ def kernel_sweep(gpu):
     out["gemv_i4_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i4", 1536, 151936, 1, torch.float32)
     out["gemv_i8_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i8", 1536, 151936, 1, torch.float32)
     out["gemv_i4_m8_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 8, torch.float16)
+    out["gemv_i4_m16_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 16, torch.float16)
     out["gemv_i4_m16_4096x11008_f32 (config 2 shape, f32 rows)"] = gemv("i4", 4096, 11008, 16, torch.float32)
+    out["gemv_i4_m8_4096x11008_f16 through kq_linear_tc (tcgen05)"] = gemv("i4", 4096, 11008, 8, torch.float16, tc=True)
+    out["gemv_i4_m16_4096x11008_f16 through kq_linear_tc (tcgen05)"] = gemv("i4", 4096, 11008, 16, torch.float16, tc=True)
     out["gemv_i4_m1_4096x128256_f32 (config 4 lm head)"] = gemv("i4", 4096, 128256, 1, torch.float32)
     out["w8a8_m1_1536x151936 (integer dot, config 1 lm head)"] = gemv("i8", 1536, 151936, 1, torch.float32, a8=True)
     out["w4a8_m1_4096x128256 (integer dot, config 4 lm head)"] = gemv("i4", 4096, 128256, 1, torch.float32, a8=True)
@@ -442,6 +447,14 @@ def run_cuda(args):
     tok_s = args.batch / (per_step_ms * 1e-3)
     tok_s_e2e = args.batch / (per_step_e2e * 1e-3)
 
+    phases = None
+    if args.phases and step.fused:
+        # every rank runs the profiled launch (the fused kernel exchanges partial sums with its
+        # peers); rank 0 reports its own CTAs
+        barrier()
+        phases = phase_table(gpu, step, cfg)
+        barrier()
+
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         bytes_rank = cfg.algorithmic_bytes(args.batch, world)
@@ -474,7 +487,6 @@ def run_cuda(args):
             threads = host_threads()
             tok_cpu, _, desc = cpu_sample(cfg, args.batch, threads, 3)
             cpu = {"value": tok_cpu, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc}
-        phases = phase_table(gpu, step, cfg) if (args.phases and step.fused and world == 1) else None
         line = {
             "metric": "decode_matmul_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm, "ms_per_step": per_step_ms, "higher_is_better": True,

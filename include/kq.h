@@ -234,6 +234,18 @@ KQ_API int kq_linear_host(kq_ctx* ctx, kq_weight w, const void* x_host, int x_dt
  *    on the GPU (different streams or contexts of one device) race on it, so the call
  *    returns only after its kernel has finished and must not be issued concurrently.
  *  - Weight, x, bias and out are the caller's, exactly as for kq_linear. */
+/* The same linear (one to four weights on one x, as kq_linear_multi) on the tcgen05 tensor
+ * cores: the weights are the 128-row side of the MMA, written into tensor memory straight from
+ * the packed layout, the activations its 16 columns, one f32 accumulator per scale group.
+ * Covered: tiled int4 / group-32 weights of one k and scale type, 5..16 binary16 rows or 5..8
+ * f32 / bf16 rows, k % 64 == 0; anything else returns KQ_ERR_UNSUPPORTED.  Same results contract
+ * as kq_linear.  kq_linear does not route here: on B200 the mma.sync kernels it uses are faster
+ * for these shapes (an MMA of 16 columns costs the tensor core as much as one of 64, and tensor
+ * memory bounds how many 64-k steps can be in flight); the entry point exists so that a host can
+ * choose and measure.  Uses the context's scratch; cannot be recorded into a fused plan. */
+KQ_API int kq_linear_tc(kq_ctx* ctx, uint32_t count, const kq_weight* w, uint64_t x_dptr, int x_dtype,
+                        const uint64_t* bias_dptr, const uint64_t* out_dptr, uint32_t m);
+
 KQ_API int kq_linear_static(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
                             uint64_t out_dptr, uint32_t m);
 

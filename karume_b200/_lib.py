@@ -59,6 +59,7 @@ SYMBOLS = {
     "kq_weight_dequant": (_i32, [_vp, _u64, _u64]),
     "kq_linear": (_i32, [_vp, _u64, _u64, _i32, _u64, _u64, _u32]),
     "kq_linear_multi": (_i32, [_vp, _u32, _pu64, _u64, _i32, _pu64, _pu64, _u32]),
+    "kq_linear_tc": (_i32, [_vp, _u32, _pu64, _u64, _i32, _pu64, _pu64, _u32]),
     "kq_linear_host": (_i32, [_vp, _u64, _vp, _i32, _u64, _vp, _u32]),
     "kq_linear_static": (_i32, [_vp, _u64, _u64, _i32, _u64, _u64, _u32]),
     "kq_rms_norm": (_i32, [_vp, _u64, _u64, ctypes.c_float, _u64, _u32, _u32]),

@@ -33,7 +33,7 @@ struct kq_ctx {
   uint64_t workspace_bytes = 0;
   unsigned int* counters = nullptr;
   uint32_t counter_count = 0;
-  int* gemm_status_host = nullptr;  // mapped, page-locked: non-zero once a bounded wait of the tcgen05 GEMM gave up
+  int* gemm_status_host = nullptr;  // mapped, page-locked: non-zero once a bounded wait of a tcgen05 kernel gave up
   int* gemm_status_dev = nullptr;
   int sm_count = 0;
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
@@ -99,6 +99,7 @@ kq::LaunchEnv env_of(kq_ctx* ctx) {
   env.counters = ctx->counters;
   env.counter_count = ctx->counter_count;
   env.sm_count = ctx->sm_count;
+  env.status = ctx->gemm_status_dev;
   return env;
 }
 
@@ -444,7 +445,7 @@ int kq_sync(kq_ctx* ctx) {
   if (*reinterpret_cast<volatile int*>(ctx->gemm_status_host) != 0) {
     const int code = *reinterpret_cast<volatile int*>(ctx->gemm_status_host);
     *reinterpret_cast<volatile int*>(ctx->gemm_status_host) = 0;
-    return fail(ctx, KQ_ERR_TIMEOUT, "a bounded wait inside the tcgen05 GEMM gave up (stage %d); its outputs are not valid", code);
+    return fail(ctx, KQ_ERR_TIMEOUT, "a bounded wait inside a tcgen05 kernel gave up (stage %d); its outputs are not valid", code);
   }
   if (ctx->comm && kq::comm_take_status(ctx->comm) != 0)
     return fail(ctx, KQ_ERR_TIMEOUT, "kq_all_reduce: a peer did not arrive within the bounded wait; the outputs are not valid");
@@ -741,6 +742,33 @@ int kq_linear_static(kq_ctx* ctx, kq_weight h, uint64_t x_dptr, int x_dtype, uin
   ctx->launches += 1;
   if (device_status != 0)
     return fail(ctx, KQ_ERR_TIMEOUT, "kq_linear_static: a bounded wait inside the kernel gave up; the output is not valid");
+  return KQ_OK;
+}
+
+int kq_linear_tc(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x_dptr, int x_dtype,
+                 const uint64_t* bias_dptr, const uint64_t* out_dptr, uint32_t m) {
+  if (!ctx) return KQ_ERR_BAD_ARG;
+  if (ctx->recording) return fail(ctx, KQ_ERR_STATE, "kq_linear_tc cannot be recorded into a fused plan");
+  if (count < 1 || count > static_cast<uint32_t>(kq::kMaxMulti) || !handles || !bias_dptr || !out_dptr)
+    return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_tc: 1..%d weights with their bias and output pointers", kq::kMaxMulti);
+  kq::LinearTarget targets[kq::kMaxMulti];
+  for (uint32_t i = 0; i < count; ++i) {
+    const Weight* w = find_weight(ctx, handles[i]);
+    const int rc = check_linear_args(ctx, w, x_dptr, x_dtype, bias_dptr[i], out_dptr[i]);
+    if (rc != KQ_OK) return rc;
+    targets[i] = kq::LinearTarget{w, reinterpret_cast<const float*>(bias_dptr[i]), reinterpret_cast<float*>(out_dptr[i])};
+  }
+  const kq::LaunchEnv env = env_of(ctx);
+  if (!kq::qgemv_i4_tc_supports(static_cast<int>(count), targets, x_dtype, m, env.sm_count))
+    return fail(ctx, KQ_ERR_UNSUPPORTED,
+                "kq_linear_tc: tiled int4 / group-32 weights of one k and scale type, 5..16 binary16 rows or 5..8 f32 / bf16 "
+                "rows, and a k whose activation image fits shared memory (got m=%u, k=%u)", m, targets[0].w ? targets[0].w->k : 0u);
+  DeviceGuard guard(ctx->device);
+  int launched = 0;
+  cudaError_t e = kq::launch_qgemv_i4_tc(env, static_cast<int>(count), targets, reinterpret_cast<const void*>(x_dptr), x_dtype, m,
+                                         &launched);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "kq_linear_tc");
+  ctx->launches += launched;
   return KQ_OK;
 }
 

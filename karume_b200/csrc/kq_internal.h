@@ -66,6 +66,7 @@ struct LaunchEnv {
   uint32_t counter_count;
   int sm_count;
   const FusedCommDev* fused = nullptr;  // non-null: add the output across ranks in the epilogue
+  int* status = nullptr;  // device-visible word a kernel sets when one of its bounded waits gives up
 };
 
 // Generic kernels: any shape the storage contract allows, native layout.
@@ -90,6 +91,12 @@ cudaError_t launch_qgemv_i8(const LaunchEnv& env, const LinearTarget& target, co
 bool qgemv_i4_supports(const Weight& w, uint32_t m);
 cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget* targets,
                             const void* x, int x_dtype, uint32_t m, int* launches);
+
+// The same on the tcgen05 tensor cores (kq_qgemv_i4_tc.cu): 5..16 binary16 rows or 5..8 f32 /
+// bf16 rows.  Needs env.status.
+bool qgemv_i4_tc_supports(int count, const LinearTarget* targets, int x_dtype, uint32_t m, int sm_count);
+cudaError_t launch_qgemv_i4_tc(const LaunchEnv& env, int count, const LinearTarget* targets, const void* x, int x_dtype,
+                               uint32_t m, int* launches);
 
 }  // namespace kq
 

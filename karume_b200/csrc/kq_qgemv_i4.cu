@@ -903,29 +903,6 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
 // have to multiply every C value of every group; a per-row one leaves the inner loop alone and
 // is applied once in the epilogue).  One CTA per activation row: largest magnitude of the row,
 // then scale[row] = 2^e and inv[row] = 2^-e (kq_gemv_core.cuh: pow2_prescale).
-template <typename XT>
-__global__ void __launch_bounds__(256)
-row_scale_kernel(const XT* __restrict__ x, uint32_t k, float* scale, float* inv) {
-  const XT* row = x + static_cast<size_t>(blockIdx.x) * k;
-  float amax = 0.0f;
-  for (uint32_t i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {  // k is a multiple of 64
-    float v[8];
-    load_x8<XT>(row + i, v);
-    amax = fmaxf(amax, absmax8(v));
-  }
-#pragma unroll
-  for (int offset = 16; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
-  __shared__ float part[8];
-  if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = amax;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, part[w]);
-    const Pow2 ps = pow2_prescale(amax);
-    scale[blockIdx.x] = ps.scale;
-    inv[blockIdx.x] = ps.inv;
-  }
-}
-
 template <typename XT, int kTiles>
 __global__ void __launch_bounds__(256)
 stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t* xs, float* corr,

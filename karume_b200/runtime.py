@@ -222,6 +222,23 @@ class Gpu:
             arr(*[b.data_ptr() for b in biases]), arr(*[o.data_ptr() for o in outs]), m))
         return outs
 
+    def linear_tc(self, x, weights, biases, outs=None):
+        """linear_multi on the tcgen05 tensor cores (kq_linear_tc): 5..16 binary16 rows or 5..8
+        f32 / bf16 rows, tiled int4 weights; raises KQ_ERR_UNSUPPORTED for anything else."""
+        torch = _torch()
+        x = x.contiguous()
+        k = weights[0].k
+        m = x.numel() // k
+        if outs is None:
+            outs = [torch.empty(tuple(x.shape[:-1]) + (w.n,), dtype=torch.float32, device=x.device)
+                    for w in weights]
+        cnt = len(weights)
+        arr = ctypes.c_uint64 * cnt
+        self._check(L.kq_linear_tc(
+            self._ctx, cnt, arr(*[w.handle for w in weights]), x.data_ptr(), _tensor_dtype_code(x),
+            arr(*[b.data_ptr() for b in biases]), arr(*[o.data_ptr() for o in outs]), m))
+        return outs
+
     # -- the matmul's neighbours in a decoder layer -------------------------------------------
     def rms_norm(self, x, weight, eps: float, out=None):
         """out = x * rsqrt(mean(x^2, last dim) + eps) * weight, f32 (the reference's rms_norm op)."""
