@@ -901,23 +901,53 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
 // matmul, and every CTA would repeat it for its k range; this way a CTA only copies bytes.
 // The wide kernel pre-scales each activation ROW by one power of two (a per-group factor would
 // have to multiply every C value of every group; a per-row one leaves the inner loop alone and
-// is applied once in the epilogue).  One CTA per activation row: largest magnitude of the row,
-// then scale[row] = 2^e and inv[row] = 2^-e (kq_gemv_core.cuh: pow2_prescale).
+// is applied once in the epilogue): scale[row] = 2^e, inv[row] = 2^-e (kq_gemv_core.cuh:
+// pow2_prescale).
+// One launch: CTA (row, slice) finds the largest magnitude of its activation row (every slice
+// of a row repeats that pass: a row is at most a few tens of KB, read from L2), derives the
+// row's power-of-two scale, and converts its slice of the row's 32-k groups.  Slice 0 also
+// publishes scale[row] and inv[row] = 2^-e for the matmul's epilogue.
 template <typename XT, int kTiles>
 __global__ void __launch_bounds__(256)
-stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t* xs, float* corr,
-                      const float* __restrict__ row_scale) {
+stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t* xs, float* corr, float* scale_out,
+                      float* inv_out) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kLoOffset = kTiles * 512u;
   constexpr uint32_t kXsStride = kLoOffset * (kHasLo ? 2u : 1u);
-  constexpr uint32_t kGroupsPerCta = 8;
-  const uint32_t groups = k / 32;
-  const uint32_t group0 = blockIdx.x * kGroupsPerCta;
-  if (group0 >= groups) return;
-  const uint32_t ng = min(kGroupsPerCta, groups - group0);
-  stage_x<XT, kHasLo, kTiles * 8, false, 1, false>(x, m, k, group0, ng, xs + static_cast<size_t>(group0) * kXsStride,
-                                                   kXsStride, corr + static_cast<size_t>(group0) * (kTiles * 8),
-                                                   kHasLo ? kLoOffset : 0u, row_scale);
+  const uint32_t row = blockIdx.x, slice = blockIdx.y, slices = gridDim.y;
+  const XT* xr = x + static_cast<size_t>(row) * k;
+  float amax = 0.0f;
+  for (uint32_t i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {  // k is a multiple of 64
+    float v[8];
+    load_x8<XT>(xr + i, v);
+    amax = fmaxf(amax, absmax8(v));
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+  __shared__ float part[8];
+  __shared__ float scale_s[16];
+  if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, part[w]);
+    const Pow2 ps = pow2_prescale(amax);
+    scale_s[row] = ps.scale;
+    if (slice == 0) {
+      scale_out[row] = ps.scale;
+      inv_out[row] = ps.inv;
+    }
+  }
+  __syncthreads();
+  const uint32_t groups = k / 32, per_slice = (groups + slices - 1) / slices;
+  const uint32_t g0 = min(slice * per_slice, groups), g1 = min(g0 + per_slice, groups);
+  const uint32_t items = (g1 - g0) * 4, items_padded = (items + 31u) & ~31u;  // whole warps run the shuffles
+  for (uint32_t item = threadIdx.x; item < items_padded; item += blockDim.x) {
+    const bool valid = item < items;
+    const uint32_t lg = g0 + (item >> 2), q = item & 3u;
+    float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (valid) load_x8<XT>(xr + (static_cast<size_t>(lg) << 5) + (q << 3), v);
+    stage_octet<kHasLo, kTiles * 8, false>(v, valid, q, row, lg, xs, kXsStride, corr, kHasLo ? kLoOffset : 0u, scale_s);
+  }
 }
 
 // ---- wide variant: more than 4 MMA columns (3 to 16 activation rows) -------------------
@@ -1176,8 +1206,8 @@ cudaError_t launch_typed_wide(const LaunchEnv& env, GemvParams& p, int count, co
   const size_t slab_bytes = static_cast<size_t>(p.slab_chunks) * per_chunk;
   const size_t red_bytes = splits > 1 ? static_cast<size_t>(p.m) * kTileRowsCta * sizeof(float) : 0;
 
-  // Convert the activations once per launch, into the context's scratch: the row scales first
-  // (one CTA per activation row), then the staged halves and the "-8 sum x" terms.
+  // Convert the activations once per launch, into the context's scratch: row scales, staged
+  // halves and the "-8 sum x" terms, one pre-kernel.
   const uint32_t groups = p.k / 32;
   const size_t xs_total = static_cast<size_t>(groups) * (kTiles * 512u * (kHasLo ? 2u : 1u));
   const size_t corr_total = static_cast<size_t>(groups) * kTiles * 8u * sizeof(float);
@@ -1188,15 +1218,15 @@ cudaError_t launch_typed_wide(const LaunchEnv& env, GemvParams& p, int count, co
     uint8_t* ws = static_cast<uint8_t*>(env.workspace);
     float* corr_ws = reinterpret_cast<float*>(ws + xs_total);
     float* scale_ws = reinterpret_cast<float*>(ws + xs_total + corr_total);
-    row_scale_kernel<XT><<<p.m, 256, 0, env.stream>>>(static_cast<const XT*>(p.x), p.k, scale_ws, scale_ws + 16);
-    stage_x_global_kernel<XT, kTiles><<<(groups + 7) / 8, 256, 0, env.stream>>>(
-        static_cast<const XT*>(p.x), p.m, p.k, ws, corr_ws, scale_ws);
+    const uint32_t slices = std::max(1u, std::min(8u, groups / 32));  // at least 32 groups per CTA
+    stage_x_global_kernel<XT, kTiles><<<dim3(p.m, slices), 256, 0, env.stream>>>(
+        static_cast<const XT*>(p.x), p.m, p.k, ws, corr_ws, scale_ws, scale_ws + 16);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     p.staged_xs = ws;
     p.staged_corr = corr_ws;
     p.staged_inv = scale_ws + 16;
-    if (extra_launches) *extra_launches += 2;
+    if (extra_launches) *extra_launches += 1;
   }
 
   cudaLaunchConfig_t cfg = {};
