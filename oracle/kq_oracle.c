@@ -16,7 +16,12 @@
  *     (packages/runtime/tests/fixtures/golden/i8_weights), and
  *   - vectors produced by importing the reference's Python exporter
  *     (karume.quantize / karume.emit), whose `dequantize_int4/int8` are the
- *     producer-side witnesses of the same single-rounding dequant rule.
+ *     producer-side witnesses of the same single-rounding dequant rule,
+ *   - the known answers of packages/runtime/tests/i8a8_reference_test.ts for the
+ *     integer-dot functions.
+ * The neighbour formulas at the end of the file (rms_norm, sigmoid / silu-mul, add) have
+ * no golden output in the reference's tests: for those three, PARITY IS UNPINNED (they are
+ * restated formulas checked against hand-computed values).
  *
  * Build: -O2/-O3 WITHOUT -ffast-math.  FP contraction is irrelevant to the f64
  * paths (an f32*f32 product is exact in f64) and is pinned off by the Makefile
