@@ -508,7 +508,7 @@ def run_cuda(args):
                          "algorithmic_bytes_per_launch": bytes_rank / max(1, launches_per_step),
                          # dram read+write of one launch: measured with ncu on a 2-layer, 1-GPU case of the
                          # same kernel (all of it weights, so it scales with the rank's weight bytes)
-                         "traffic": (bytes_rank * 1.002) if step.fused else None,
+                         "traffic": (bytes_rank * 1.004) if step.fused else None,
                          "traffic_source": "ncu capture of the 2-layer 1-GPU case of the same kernel, scaled by this rank's weight bytes"
                                            if step.fused else None},
             "parity": parity,
