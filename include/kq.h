@@ -358,7 +358,11 @@ KQ_API int kq_plan_profile(kq_ctx* ctx, kq_plan plan, uint64_t* stamps, uint64_t
  * that reads the peers' buffers over NVLink; the sum is taken in rank order, so all ranks
  * hold the same bits.  Every rank must issue the same sequence of kq_all_reduce calls.
  * The kernel can be captured in a CUDA graph.  A peer that does not arrive within the
- * kernel's bounded wait is reported by the next kq_sync as KQ_ERR_TIMEOUT. */
+ * kernel's bounded wait is reported by the next kq_sync as KQ_ERR_TIMEOUT (the context stays
+ * usable; a rank that was late can still make the same call and catches up).
+ * Teardown: kq_destroy unmaps the peers' buffers and frees the exported one.  All ranks must
+ * have finished their last exchange (kq_sync) and met at a host-side barrier before any of
+ * them calls kq_destroy, so that no peer's kernel still reads or writes the freed buffer. */
 KQ_API int kq_comm_create(kq_ctx* ctx, uint32_t rank, uint32_t world, uint64_t max_bytes, uint8_t* out_handle);
 KQ_API int kq_comm_connect(kq_ctx* ctx, const uint8_t* all_handles);
 KQ_API int kq_all_reduce(kq_ctx* ctx, uint64_t f32_dptr, uint64_t count);
