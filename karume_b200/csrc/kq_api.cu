@@ -35,6 +35,10 @@ struct kq_ctx {
   uint32_t counter_count = 0;
   int* gemm_status_host = nullptr;  // mapped, page-locked: non-zero once a bounded wait of a tcgen05 kernel gave up
   int* gemm_status_dev = nullptr;
+  // neighbours kq_linear_fused hands to the next wide-GEMV launch (set and cleared around one call)
+  const float* nb_norm_weight = nullptr;
+  float nb_norm_eps = 0.0f;
+  const float* nb_residual = nullptr;
   int sm_count = 0;
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
   uint64_t launches = 0;
@@ -100,6 +104,9 @@ kq::LaunchEnv env_of(kq_ctx* ctx) {
   env.counter_count = ctx->counter_count;
   env.sm_count = ctx->sm_count;
   env.status = ctx->gemm_status_dev;
+  env.norm_weight = ctx->nb_norm_weight;
+  env.norm_eps = ctx->nb_norm_eps;
+  env.residual = ctx->nb_residual;
   return env;
 }
 
@@ -1033,7 +1040,43 @@ int kq_linear_fused(kq_ctx* ctx, uint32_t count, const kq_weight* w, uint64_t x_
   }
   if (m == 0) return KQ_OK;
   DeviceGuard guard(ctx->device);
-  // Outside a plan: the same arithmetic as a sequence of kernels.
+  // Outside a plan: the same arithmetic as a sequence of kernels — except where the GEMV takes
+  // the norm and the residual into its own launches (five and more rows, tiled int4 weights).
+  {
+    kq::LinearTarget probe[kq::kMaxMulti];
+    bool known = true;
+    for (uint32_t i = 0; i < count; ++i) {
+      probe[i] = kq::LinearTarget{find_weight(ctx, w[i]), nullptr, nullptr};
+      known = known && probe[i].w != nullptr;
+    }
+    if (known && !reduce &&
+        kq::qgemv_i4_fuses_neighbours(static_cast<int>(count), probe, x_dtype, m) && (norm_weight_dptr || residual_dptr)) {
+      int rc;
+      if (swiglu) {
+        const uint64_t each = static_cast<uint64_t>(m) * w0->n;
+        rc = grow_scratch(ctx, &ctx->fused_gu, &ctx->fused_gu_bytes, 2 * each * sizeof(float), "kq_linear_fused");
+        if (rc != KQ_OK) return rc;
+        if (!out_dptr[0]) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: out is null");
+        const uint64_t outs[2] = {reinterpret_cast<uint64_t>(ctx->fused_gu), reinterpret_cast<uint64_t>(ctx->fused_gu + each)};
+        ctx->nb_norm_weight = reinterpret_cast<const float*>(norm_weight_dptr);
+        ctx->nb_norm_eps = norm_eps;
+        rc = run_linear(ctx, 2, w, x_dptr, x_dtype, bias_dptr, outs, m);
+        ctx->nb_norm_weight = nullptr;
+        if (rc != KQ_OK) return rc;
+        cudaError_t e = kq::launch_silu_mul(env_of(ctx), ctx->fused_gu, ctx->fused_gu + each, reinterpret_cast<float*>(out_dptr[0]), each);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "silu_mul launch");
+        ctx->launches += 1;
+        return KQ_OK;
+      }
+      ctx->nb_norm_weight = reinterpret_cast<const float*>(norm_weight_dptr);
+      ctx->nb_norm_eps = norm_eps;
+      ctx->nb_residual = reinterpret_cast<const float*>(residual_dptr);
+      rc = run_linear(ctx, count, w, x_dptr, x_dtype, bias_dptr, out_dptr, m);
+      ctx->nb_norm_weight = nullptr;
+      ctx->nb_residual = nullptr;
+      return rc;
+    }
+  }
   uint64_t x_eff = x_dptr;
   if (norm_weight_dptr) {
     if (!x_dptr) return fail(ctx, KQ_ERR_BAD_ARG, "kq_linear_fused: x is null");

@@ -67,6 +67,12 @@ struct LaunchEnv {
   int sm_count;
   const FusedCommDev* fused = nullptr;  // non-null: add the output across ranks in the epilogue
   int* status = nullptr;  // device-visible word a kernel sets when one of its bounded waits gives up
+  // Neighbours the wide GEMV (5..16 activation rows, one weight or several) takes into its own
+  // launches when qgemv_i4_fuses_neighbours() says so: an rms_norm of the f32 activations in its
+  // staging pre-kernel and a residual [m, n] (single weight; may alias the output) in its stores.
+  const float* norm_weight = nullptr;
+  float norm_eps = 0.0f;
+  const float* residual = nullptr;
 };
 
 // Generic kernels: any shape the storage contract allows, native layout.
@@ -89,6 +95,7 @@ cudaError_t launch_qgemv_i8(const LaunchEnv& env, const LinearTarget& target, co
 // Tensor-core GEMV for the tiled int4 layout, m <= 16.  Returns cudaErrorInvalidValue
 // when the request needs more workspace than the context owns.
 bool qgemv_i4_supports(const Weight& w, uint32_t m);
+bool qgemv_i4_fuses_neighbours(int count, const LinearTarget* targets, int x_dtype, uint32_t m);
 cudaError_t launch_qgemv_i4(const LaunchEnv& env, int count, const LinearTarget* targets,
                             const void* x, int x_dtype, uint32_t m, int* launches);
 

@@ -77,6 +77,7 @@ struct GemvParams {
   const uint8_t* staged_xs;
   const float* staged_corr;
   const float* staged_inv;  // [m]: 2^-e of every activation row (wide kernel)
+  const float* residual;    // null, or [m, n] added to the single output (wide kernel; may alias the output)
   // Non-null: a row-parallel shard; the outputs are added across ranks in the epilogue.
   const FusedCommDev* fcomm;
 };
@@ -132,7 +133,9 @@ __device__ __forceinline__ void cluster_reduce_store(const GemvParams& p, float*
     float sum = 0.0f;
     for (uint32_t s = 0; s < p.splits; ++s) sum += ld_cluster_f32(cluster_map_shared(local, s));
     const uint32_t row = tile * tile_rows + r;
-    out[static_cast<size_t>(mm) * n + row] = fmaf(sum, kUnscale, bias[row]);
+    float v = fmaf(sum, kUnscale, bias[row]);
+    if (p.residual != nullptr) v = __fadd_rn(v, p.residual[static_cast<size_t>(mm) * n + row]);
+    out[static_cast<size_t>(mm) * n + row] = v;
   }
   cluster_sync_all();  // nobody's shared memory may go away while a peer still reads it
 }
@@ -910,22 +913,56 @@ cudaError_t launch_typed_gp(const LaunchEnv& env, GemvParams& p, int count, cons
 template <typename XT, int kTiles>
 __global__ void __launch_bounds__(256)
 stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t* xs, float* corr, float* scale_out,
-                      float* inv_out) {
+                      float* inv_out, const float* __restrict__ norm_weight, float norm_eps) {
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kLoOffset = kTiles * 512u;
   constexpr uint32_t kXsStride = kLoOffset * (kHasLo ? 2u : 1u);
   const uint32_t row = blockIdx.x, slice = blockIdx.y, slices = gridDim.y;
   const XT* xr = x + static_cast<size_t>(row) * k;
+  __shared__ float part[8];
+  __shared__ float scale_s[16];
+  __shared__ float r_inv_s;
+  // With an rms_norm in front (packages/runtime/src/kernels/rms-norm.ts:60-90) what is staged is
+  // (x * rsqrt(mean(x^2) + eps)) * weight: one more pass over the row for the sum of squares,
+  // added in a fixed order (thread-strided, shuffle tree, warps in order).
+  float r_inv = 1.0f;
+  if (norm_weight != nullptr) {
+    float sq = 0.0f;
+    for (uint32_t i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {
+      float v[8];
+      load_x8<XT>(xr + i, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq = fmaf(v[e], v[e], sq);
+    }
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float total = 0.0f;
+      for (int w = 0; w < 8; ++w) total += part[w];
+      r_inv_s = rsqrtf(total * (1.0f / static_cast<float>(k)) + norm_eps);
+    }
+    __syncthreads();
+    r_inv = r_inv_s;
+  }
+  auto load_row8 = [&](uint32_t i, float (&v)[8]) {
+    load_x8<XT>(xr + i, v);
+    if (norm_weight != nullptr) {
+      const float4 w0 = __ldg(reinterpret_cast<const float4*>(norm_weight + i));
+      const float4 w1 = __ldg(reinterpret_cast<const float4*>(norm_weight + i + 4));
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(__fmul_rn(v[e], r_inv), wv[e]);
+    }
+  };
   float amax = 0.0f;
   for (uint32_t i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {  // k is a multiple of 64
     float v[8];
-    load_x8<XT>(xr + i, v);
+    load_row8(i, v);
     amax = fmaxf(amax, absmax8(v));
   }
 #pragma unroll
   for (int offset = 16; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
-  __shared__ float part[8];
-  __shared__ float scale_s[16];
   if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = amax;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -945,7 +982,7 @@ stage_x_global_kernel(const XT* __restrict__ x, uint32_t m, uint32_t k, uint8_t*
     const bool valid = item < items;
     const uint32_t lg = g0 + (item >> 2), q = item & 3u;
     float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (valid) load_x8<XT>(xr + (static_cast<size_t>(lg) << 5) + (q << 3), v);
+    if (valid) load_row8((lg << 5) + (q << 3), v);
     stage_octet<kHasLo, kTiles * 8, false>(v, valid, q, row, lg, xs, kXsStride, corr, kHasLo ? kLoOffset : 0u, scale_s);
   }
 }
@@ -1162,8 +1199,13 @@ qgemv_i4_wide_kernel(const GemvParams p) {
         const float inv = __ldg(p.staged_inv + mm);  // undo the row's power-of-two pre-scale (exact)
         const float va = acc[r][tile_m][j] * inv, vb = acc[r][tile_m][2 + j] * inv;
         if (p.splits == 1) {
-          out[static_cast<size_t>(mm) * n + row_a] = fmaf(va, kUnscale, bias_a);
-          out[static_cast<size_t>(mm) * n + row_a + 8] = fmaf(vb, kUnscale, bias_b);
+          float oa = fmaf(va, kUnscale, bias_a), ob = fmaf(vb, kUnscale, bias_b);
+          if (p.residual != nullptr) {
+            oa = __fadd_rn(oa, p.residual[static_cast<size_t>(mm) * n + row_a]);
+            ob = __fadd_rn(ob, p.residual[static_cast<size_t>(mm) * n + row_a + 8]);
+          }
+          out[static_cast<size_t>(mm) * n + row_a] = oa;
+          out[static_cast<size_t>(mm) * n + row_a + 8] = ob;
         } else {
           red[mm * kTileRowsCta + tr_a] = va;
           red[mm * kTileRowsCta + tr_a + 8] = vb;
@@ -1220,7 +1262,8 @@ cudaError_t launch_typed_wide(const LaunchEnv& env, GemvParams& p, int count, co
     float* scale_ws = reinterpret_cast<float*>(ws + xs_total + corr_total);
     const uint32_t slices = std::max(1u, std::min(8u, groups / 32));  // at least 32 groups per CTA
     stage_x_global_kernel<XT, kTiles><<<dim3(p.m, slices), 256, 0, env.stream>>>(
-        static_cast<const XT*>(p.x), p.m, p.k, ws, corr_ws, scale_ws, scale_ws + 16);
+        static_cast<const XT*>(p.x), p.m, p.k, ws, corr_ws, scale_ws, scale_ws + 16, env.norm_weight, env.norm_eps);
+    p.residual = env.residual;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     p.staged_xs = ws;
@@ -1293,6 +1336,18 @@ cudaError_t launch_x(const LaunchEnv& env, GemvParams& p, int count, const Linea
 }
 
 }  // namespace
+
+// True when launch_qgemv_i4 takes this request to the wide kernel, which applies
+// env.norm_weight / env.residual itself (the branch of launch_x, restated).
+bool qgemv_i4_fuses_neighbours(int count, const LinearTarget* targets, int x_dtype, uint32_t m) {
+  if (count < 1 || count > kMaxMulti || m < 5 || m > 16) return false;
+  if (x_dtype != KQ_F32 && x_dtype != KQ_F16 && x_dtype != KQ_BF16) return false;
+  for (int i = 0; i < count; ++i) {
+    const Weight& w = *targets[i].w;
+    if (w.layout != kLayoutTiledI4 || w.k != targets[0].w->k || w.scale_dtype != targets[0].w->scale_dtype || w.n == 0) return false;
+  }
+  return true;
+}
 
 bool qgemv_i4_supports(const Weight& w, uint32_t m) {
   return w.layout == kLayoutTiledI4 && m >= 1 && m <= 16;
