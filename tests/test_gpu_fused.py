@@ -83,11 +83,15 @@ def reference_layer(mats, g1, g2, h, eps):
 
 
 @pytest.mark.parametrize("mode", ["direct", "plan"])
-@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("m", [1, 2, 5, 16])
 @pytest.mark.parametrize("hidden,ffn", [(256, 512), (1024, 2816)])
 def test_decoder_layer_of_fused_linears(gpu, mode, m, hidden, ffn):
-    """norm -> q ; o + residual ; norm -> silu(gate) * up ; down + residual, in place on h."""
+    """norm -> q ; o + residual ; norm -> silu(gate) * up ; down + residual, in place on h.
+    From five rows on, the direct form runs the norm inside the GEMV's staging pre-kernel and adds
+    the residual in its stores; a plan takes one or two rows."""
     import torch
+    if mode == "plan" and m > 2:
+        pytest.skip("fused neighbours inside a plan: one or two f32 rows")
     eps = 1e-5
     mats, g1, g2, h0 = layer_case(m, hidden, ffn, seed=hidden + m)
     W = {name: gpu.upload_weight("i4", d, s, (n, k), 32) for name, (d, s, b, n, k) in mats.items()}
