@@ -288,24 +288,28 @@ qgemm_i4_kernel(const GemmParams p) {
             "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
           : "r"(taddr));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      // A lane holds 32 consecutive outputs of ONE row: stored like that, a warp's store touches
+      // 32 different lines, 16 bytes each.  The batch goes through shared memory (the stage
+      // buffers are free: the last MMA has completed) and leaves transposed — one coalesced
+      // 128-byte store per row (wider stores, four rows each, measured slightly slower).  Row
+      // stride 36 floats: both the 16-byte writes and the 4-byte reads are bank-conflict free.
       const uint32_t col0 = n0 + cb * 32u;
-      if (row < p.m) {
-        const bool final_sum = p.splits == 1;
-        float* dst = (final_sum ? p.out : p.partial + static_cast<size_t>(blockIdx.z) * p.m * p.n) +
-                     static_cast<size_t>(row) * p.n + col0;
+      float* scratch = reinterpret_cast<float*>(generic_base) + warp * (32u * 36u);
+      __syncwarp();  // the previous batch has been read
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          if (col0 + j < p.n) {  // n is a multiple of 16, so a valid quad is wholly valid
-            const float4 b = final_sum ? *reinterpret_cast<const float4*>(p.bias + col0 + j)
-                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            float4 o;
-            o.x = __uint_as_float(v[j]) + b.x;
-            o.y = __uint_as_float(v[j + 1]) + b.y;
-            o.z = __uint_as_float(v[j + 2]) + b.z;
-            o.w = __uint_as_float(v[j + 3]) + b.w;
-            *reinterpret_cast<float4*>(dst + j) = o;
-          }
-        }
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(scratch + lane * 36u + j) =
+            make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      __syncwarp();
+      const bool final_sum = p.splits == 1;
+      const uint32_t col = col0 + lane;
+      if (col < p.n) {
+        const float b = final_sum ? p.bias[col] : 0.0f;
+        const uint32_t row_first = row - lane;  // first row of this warp's 32
+        float* dst = (final_sum ? p.out : p.partial + static_cast<size_t>(blockIdx.z) * p.m * p.n) + col;
+        const uint32_t rows_here = row_first < p.m ? min(32u, p.m - row_first) : 0u;
+        for (uint32_t rr = 0; rr < rows_here; ++rr)
+          dst[static_cast<size_t>(row_first + rr) * p.n] = scratch[rr * 36u + lane] + b;
       }
     }
   } else {
