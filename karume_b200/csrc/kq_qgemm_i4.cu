@@ -197,21 +197,44 @@ qgemm_i4_kernel(const GemmParams p) {
     // The lane's two weight chunks (and their scales) of a k-step, fetched one k-step ahead.
     uint4 wq_next[kChunksPerWarp];
     typename std::conditional<kScaleF16, uint2, uint4>::type sc_next[kChunksPerWarp];
+    // Addresses that only advance by a constant per k-step are kept in registers: the lane's
+    // word of each of its chunks (next k-step: + one chunk) ...
+    const uint8_t* chunk_ptr[kChunksPerWarp];
+    bool chunk_live[kChunksPerWarp];
+#pragma unroll
+    for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+      const uint32_t row0 = n0 + (warp * kChunksPerWarp + cc) * 16u;  // first output channel of the row block
+      chunk_live[cc] = row0 < p.n;
+      chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks_begin) * kCB + lane * 16;
+    }
+    const uint32_t scale_off = kChunkWeightBytes - lane * 16 + g * (kScaleF16 ? 8u : 16u);
     auto fetch_weights = [&](uint32_t ks) {
 #pragma unroll
       for (int cc = 0; cc < kChunksPerWarp; ++cc) {
-        const uint32_t row0 = n0 + (warp * kChunksPerWarp + cc) * 16u;  // first output channel of the row block
         wq_next[cc] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // u = 8 -> value 0
         if constexpr (kScaleF16) sc_next[cc] = make_uint2(0, 0);
         else sc_next[cc] = make_uint4(0, 0, 0, 0);
-        if (row0 < p.n && ks < ksteps) {
-          const uint8_t* chunk = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks_begin + ks) * kCB;
-          wq_next[cc] = *reinterpret_cast<const uint4*>(chunk + lane * 16);
-          if constexpr (kScaleF16) sc_next[cc] = *reinterpret_cast<const uint2*>(chunk + kChunkWeightBytes + g * 8);
-          else sc_next[cc] = *reinterpret_cast<const uint4*>(chunk + kChunkWeightBytes + g * 16);
+        if (chunk_live[cc] && ks < ksteps) {
+          wq_next[cc] = *reinterpret_cast<const uint4*>(chunk_ptr[cc]);
+          if constexpr (kScaleF16) sc_next[cc] = *reinterpret_cast<const uint2*>(chunk_ptr[cc] + scale_off);
+          else sc_next[cc] = *reinterpret_cast<const uint4*>(chunk_ptr[cc] + scale_off);
+          chunk_ptr[cc] += kCB;
         }
       }
     };
+    // ... and the source and the swizzled destination offset of the thread's activation pieces
+    // (next k-step: + 64 elements; the stage base is added per step)
+    const __nv_bfloat16* a_src[kAPiecesPerThread];
+    uint32_t a_dst[kAPiecesPerThread], a_bytes[kAPiecesPerThread];
+#pragma unroll
+    for (int i = 0; i < kAPiecesPerThread; ++i) {
+      const uint32_t piece = tid + i * (kProducerWarps * 32u);
+      const uint32_t r = piece >> 3, c = piece & 7u;
+      const bool in_range = m0 + r < p.m;
+      a_src[i] = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + ks_begin * kBK + c * 8;
+      a_dst[i] = swz(r, c);
+      a_bytes[i] = in_range ? 16u : 0u;
+    }
     fetch_weights(0);
     for (uint32_t ks = 0; ks < ksteps; ++ks) {
       const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
@@ -221,12 +244,9 @@ qgemm_i4_kernel(const GemmParams p) {
       // swizzled tile (rows past m are zero-filled); the copy flies while we dequantise
 #pragma unroll
       for (int i = 0; i < kAPiecesPerThread; ++i) {
-        const uint32_t piece = tid + i * (kProducerWarps * 32u);
-        const uint32_t r = piece >> 3, c = piece & 7u;
-        const bool in_range = m0 + r < p.m;
-        const __nv_bfloat16* src = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + (ks_begin + ks) * kBK + c * 8;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_tile + swz(r, c)), "l"(src),
-                     "r"(in_range ? 16u : 0u) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_tile + a_dst[i]), "l"(a_src[i]), "r"(a_bytes[i])
+                     : "memory");
+        a_src[i] += kBK;
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
       // weights: this k-step's chunks are already in registers; fetch the next k-step's
