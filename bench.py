@@ -214,7 +214,7 @@ def kernel_sweep(gpu):
         else:
             data, scale = synth_i8(n, k, 1)
         wbytes = data.nbytes + scale.nbytes
-        copies = max(2, min(48, int(400e6 // wbytes) + 1))
+        copies = max(2, min(128, int(400e6 // wbytes) + 1))
         ws = [gpu.upload_weight(storage, data, scale, (n, k), 32 if storage == "i4" else 0) for _ in range(copies)]
         x = torch.randn(m, k, device="cuda").to(dtype)
         bias = torch.zeros(n, device="cuda")
@@ -244,11 +244,15 @@ def kernel_sweep(gpu):
             w.free()
         alg = wbytes + m * k * (1 if a8 else x.element_size()) + m * n * 4
         us = best * 1e3 / copies
-        return {"us": round(us, 3), "GB/s": round(alg / us / 1e3, 1), "frac_of_8TB/s": round(alg / us / 1e3 / 8000, 3)}
+        return {"us": round(us, 3), "GB/s": round(alg / us / 1e3, 1), "frac_of_8TB/s": round(alg / us / 1e3 / 8000, 3),
+                "weights": "stream from HBM" if copies * wbytes > 200e6 else "L2-resident (the copies total less than L2)"}
 
     out["gemv_i4_m1_4096x4096_f32 (config 0)"] = gemv("i4", 4096, 4096, 1, torch.float32)
     out["gemv_i4_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i4", 1536, 151936, 1, torch.float32)
     out["gemv_i8_m1_1536x151936_f32 (config 1 lm head)"] = gemv("i8", 1536, 151936, 1, torch.float32)
+    for k, n in ((1536, 1536), (1536, 256), (1536, 8960), (8960, 1536)):  # config 1's projection shapes
+        out[f"gemv_i4_m1_{k}x{n}_f32 (config 1)"] = gemv("i4", k, n, 1, torch.float32)
+        out[f"gemv_i8_m1_{k}x{n}_f32 (config 1)"] = gemv("i8", k, n, 1, torch.float32)
     out["gemv_i4_m8_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 8, torch.float16)
     out["gemv_i4_m16_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 16, torch.float16)
     out["gemv_i4_m16_4096x11008_f32 (config 2 shape, f32 rows)"] = gemv("i4", 4096, 11008, 16, torch.float32)
