@@ -105,3 +105,49 @@ def test_plans_refuse_what_the_fused_kernel_does_not_cover(gpu):
     with pytest.raises(kb.KqError):
         gpu.plan_end()  # empty plan
     w.free()
+
+
+def test_a_plan_refuses_host_copies_it_could_not_replay_in_place(gpu):
+    """Host-to-device copies run before the fused kernel and device-to-host copies after it, so a
+    write recorded after the first linear, or a read recorded before it, cannot keep its place:
+    both make kq_plan_end fail (nothing is replayed in another order, no host buffer is touched)."""
+    import ctypes
+    import torch
+    import karume_b200 as kb
+    L = kb.lib
+    n, k = 64, 128
+    data, scale = cases.synth_i4(n, k, seed=2)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    x = torch.zeros(1, k, device="cuda")
+    out = torch.zeros(1, n, device="cuda")
+    bias = torch.zeros(n, device="cuda")
+    host = (ctypes.c_float * k)(*([1.0] * k))
+    host_out = (ctypes.c_float * n)(*([7.0] * n))
+
+    gpu.plan_begin()
+    gpu.linear(x, w, bias, out=out)
+    assert L.kq_buffer_write(gpu._ctx, x.data_ptr(), 0, host, k * 4) == 0  # recorded, judged at the end
+    with pytest.raises(kb.KqError) as err:
+        gpu.plan_end()
+    assert err.value.status == "KQ_ERR_UNSUPPORTED" and "writes must come before" in str(err.value)
+
+    gpu.plan_begin()
+    assert L.kq_buffer_read(gpu._ctx, out.data_ptr(), 0, host_out, n * 4) == 0
+    gpu.linear(x, w, bias, out=out)
+    with pytest.raises(kb.KqError) as err:
+        gpu.plan_end()
+    assert err.value.status == "KQ_ERR_UNSUPPORTED"
+    assert list(host_out) == [7.0] * n and list(host) == [1.0] * k  # neither host buffer was touched
+
+    # the legal order records and replays
+    gpu.plan_begin()
+    assert L.kq_buffer_write(gpu._ctx, x.data_ptr(), 0, host, k * 4) == 0
+    gpu.linear(x, w, bias, out=out)
+    assert L.kq_buffer_read(gpu._ctx, out.data_ptr(), 0, host_out, n * 4) == 0
+    plan = gpu.plan_end()
+    gpu.plan_launch(plan)
+    gpu.sync()
+    ref = oracle.linear_i4(np.ones((1, k), np.float32), data, scale.astype(np.float32), np.zeros(n, np.float32), n, k, 32)
+    assert oracle.allclose(np.array(list(host_out), np.float32).reshape(1, n), ref, atol=1e-5, rtol=1e-3)["pass"]
+    gpu.plan_free(plan)
+    w.free()
