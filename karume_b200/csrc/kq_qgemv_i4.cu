@@ -830,11 +830,12 @@ cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count
   const uint32_t units_per_row = p.k / kChunkK / kCU;  // the caller checked divisibility
   const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * kWantCtasPerSm;
   uint32_t splits = 1;
-  // ... as long as a split keeps at least six chunks of k: below that a CTA's fixed cost (staging,
-  // cluster reduction) outweighs its share of the stream (1536 -> 8960: 5.3 us with four splits
-  // of six chunks, 7.9 us with eight of at most four).
+  // ... and, once every SM has a CTA, as long as a split keeps at least six chunks of k: below that
+  // a CTA's fixed cost (staging, cluster reduction) outweighs its share of the stream
+  // (1536 -> 8960: 5.3 us with four splits of six chunks, 7.9 us with eight of at most four).
   constexpr uint32_t kMinUnits = 6 / kCU;
-  while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas && splits * 2 * kMinUnits <= units_per_row)
+  while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas && splits * 2 <= units_per_row &&
+         (tiles * splits < static_cast<uint32_t>(env.sm_count) || splits * 2 * kMinUnits <= units_per_row))
     splits *= 2;
   p.splits = splits;
   p.chunks_per_split = (units_per_row + splits - 1) / splits * kCU;

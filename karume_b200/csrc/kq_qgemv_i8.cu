@@ -345,7 +345,10 @@ cudaError_t launch_typed8(const LaunchEnv& env, Gemv8Params& p) {
   const uint32_t chunks_per_row = p.k / kChunkK8;
   const uint32_t want_ctas = static_cast<uint32_t>(env.sm_count) * 4u;
   uint32_t splits = 1;
-  while (splits < static_cast<uint32_t>(kMaxCluster8) && tiles * splits < want_ctas && splits * 2 <= chunks_per_row)
+  // once every SM has a CTA, a split keeps at least twelve 32-k chunks: below that a CTA's fixed
+  // cost outweighs its share of the stream
+  while (splits < static_cast<uint32_t>(kMaxCluster8) && tiles * splits < want_ctas && splits * 2 <= chunks_per_row &&
+         (tiles * splits < static_cast<uint32_t>(env.sm_count) || splits * 2 * 12 <= chunks_per_row))
     splits *= 2;
   p.splits = splits;
   p.chunks_per_split = (chunks_per_row + splits - 1) / splits;
