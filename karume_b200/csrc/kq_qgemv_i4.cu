@@ -811,9 +811,14 @@ cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count
                                   bool probe_only, uint32_t* ctas_out, uint32_t* capacity_out) {
   auto kernel = qgemv_i4_gp_kernel<XT, kScaleF16, kG, kD>;
   static bool configured = false;
+  static uint32_t max_cluster = kMaxCluster;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return e;
+    // few row tiles and a long k (8960 -> 1536): sixteen splits, the largest cluster the device
+    // takes with this opt-in, halve each CTA's share again
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) max_cluster = 16;
+    else (void)cudaGetLastError();
     configured = true;
   }
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
@@ -834,7 +839,8 @@ cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count
   // a CTA's fixed cost (staging, cluster reduction) outweighs its share of the stream
   // (1536 -> 8960: 5.3 us with four splits of six chunks, 7.9 us with eight of at most four).
   constexpr uint32_t kMinUnits = 6 / kCU;
-  while (splits < static_cast<uint32_t>(kMaxCluster) && tiles * splits < want_ctas && splits * 2 <= units_per_row &&
+  const uint32_t split_limit = env.fused != nullptr ? static_cast<uint32_t>(kMaxCluster) : max_cluster;
+  while (splits < split_limit && tiles * splits < want_ctas && splits * 2 <= units_per_row &&
          (tiles * splits < static_cast<uint32_t>(env.sm_count) || splits * 2 * kMinUnits <= units_per_row))
     splits *= 2;
   p.splits = splits;

@@ -334,9 +334,13 @@ template <typename XT, bool kScaleF16, int kCols, int kRB>
 cudaError_t launch_typed8(const LaunchEnv& env, Gemv8Params& p) {
   auto kernel = qgemv_i8_kernel<XT, kScaleF16, kCols, kRB>;
   static bool configured = false;
+  static uint32_t max_cluster = kMaxCluster8;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return e;
+    // few row tiles and a long k: sixteen splits (the largest cluster, by opt-in)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) max_cluster = 16;
+    else (void)cudaGetLastError();
     configured = true;
   }
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
@@ -347,7 +351,7 @@ cudaError_t launch_typed8(const LaunchEnv& env, Gemv8Params& p) {
   uint32_t splits = 1;
   // once every SM has a CTA, a split keeps at least twelve 32-k chunks: below that a CTA's fixed
   // cost outweighs its share of the stream
-  while (splits < static_cast<uint32_t>(kMaxCluster8) && tiles * splits < want_ctas && splits * 2 <= chunks_per_row &&
+  while (splits < max_cluster && tiles * splits < want_ctas && splits * 2 <= chunks_per_row &&
          (tiles * splits < static_cast<uint32_t>(env.sm_count) || splits * 2 * 12 <= chunks_per_row))
     splits *= 2;
   p.splits = splits;
