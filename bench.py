@@ -380,6 +380,9 @@ def run_cuda(args):
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL's version banner goes to stdout; rank 0's stdout carries the one JSON line
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = DecodeConfig(layers=args.layers)
     gpu = kb.acquire_gpu(local)
