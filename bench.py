@@ -366,6 +366,13 @@ def phase_table(gpu, step, cfg):
 
 
 def run_cuda(args):
+    # Libraries write banners to the process's stdout (NCCL's version line comes from native code);
+    # rank 0's stdout must carry the one JSON line only, so everything else goes to stderr and the
+    # line is written to the original descriptor at the end.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
 
@@ -380,9 +387,6 @@ def run_cuda(args):
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
     torch.cuda.set_device(local)
     if world > 1:
-        # NCCL's version banner goes to stdout; rank 0's stdout carries the one JSON line
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = DecodeConfig(layers=args.layers)
     gpu = kb.acquire_gpu(local)
@@ -526,7 +530,8 @@ def run_cuda(args):
             "clocks": clocks,
             "finite_outputs": logits_ok,
         }
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         # Tearing down NCCL communicators that a CUDA graph still references can block;
         # everything is measured and printed, so synchronise, flush and leave.
