@@ -255,8 +255,9 @@ def kernel_sweep(gpu, peak_gbs, peak_tf):
     for k, n in ((1536, 1536), (1536, 256), (1536, 8960), (8960, 1536)):  # config 1's projection shapes
         out[f"gemv_i4_m1_{k}x{n}_f32 (config 1)"] = gemv("i4", k, n, 1, torch.float32)
         out[f"gemv_i8_m1_{k}x{n}_f32 (config 1)"] = gemv("i8", k, n, 1, torch.float32)
-    out["gemv_i4_m8_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 8, torch.float16)
-    out["gemv_i4_m16_4096x11008_f16 (config 2)"] = gemv("i4", 4096, 11008, 16, torch.float16)
+    for n in (4096, 11008):  # config 2: the small-batch / verify shapes, binary16 activations
+        for m in (1, 2, 4, 8, 16):
+            out[f"gemv_i4_m{m}_4096x{n}_f16 (config 2)"] = gemv("i4", 4096, n, m, torch.float16)
     out["gemv_i4_m16_4096x11008_f32 (config 2 shape, f32 rows)"] = gemv("i4", 4096, 11008, 16, torch.float32)
     out["gemv_i4_m8_4096x11008_f16 through kq_linear_tc (tcgen05)"] = gemv("i4", 4096, 11008, 8, torch.float16, tc=True)
     out["gemv_i4_m16_4096x11008_f16 through kq_linear_tc (tcgen05)"] = gemv("i4", 4096, 11008, 16, torch.float16, tc=True)
