@@ -294,6 +294,19 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
     }
     return KQ_OK;
   }
+  if (all_tiled && kq::qgemm_i4_x32_supports(*targets[0].w, x_dtype, m) && ctx->workspace != nullptr &&
+      static_cast<uint64_t>(targets[0].w->k) * 4 * 32 <= ctx->workspace_bytes) {
+    // Prefill with f32 / binary16 activations: the split-operand tcgen05 GEMM, one weight at a time.
+    for (uint32_t i = 0; i < count; ++i) {
+      if (targets[i].w->n == 0) continue;
+      int launched = 0;
+      cudaError_t e = kq::launch_qgemm_i4_x32(env, targets[i], reinterpret_cast<const void*>(x), x_dtype, m, ctx->gemm_status_dev,
+                                              &launched);
+      if (e != cudaSuccess) return cuda_fail(ctx, e, "qgemm_i4_x32 launch");
+      ctx->launches += launched;
+    }
+    return KQ_OK;
+  }
   if (all_tiled && same_scale) {
     // Tiled int4: row panels of at most 16 activation rows per launch.
     for (uint32_t m0 = 0; m0 < m; m0 += 16) {

@@ -121,3 +121,76 @@ def test_few_output_tiles_split_k_and_reduce_in_order(gpu, m, n, k):
     assert rep["pass"], (atol, rep)
     assert np.all(np.isfinite(got))
     w.free()
+
+
+# ---- f32 / binary16 activations, m > 16: both operands as two bf16 numbers ------------------
+
+@pytest.mark.parametrize("xdt", ["f32", "f16"])
+@pytest.mark.parametrize("m,n,k", [(17, 272, 512), (130, 512, 256), (300, 784, 1024), (513, 256, 2048)])
+def test_split_operand_gemm_matches_the_f64_oracle(gpu, xdt, m, n, k):
+    """The result contract of the decode path (unrounded weights, f64-accumulate oracle) with the
+    absolute term widened to 4e-5 * max(1, rms): f32 activations are carried with 16 significant
+    bits (binary16 ones exactly), the weights exactly for binary16 scales."""
+    import torch
+    data, scale = cases.synth_i4(n, k, seed=m + n + 1)
+    rng = np.random.default_rng(m + 3)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    if xdt == "f16":
+        x = oracle.round_to_f16(x)
+    bias = rng.standard_normal(n).astype(np.float32)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    out = torch.full((m, n), float("nan"), device="cuda")
+    gpu.linear(dev(x).to(torch.float32 if xdt == "f32" else torch.float16), w, dev(bias), out=out)
+    gpu.sync()
+    ref = oracle.linear_i4(x, data, scale.astype(np.float32), bias, n, k, 32)
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    rep = oracle.allclose(out.cpu().numpy(), ref, atol=4e-5 * max(1.0, rms), rtol=1e-3)
+    assert rep["pass"], rep
+    again = torch.full((m, n), float("nan"), device="cuda")
+    gpu.linear(dev(x).to(torch.float32 if xdt == "f32" else torch.float16), w, dev(bias), out=again)
+    gpu.sync()
+    assert torch.equal(out, again)
+    w.free()
+
+
+def test_split_operand_gemm_with_binary16_inputs_is_exact_up_to_the_f32_sum(gpu):
+    """binary16 activations and binary16 scales: every product the tensor core sees is exact, so
+    the only error is the f32 accumulation — the standard tolerance holds."""
+    import torch
+    m, n, k = 64, 256, 1024
+    data, scale = cases.synth_i4(n, k, seed=9)
+    rng = np.random.default_rng(10)
+    x = oracle.round_to_f16(rng.standard_normal((m, k)).astype(np.float32))
+    bias = np.zeros(n, np.float32)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    out = gpu.linear(dev(x).to(torch.float16), w, dev(bias))
+    gpu.sync()
+    ref = oracle.linear_i4(x, data, scale.astype(np.float32), bias, n, k, 32)
+    rep = oracle.allclose(out.cpu().numpy(), ref, atol=1e-5, rtol=1e-3)
+    assert rep["pass"], rep
+    w.free()
+
+
+@pytest.mark.parametrize("m,k,n", [(512, 4096, 14336), (2048, 14336, 4096)])
+def test_split_operand_gemm_on_prefill_shapes_sampled(gpu, m, k, n):
+    """Full prefill shapes with f32 activations (the second one runs in row panels and with K split):
+    sampled rows and columns against the f64 oracle."""
+    import torch
+    data, scale = cases.synth_i4(n, k, seed=k + 1)
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    out = gpu.linear(dev(x), w, dev(bias))
+    gpu.sync()
+    got = out.cpu().numpy()
+    assert np.all(np.isfinite(got))
+    rows = rng.choice(m, 48, replace=False)
+    cols = np.sort(rng.choice(n, 384, replace=False))
+    sub = data.reshape(n, k // 2)[cols]
+    wq = oracle.decode_i4(sub, (len(cols), k), scale.astype(np.float32)[cols], (len(cols), k // 32), 32)
+    ref = oracle.linear_f64(x[rows], wq, bias[cols])
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    rep = oracle.allclose(got[np.ix_(rows, cols)], ref, atol=4e-5 * max(1.0, rms), rtol=1e-3)
+    assert rep["pass"], rep
+    w.free()
