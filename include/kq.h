@@ -69,7 +69,7 @@ enum kq_shard { KQ_SHARD_NONE = 0, KQ_SHARD_COLUMN = 1, KQ_SHARD_ROW = 2 };
 /* ---- context --------------------------------------------------------------
  * Replaces acquireGpu() -> GpuContext (packages/runtime/src/gpu/device.ts:1182-1218):
  * one device per context.  `device` is a CUDA ordinal.  workspace_bytes sizes the
- * context-owned scratch the split-K kernels use (0 = default 64 MiB). */
+ * context-owned scratch of the split-K kernels and the activation pre-kernels (0 = default 256 MiB). */
 KQ_API int kq_init(int device, uint64_t workspace_bytes, kq_ctx** out);
 KQ_API void kq_destroy(kq_ctx* ctx);
 

@@ -294,8 +294,10 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
     }
     return KQ_OK;
   }
-  if (all_tiled && kq::qgemm_i4_x32_supports(*targets[0].w, x_dtype, m) && ctx->workspace != nullptr &&
-      static_cast<uint64_t>(targets[0].w->k) * 4 * 32 <= ctx->workspace_bytes) {
+  bool x32 = all_tiled;
+  for (uint32_t i = 0; i < count && x32; ++i)
+    x32 = targets[i].w->n == 0 || kq::qgemm_i4_x32_supports(*targets[i].w, x_dtype, m, ctx->workspace ? ctx->workspace_bytes : 0);
+  if (x32) {
     // Prefill with f32 / binary16 activations: the split-operand tcgen05 GEMM, one weight at a time.
     for (uint32_t i = 0; i < count; ++i) {
       if (targets[i].w->n == 0) continue;
@@ -390,7 +392,7 @@ int kq_init(int device, uint64_t workspace_bytes, kq_ctx** out) {
   kq_ctx* ctx = new kq_ctx();
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
-  ctx->workspace_bytes = workspace_bytes ? workspace_bytes : (64ull << 20);
+  ctx->workspace_bytes = workspace_bytes ? workspace_bytes : (256ull << 20);
   ctx->counter_count = 8192;
   e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes);

@@ -113,7 +113,7 @@ bool qgemm_i4_supports(const Weight& w, int x_dtype, uint32_t m);
 cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, const void* x, uint32_t m,
                             int* status_word, int* extra_launches);
 // The same for f32 and binary16 activations (kq_qgemm_i4_x32.cu): both operands as two bf16 numbers.
-bool qgemm_i4_x32_supports(const Weight& w, int x_dtype, uint32_t m);
+bool qgemm_i4_x32_supports(const Weight& w, int x_dtype, uint32_t m, uint64_t workspace_bytes);
 cudaError_t launch_qgemm_i4_x32(const LaunchEnv& env, const LinearTarget& target, const void* x, int x_dtype, uint32_t m,
                                 int* status_word, int* launches);
 }  // namespace kq

@@ -345,11 +345,18 @@ cudaError_t launch_x32(const LaunchEnv& env, const LinearTarget& target, const X
   const uint32_t ksteps_total = w.k / kXK;
   const size_t smem = kXStages * kXStage + 1024 + 256;
   if (env.workspace == nullptr) return cudaErrorMemoryAllocation;
+  // The tensor core's f32 accumulation truncates: over a chain of c accumulating MMAs the sum
+  // drifts by about c * 2^-24 of its magnitude (measured: 3.5e-4 of the output's rms over
+  // k = 14336 in one chain, 2,688 MMAs).  A chain therefore covers at most 32 k-steps (2048 k, 384
+  // MMAs); longer K is split over blockIdx.z and the slices are added in IEEE f32 by
+  // x32_reduce_kernel, whatever the number of tiles.
+  const uint32_t chain_splits = (ksteps_total + 31) / 32;
   // row panels: [x_hi | x_lo] of a panel, then the partial sums of a split launch, fit the scratch
   const uint64_t row_bytes = static_cast<uint64_t>(w.k) * 2 * sizeof(__nv_bfloat16);
-  if (row_bytes * 32 > env.workspace_bytes) return cudaErrorMemoryAllocation;
-  uint32_t panel = static_cast<uint32_t>(std::min<uint64_t>(m, env.workspace_bytes / 2 / row_bytes));
-  panel = std::max(32u, panel / kXM * kXM ? panel / kXM * kXM : panel);
+  const uint64_t per_row = row_bytes + (chain_splits > 1 ? static_cast<uint64_t>(chain_splits) * w.n * sizeof(float) : 0);
+  if (per_row * 32 > env.workspace_bytes) return cudaErrorMemoryAllocation;
+  uint32_t panel = static_cast<uint32_t>(std::min<uint64_t>(m, env.workspace_bytes / per_row));
+  if (panel >= static_cast<uint32_t>(kXM)) panel = panel / kXM * kXM;
   for (uint32_t r0 = 0; r0 < m; r0 += panel) {
     const uint32_t pm = std::min(panel, m - r0);
     __nv_bfloat16* hi = static_cast<__nv_bfloat16*>(env.workspace);
@@ -372,7 +379,7 @@ cudaError_t launch_x32(const LaunchEnv& env, const LinearTarget& target, const X
     p.k = w.k;
     p.status = status_word;
     const uint32_t tiles = ((w.n + kXN - 1) / kXN) * ((pm + kXM - 1) / kXM);
-    uint32_t splits = 1;
+    uint32_t splits = chain_splits;
     while (splits < 8 && tiles * splits * 2 <= static_cast<uint32_t>(env.sm_count) && ksteps_total / (splits * 2) >= 8 &&
            static_cast<uint64_t>(splits * 2) * pm * w.n * sizeof(float) <= partial_room)
       splits *= 2;
@@ -414,13 +421,17 @@ cudaError_t launch_x32(const LaunchEnv& env, const LinearTarget& target, const X
 
 }  // namespace
 
-bool qgemm_i4_x32_supports(const Weight& w, int x_dtype, uint32_t m) {
-  return w.layout == kLayoutTiledI4 && (x_dtype == KQ_F32 || x_dtype == KQ_F16) && m > 16 && w.n != 0;
+bool qgemm_i4_x32_supports(const Weight& w, int x_dtype, uint32_t m, uint64_t workspace_bytes) {
+  if (w.layout != kLayoutTiledI4 || (x_dtype != KQ_F32 && x_dtype != KQ_F16) || m <= 16 || w.n == 0) return false;
+  // 32 rows of the split activations and of the partial sums must fit the scratch (launch_x32)
+  const uint64_t chain_splits = (w.k / kXK + 31) / 32;
+  const uint64_t per_row = static_cast<uint64_t>(w.k) * 4 + (chain_splits > 1 ? chain_splits * w.n * sizeof(float) : 0);
+  return per_row * 32 <= workspace_bytes;
 }
 
 cudaError_t launch_qgemm_i4_x32(const LaunchEnv& env, const LinearTarget& target, const void* x, int x_dtype, uint32_t m,
                                 int* status_word, int* launches) {
-  if (!qgemm_i4_x32_supports(*target.w, x_dtype, m)) return cudaErrorInvalidValue;
+  if (!qgemm_i4_x32_supports(*target.w, x_dtype, m, env.workspace ? env.workspace_bytes : 0)) return cudaErrorInvalidValue;
   if (x_dtype == KQ_F32) return launch_x32<float>(env, target, static_cast<const float*>(x), m, status_word, launches);
   return launch_x32<__half>(env, target, static_cast<const __half*>(x), m, status_word, launches);
 }
