@@ -64,3 +64,13 @@ def test_without_a_gpu_the_library_fails_loudly():
     rc = kb.lib.kq_init(0, 0, ctypes.byref(ctx))
     assert rc != 0 and ctx.value is None
     assert kb.lib.kq_last_error(None)
+
+
+def test_the_deno_binding_table_lists_every_export():
+    """INTEGRATION.md shows the Deno.dlopen symbol table a karume maintainer would paste: it has
+    to name every entry point of the header."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    table = set(re.findall(r"^\s*(kq_\w+):\s*\{\s*parameters", text, flags=re.M))
+    declared = set(declared_symbols())
+    assert declared <= table, f"missing from the dlopen table: {sorted(declared - table)}"
+    assert table <= declared, f"in the table but not in the header: {sorted(table - declared)}"
