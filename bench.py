@@ -286,6 +286,8 @@ def kernel_sweep(gpu, peak_gbs, peak_tf):
 
     out["gemm_i4_bf16_m2048_4096x14336 (config 3)"] = gemm(2048, 4096, 14336)
     out["gemm_i4_bf16_m2048_14336x4096 (config 3)"] = gemm(2048, 14336, 4096)
+    out["gemm_i4_bf16_m512_4096x14336 (config 3)"] = gemm(512, 4096, 14336)
+    out["gemm_i4_bf16_m512_14336x4096 (config 3)"] = gemm(512, 14336, 4096)
     # the same shapes with f32 activations: operands carried as two bf16 numbers each (three MMAs per product)
     out["gemm_i4_f32_m2048_4096x14336 (config 3 shape, f32 rows)"] = gemm(2048, 4096, 14336, torch.float32)
     out["gemm_i4_f32_m2048_14336x4096 (config 3 shape, f32 rows)"] = gemm(2048, 14336, 4096, torch.float32)
