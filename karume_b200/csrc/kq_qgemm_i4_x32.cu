@@ -345,8 +345,9 @@ cudaError_t launch_x32(const LaunchEnv& env, const LinearTarget& target, const X
   const uint32_t ksteps_total = w.k / kXK;
   const size_t smem = kXStages * kXStage + 1024 + 256;
   if (env.workspace == nullptr) return cudaErrorMemoryAllocation;
-  // The tensor core's f32 accumulation truncates: over a chain of c accumulating MMAs the sum
-  // drifts by about c * 2^-24 of its magnitude (measured: 3.5e-4 of the output's rms over
+  // The tensor core's f32 accumulation loses precision with the length of the chain (as adds that
+  // truncate would): over a chain of c accumulating MMAs the sum drifts by about c * 2^-24 of its
+  // magnitude (measured: 3.5e-4 of the output's rms over
   // k = 14336 in one chain, 2,688 MMAs).  A chain therefore covers at most 32 k-steps (2048 k, 384
   // MMAs); longer K is split over blockIdx.z and the slices are added in IEEE f32 by
   // x32_reduce_kernel, whatever the number of tiles.
