@@ -266,9 +266,12 @@ def kernel_sweep(gpu, peak_gbs, peak_tf):
     out["w4a8_m1_4096x128256 (integer dot, config 4 lm head)"] = gemv("i4", 4096, 128256, 1, torch.float32, a8=True)
     out["w4a8_m8_4096x11008 (integer dot, config 2 shape)"] = gemv("i4", 4096, 11008, 8, torch.float32, a8=True)
 
-    def gemm(m, k, n, dtype=torch.bfloat16):
-        data, scale = synth_weight(1, f"sweep.{n}x{k}", n, k)
-        w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    def gemm(m, k, n, dtype=torch.bfloat16, storage="i4"):
+        if storage == "i4":
+            data, scale = synth_weight(1, f"sweep.{n}x{k}", n, k)
+        else:
+            data, scale = synth_i8(n, k, 1)
+        w = gpu.upload_weight(storage, data, scale, (n, k), 32 if storage == "i4" else 0)
         x = torch.randn(m, k, device="cuda").to(dtype)
         bias = torch.zeros(n, device="cuda")
         y = torch.empty(m, n, device="cuda")
@@ -291,6 +294,9 @@ def kernel_sweep(gpu, peak_gbs, peak_tf):
     # the same shapes with f32 activations: operands carried as two bf16 numbers each (three MMAs per product)
     out["gemm_i4_f32_m2048_4096x14336 (config 3 shape, f32 rows)"] = gemm(2048, 4096, 14336, torch.float32)
     out["gemm_i4_f32_m2048_14336x4096 (config 3 shape, f32 rows)"] = gemm(2048, 14336, 4096, torch.float32)
+    # int8 weights through the same tcgen05 kernel (bf16 rows)
+    out["gemm_i8_bf16_m2048_4096x14336 (config 3 shape, int8 weights)"] = gemm(2048, 4096, 14336, storage="i8")
+    out["gemm_i8_bf16_m2048_14336x4096 (config 3 shape, int8 weights)"] = gemm(2048, 14336, 4096, storage="i8")
     return out
 
 

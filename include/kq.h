@@ -199,8 +199,10 @@ KQ_API int kq_model_tensor_info(kq_model model, const char* key, char* dtype8, u
  * More than 16 rows on a tiled int4 weight run on the tcgen05 tensor cores: bf16 activations
  * with operands rounded to bf16 once (results within rtol 1e-3, atol 1e-4 * rms of the oracle
  * on bf16-rounded operands), f32 / binary16 activations with both operands carried as two bf16
- * numbers (the decode contract, atol 4e-5 * max(1, rms) for f32 activations).  Everything up
- * to 16 rows keeps atol 1e-5 * max(1, rms), rtol 1e-3 against the f64-accumulate reference. */
+ * numbers (the decode contract, atol 4e-5 * max(1, rms) for f32 activations).  A tiled int8
+ * weight with k % 64 == 0 takes the same bf16 kernel and contract; its other cases, and
+ * everything up to 16 rows, keep atol 1e-5 * max(1, rms), rtol 1e-3 against the f64-accumulate
+ * reference. */
 KQ_API int kq_linear(kq_ctx* ctx, kq_weight w, uint64_t x_dptr, int x_dtype, uint64_t bias_dptr,
                      uint64_t out_dptr, uint32_t m);
 

@@ -342,6 +342,14 @@ int run_linear(kq_ctx* ctx, uint32_t count, const kq_weight* handles, uint64_t x
       continue;
     }
     if (w.n == 0) continue;
+    if (kq::qgemm_i8_supports(w, x_dtype, m)) {
+      // Prefill over an int8 weight: the tcgen05 GEMM with the int8 producer path.
+      int extra = 0;
+      cudaError_t e = kq::launch_qgemm_i4(env, targets[i], reinterpret_cast<const void*>(x), m, ctx->gemm_status_dev, &extra);
+      if (e != cudaSuccess) return cuda_fail(ctx, e, "qgemm_i8 launch");
+      ctx->launches += 1 + extra;
+      continue;
+    }
     if (w.layout == kq::kLayoutTiledI8) {
       // Tiled int8: row panels of at most 16 activation rows per launch.
       for (uint32_t m0 = 0; m0 < m; m0 += 16) {

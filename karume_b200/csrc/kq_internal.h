@@ -110,6 +110,8 @@ cudaError_t launch_qgemv_i4_tc(const LaunchEnv& env, int count, const LinearTarg
 // ---- tcgen05 prefill GEMM (kq_qgemm_i4.cu): tiled int4 weights, bf16 activations, m > 16
 namespace kq {
 bool qgemm_i4_supports(const Weight& w, int x_dtype, uint32_t m);
+// The same GEMM over a tiled int8 weight (launch_qgemm_i4 takes both storages).
+bool qgemm_i8_supports(const Weight& w, int x_dtype, uint32_t m);
 cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, const void* x, uint32_t m,
                             int* status_word, int* extra_launches);
 // The same for f32 and binary16 activations (kq_qgemm_i4_x32.cu): both operands as two bf16 numbers.

@@ -55,7 +55,8 @@ constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
 constexpr uint32_t kTmemCols = 512;
 
 struct GemmParams {
-  const uint8_t* w;  // tiled int4 weight
+  const uint8_t* w;  // tiled int4 weight (scales inside the chunks) or tiled int8 weight
+  const void* scale;  // int8 only: the per-output-channel scales, [n]
   const __nv_bfloat16* x;
   const float* bias;
   float* out;
@@ -67,9 +68,27 @@ struct GemmParams {
   float* partial;
 };
 
-template <bool kScaleF16>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-qgemm_i4_kernel(const GemmParams p) {
+// Four bytes q + 128 of one weight row -> four bf16 values RNE_bf16(fround(q * s)).  A byte
+// placed under the exponent of 2^23 reads as the float 2^23 + byte exactly; subtracting
+// 2^23 + 128 leaves q exactly, so the multiply's rounding is the reference's only one
+// (kq::dequant_i8's rule).
+__device__ __forceinline__ uint2 dequant4_i8_bf16(uint32_t word, float s) {
+  const float v0 = (__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650u)) - 8388736.0f) * s;
+  const float v1 = (__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7651u)) - 8388736.0f) * s;
+  const float v2 = (__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7652u)) - 8388736.0f) * s;
+  const float v3 = (__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7653u)) - 8388736.0f) * s;
+  uint2 out;
+  __nv_bfloat162 q;
+  q = __floats2bfloat162_rn(v0, v1); out.x = *reinterpret_cast<uint32_t*>(&q);
+  q = __floats2bfloat162_rn(v2, v3); out.y = *reinterpret_cast<uint32_t*>(&q);
+  return out;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint2 v) {
+  asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
+}
+
+template <bool kInt8, bool kScaleF16>
+__device__ __forceinline__ void qgemm_body(const GemmParams& p) {
   constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
   constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;
   extern __shared__ uint8_t smem_raw[];
@@ -127,7 +146,32 @@ qgemm_i4_kernel(const GemmParams p) {
       chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks_begin) * kCB + lane * 16;
     }
     const uint32_t scale_off = kChunkWeightBytes - lane * 16 + g * (kScaleF16 ? 8u : 16u);
+    // int8: a 16-row block's k-step is two adjacent 512-byte chunks (32 k each), one 16-byte
+    // read per lane and chunk; the two rows' scales do not change along k.
+    uint4 w8_next[kChunksPerWarp][2];
+    float s8[kChunksPerWarp][2];
+    if constexpr (kInt8) {
+#pragma unroll
+      for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+        const uint32_t row0 = n0 + (warp * kChunksPerWarp + cc) * 16u;
+        chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * (p.k / kChunkK8) + ks_begin * 2u) * 512u + lane * 16;
+        s8[cc][0] = chunk_live[cc] ? load_scale<kScaleF16>(p.scale, row0 + g) : 0.0f;
+        s8[cc][1] = chunk_live[cc] ? load_scale<kScaleF16>(p.scale, row0 + g + 8u) : 0.0f;
+      }
+    }
     auto fetch_weights = [&](uint32_t ks) {
+      if constexpr (kInt8) {
+#pragma unroll
+        for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+          w8_next[cc][0] = w8_next[cc][1] = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // q = 0
+          if (chunk_live[cc] && ks < ksteps) {
+            w8_next[cc][0] = *reinterpret_cast<const uint4*>(chunk_ptr[cc]);
+            w8_next[cc][1] = *reinterpret_cast<const uint4*>(chunk_ptr[cc] + 512);
+            chunk_ptr[cc] += 1024;
+          }
+        }
+        return;
+      }
 #pragma unroll
       for (int cc = 0; cc < kChunksPerWarp; ++cc) {
         wq_next[cc] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // u = 8 -> value 0
@@ -168,6 +212,35 @@ qgemm_i4_kernel(const GemmParams p) {
         a_src[i] += kBK;
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
+      if constexpr (kInt8) {
+        uint4 w8[kChunksPerWarp][2];
+#pragma unroll
+        for (int cc = 0; cc < kChunksPerWarp; ++cc) { w8[cc][0] = w8_next[cc][0]; w8[cc][1] = w8_next[cc][1]; }
+        fetch_weights(ks + 1);
+#pragma unroll
+        for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+          // chunk j, words x | y | z | w = row g k 4t.. | row g+8 same k | row g k 16+4t.. | row g+8:
+          // four weights = 8 bytes = half (t & 1) of 16-byte piece 4j + 2h + (t >> 1) of the tile
+          // row.  The 16 lanes of a shared-memory phase (four values of g) must hit 8 different
+          // swizzled pieces: the order in which a lane walks its four (j, h) pairs is XORed with
+          // a value that differs where the rows' swizzle term (g >> 1) does not.
+          const uint32_t r_a = (warp * kChunksPerWarp + cc) * 16u + g, r_b = r_a + 8u;
+          const bool odd = (g & 1u) != 0;
+          const uint32_t sub = (t >> 1), byte = (t & 1u) * 8u;
+          uint2 da[4], db[4];  // index 2j + h
+          da[0] = dequant4_i8_bf16(w8[cc][0].x, s8[cc][0]); db[0] = dequant4_i8_bf16(w8[cc][0].y, s8[cc][1]);
+          da[1] = dequant4_i8_bf16(w8[cc][0].z, s8[cc][0]); db[1] = dequant4_i8_bf16(w8[cc][0].w, s8[cc][1]);
+          da[2] = dequant4_i8_bf16(w8[cc][1].x, s8[cc][0]); db[2] = dequant4_i8_bf16(w8[cc][1].y, s8[cc][1]);
+          da[3] = dequant4_i8_bf16(w8[cc][1].z, s8[cc][0]); db[3] = dequant4_i8_bf16(w8[cc][1].w, s8[cc][1]);
+#pragma unroll
+          for (uint32_t i = 0; i < 4; ++i) {
+            const uint32_t o = odd ? (i ^ 2u) : i;  // the (j, h) pair of this store
+            const uint2 va = odd ? da[i ^ 2u] : da[i], vb = odd ? db[i ^ 2u] : db[i];
+            sts64(b_tile + swz(r_a, o * 2u + sub) + byte, va);
+            sts64(b_tile + swz(r_b, o * 2u + sub) + byte, vb);
+          }
+        }
+      } else {
       // weights: this k-step's chunks are already in registers; fetch the next k-step's
       uint4 wq[kChunksPerWarp];
       float sc[kChunksPerWarp][4];
@@ -199,6 +272,7 @@ qgemm_i4_kernel(const GemmParams p) {
         sts128(b_tile + swz(r_a, odd ? t : 4u + t), odd ? a0 : a1);
         sts128(b_tile + swz(r_b, odd ? 4u + t : t), odd ? b1 : b0);
         sts128(b_tile + swz(r_b, odd ? t : 4u + t), odd ? b0 : b1);
+      }
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
@@ -285,6 +359,18 @@ qgemm_i4_kernel(const GemmParams p) {
   }
 }
 
+template <bool kScaleF16>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+qgemm_i4_kernel(const GemmParams p) { qgemm_body<false, kScaleF16>(p); }
+
+// The same kernel over a tiled int8 weight (per-output-channel scales): only the producers'
+// weight path differs.  Replaces the reference's large-M linear variants with in-kernel int8
+// dequant (the ":wi8" pipeline keys — packages/runtime/src/kernels/weight-storage.ts:82-83,
+// geometry from packages/runtime/src/kernels/gemm-geometry.ts:243-267).
+template <bool kScaleF16>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+qgemm_i8_kernel(const GemmParams p) { qgemm_body<true, kScaleF16>(p); }
+
 // out = bias + sum over the K slices, slices in ascending order (deterministic).
 __global__ void __launch_bounds__(256)
 qgemm_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ bias, float* __restrict__ out,
@@ -311,12 +397,32 @@ bool qgemm_i4_supports(const Weight& w, int x_dtype, uint32_t m) {
   return w.layout == kLayoutTiledI4 && x_dtype == KQ_BF16 && m > 16;
 }
 
+bool qgemm_i8_supports(const Weight& w, int x_dtype, uint32_t m) {
+  return w.layout == kLayoutTiledI8 && x_dtype == KQ_BF16 && m > 16 && w.k % kBK == 0;
+}
+
+namespace {
+template <typename Kernel>
+cudaError_t launch_gemm_kernel(Kernel kernel, bool* configured, const dim3& grid, size_t smem, cudaStream_t stream,
+                               const GemmParams& p) {
+  if (!*configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    *configured = true;
+  }
+  kernel<<<grid, kGemmThreads, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, const void* x, uint32_t m,
                             int* status_word, int* extra_launches) {
   const Weight& w = *target.w;
-  if (w.layout != kLayoutTiledI4) return cudaErrorInvalidValue;
+  const bool int8 = w.layout == kLayoutTiledI8;
+  if (w.layout != kLayoutTiledI4 && !(int8 && w.k % kBK == 0)) return cudaErrorInvalidValue;
   GemmParams p = {};
   p.w = static_cast<const uint8_t*>(w.data);
+  p.scale = w.scale;
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.bias = target.bias;
   p.out = target.out;
@@ -337,25 +443,16 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
   p.ksteps_per_split = (ksteps_total + splits - 1) / splits;
   p.partial = static_cast<float*>(env.workspace);
   const dim3 grid((w.n + kBN - 1) / kBN, (m + kBM - 1) / kBM, splits);
+  static bool configured[4] = {false, false, false, false};
   cudaError_t e;
-  if (w.scale_dtype == KQ_F16) {
-    static bool configured = false;
-    if (!configured) {
-      e = cudaFuncSetAttribute(qgemm_i4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      if (e != cudaSuccess) return e;
-      configured = true;
-    }
-    qgemm_i4_kernel<true><<<grid, kGemmThreads, smem, env.stream>>>(p);
+  const bool f16 = w.scale_dtype == KQ_F16;
+  if (int8) {
+    e = f16 ? launch_gemm_kernel(qgemm_i8_kernel<true>, &configured[2], grid, smem, env.stream, p)
+            : launch_gemm_kernel(qgemm_i8_kernel<false>, &configured[3], grid, smem, env.stream, p);
   } else {
-    static bool configured = false;
-    if (!configured) {
-      e = cudaFuncSetAttribute(qgemm_i4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      if (e != cudaSuccess) return e;
-      configured = true;
-    }
-    qgemm_i4_kernel<false><<<grid, kGemmThreads, smem, env.stream>>>(p);
+    e = f16 ? launch_gemm_kernel(qgemm_i4_kernel<true>, &configured[0], grid, smem, env.stream, p)
+            : launch_gemm_kernel(qgemm_i4_kernel<false>, &configured[1], grid, smem, env.stream, p);
   }
-  e = cudaGetLastError();
   if (e != cudaSuccess || splits == 1) return e;
   const size_t quads = static_cast<size_t>(m) * w.n / 4;
   const int rgrid = static_cast<int>(std::min<size_t>((quads + 255) / 256, static_cast<size_t>(env.sm_count) * 8));

@@ -194,3 +194,91 @@ def test_split_operand_gemm_on_prefill_shapes_sampled(gpu, m, k, n):
     rep = oracle.allclose(got[np.ix_(rows, cols)], ref, atol=4e-5 * max(1.0, rms), rtol=1e-3)
     assert rep["pass"], rep
     w.free()
+
+
+# ---- int8 weights (per-output-channel scales), bf16 activations, m > 16 ----------------------
+
+def _i8_weights_bf16(q, scale, rows=None):
+    """RNE_bf16 of the reference's dequantised int8 weight (format/i8.ts:107), all rows or a subset."""
+    q = np.asarray(q).view(np.int8)
+    s = np.asarray(scale, np.float32).reshape(-1)
+    if rows is not None:
+        q, s = q[rows], s[rows]
+    return oracle.round_to_bf16(oracle.decode_i8(q, q.shape, s.reshape(-1, 1), (len(s), 1)))
+
+
+@pytest.mark.parametrize("scale_dtype", ["f16", "f32"])
+def test_int8_dequantised_tile_is_bit_exact_through_one_hot_activations(gpu, scale_dtype):
+    import torch
+    n, k = 272, 256  # two n tiles (the second ragged), four k steps = eight int8 chunks per row block
+    q, s = cases.synth_i8(n, k, seed=3)
+    s = s.astype(np.float32) * np.float32(1.37) if scale_dtype == "f32" else s  # f32 scales with bits below binary16's
+    w = gpu.upload_weight("i8", q, s, (n, k))
+    x = torch.eye(k, dtype=torch.bfloat16, device="cuda")
+    out = torch.full((k, n), float("nan"), device="cuda")
+    gpu.linear(x, w, torch.zeros(n, device="cuda"), out=out)
+    gpu.sync()
+    want = _i8_weights_bf16(q, s)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want.T))
+    w.free()
+
+
+@pytest.mark.parametrize("m,n,k", [(17, 272, 512), (65, 512, 256), (256, 256, 64), (300, 784, 1024), (513, 256, 2048)])
+def test_int8_gemm_matches_oracle_on_prerounded_inputs(gpu, m, n, k):
+    import torch
+    q, s = cases.synth_i8(n, k, seed=m + n)
+    rng = np.random.default_rng(m)
+    x = oracle.round_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    bias = rng.standard_normal(n).astype(np.float32)
+    w = gpu.upload_weight("i8", q, s, (n, k))
+    out = torch.full((m, n), float("nan"), device="cuda")
+    gpu.linear(dev(x).to(torch.bfloat16), w, dev(bias), out=out)
+    gpu.sync()
+    ref = oracle.linear_f64(x, _i8_weights_bf16(q, s), bias)
+    rep = oracle.allclose(out.cpu().numpy(), ref, atol=1e-5, rtol=1e-3)
+    assert rep["pass"], rep
+    w.free()
+
+
+@pytest.mark.parametrize("m,k,n", [(2048, 4096, 14336), (512, 14336, 4096)])
+def test_int8_prefill_shapes_sampled_and_replayed(gpu, m, k, n):
+    """Full prefill sizes, the second one split along K (few output tiles): sampled rows and
+    columns against the oracle, and the same call twice gives the same bits."""
+    import torch
+    q, s = cases.synth_i8(n, k, seed=k)
+    rng = np.random.default_rng(9)
+    x = oracle.round_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    bias = rng.standard_normal(n).astype(np.float32)
+    w = gpu.upload_weight("i8", q, s, (n, k))
+    xd, bd = dev(x).to(torch.bfloat16), dev(bias)
+    out = gpu.linear(xd, w, bd)
+    again = gpu.linear(xd, w, bd)
+    gpu.sync()
+    assert torch.equal(out, again)
+    got = out.cpu().numpy()
+    assert np.all(np.isfinite(got))
+    rows = rng.choice(m, 48, replace=False)
+    cols = np.sort(rng.choice(n, 384, replace=False))
+    ref = oracle.linear_f64(x[rows], _i8_weights_bf16(q, s, cols), bias[cols])
+    atol = max(1e-5, 1e-4 * float(np.sqrt(np.mean(ref.astype(np.float64) ** 2))))
+    rep = oracle.allclose(got[np.ix_(rows, cols)], ref, atol=atol, rtol=1e-3)
+    assert rep["pass"], (atol, rep)
+    w.free()
+
+
+def test_int8_weight_with_k_not_a_multiple_of_64_keeps_the_gemv_panels(gpu):
+    """k = 96 has no 64-wide k-step: the call is served by row panels of the int8 GEMV, whose
+    contract is the f32 one (no bf16 rounding of the weights)."""
+    import torch
+    m, n, k = 40, 64, 96
+    q, s = cases.synth_i8(n, k, seed=2)
+    rng = np.random.default_rng(2)
+    x = oracle.round_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    bias = rng.standard_normal(n).astype(np.float32)
+    w = gpu.upload_weight("i8", q, s, (n, k))
+    out = gpu.linear(dev(x).to(torch.bfloat16), w, dev(bias))
+    gpu.sync()
+    ref = oracle.linear_i8(x, np.asarray(q).view(np.int8), s.astype(np.float32), bias, n, k)
+    rep = oracle.allclose(out.cpu().numpy(), ref, atol=1e-5, rtol=1e-3)
+    assert rep["pass"], rep
+    w.free()
