@@ -46,8 +46,6 @@ constexpr int kBM = 256, kBN = 256, kBK = 64, kStagesG = 3;
 #define KQ_GEMM_PRODUCER_WARPS 16
 #endif
 constexpr int kProducerWarps = KQ_GEMM_PRODUCER_WARPS;  // 8 or 16
-constexpr int kChunksPerWarp = 16 / kProducerWarps;      // 16-row weight chunks per warp and k-step
-constexpr int kAPiecesPerThread = 2048 / (kProducerWarps * 32);
 constexpr int kGemmThreads = kProducerWarps * 32 + 32;
 constexpr uint32_t kATileBytes = kBM * kBK * 2;  // 32 KB
 constexpr uint32_t kBTileBytes = kBN * kBK * 2;  // 32 KB
@@ -87,23 +85,37 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint2 v) {
   asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
 }
 
-template <bool kInt8, bool kScaleF16>
+// kPair: the two CTAs of a cluster (consecutive blockIdx.x = consecutive 256-row tiles of m, the
+// same 256 output channels) run ONE tcgen05.mma.cta_group::2 stream: each CTA keeps its own
+// activation tile and accumulators, and dequantises only half of the weight tile (128
+// channels) — the tensor core reads the other half from the peer's shared memory.  The MMAs are
+// issued by the CTA of cluster rank 0; the peer's producers arrive on that CTA's "full"
+// barriers, and each commit is sent to both CTAs' "empty" barriers.
+template <bool kInt8, bool kScaleF16, bool kPair, int kGroups>
 __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
+  static_assert(!kPair || (kProducerWarps == 16 && kGroups == 2), "the pair form: two groups of 8 warps");
+  // The producer warps work in kGroups groups, group j filling the stages of k-steps j, j + kGroups, ...:
+  // while one group sits in its barrier wait, fences and arrival, the other computes.
+  constexpr int kGW = kProducerWarps / kGroups;           // warps per group
+  constexpr int kChunksPerWarp = (kPair ? 8 : 16) / kGW;  // 16-row weight blocks per warp and k-step
+  constexpr int kAPiecesPerThread = 2048 / (kGW * 32);
   constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
   constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;
+  constexpr int kStagesG = kPair ? 4 : kq::kStagesG;  // a pair's stage is 48 KB instead of 64
+  constexpr uint32_t kStageBytes = kATileBytes + (kPair ? kBTileBytes / 2 : kBTileBytes);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t raw_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
   const uint32_t tiles = (raw_base + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-  const uint32_t bars = tiles + kStagesG * kStageBytes;  // full[3], empty[3], accum
-  const uint32_t tmem_slot = bars + 64;
-  const uint32_t abort_addr = bars + 72;
+  const uint32_t bars = tiles + kStagesG * kStageBytes;  // full[stages], empty[stages], accum
+  const uint32_t tmem_slot = bars + 96;
   uint8_t* generic_base = smem_raw + (tiles - raw_base);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + kStagesG * kStageBytes + 72);
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + kStagesG * kStageBytes + 64);
-  (void)abort_addr;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + kStagesG * kStageBytes + 104);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + kStagesG * kStageBytes + 96);
+  const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
 
-  const uint32_t n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+  // a pair lies along x (the hardware pairs CTAs of consecutive cluster rank): there x walks m
+  const uint32_t n0 = (kPair ? blockIdx.y : blockIdx.x) * kBN, m0 = (kPair ? blockIdx.x : blockIdx.y) * kBM;
   const uint32_t ks_begin = blockIdx.z * p.ksteps_per_split;
   const uint32_t ks_end = min(ks_begin + p.ksteps_per_split, p.k / kBK);
   const uint32_t ksteps = ks_end - ks_begin;  // k-steps of this slice; stage and phase count from 0
@@ -112,7 +124,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
   if (warp == kProducerWarps) {
     if (lane == 0) {
       for (int s = 0; s < kStagesG; ++s) {
-        mbar_init(bars + s * 8, kProducerWarps * 32);  // full: every producer thread arrives
+        mbar_init(bars + s * 8, (kPair ? 2 : 1) * kGW * 32);  // full: every thread of the filling group (of both CTAs) arrives
         mbar_init(bars + (kStagesG + s) * 8, 1);       // empty: one tcgen05.commit
       }
       mbar_init(bars + 2 * kStagesG * 8, 1);           // accumulators complete
@@ -120,17 +132,24 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (kPair) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all();  // the peer's barriers are initialised before anyone arrives on them
+  else __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   if (warp < kProducerWarps) {
     // ---------------- producers ----------------
-    const uint32_t tid = threadIdx.x;  // producer thread index
+    const uint32_t grp = warp / kGW, wg = warp % kGW;  // group, warp within it
+    const uint32_t tid = threadIdx.x % (kGW * 32u);    // thread within the group
     const uint32_t g = lane >> 2, t = lane & 3u;
     // The lane's two weight chunks (and their scales) of a k-step, fetched one k-step ahead.
     uint4 wq_next[kChunksPerWarp];
@@ -141,9 +160,10 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
     bool chunk_live[kChunksPerWarp];
 #pragma unroll
     for (int cc = 0; cc < kChunksPerWarp; ++cc) {
-      const uint32_t row0 = n0 + (warp * kChunksPerWarp + cc) * 16u;  // first output channel of the row block
+      // first output channel of the row block; in a pair two warps share a block of this CTA's 128 channels
+      const uint32_t row0 = n0 + (kPair ? cta_rank * 128u : 0u) + (wg * kChunksPerWarp + cc) * 16u;
       chunk_live[cc] = row0 < p.n;
-      chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks_begin) * kCB + lane * 16;
+      chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks_begin + grp) * kCB + lane * 16;
     }
     const uint32_t scale_off = kChunkWeightBytes - lane * 16 + g * (kScaleF16 ? 8u : 16u);
     // int8: a 16-row block's k-step is two adjacent 512-byte chunks (32 k each), one 16-byte
@@ -153,8 +173,8 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
     if constexpr (kInt8) {
 #pragma unroll
       for (int cc = 0; cc < kChunksPerWarp; ++cc) {
-        const uint32_t row0 = n0 + (warp * kChunksPerWarp + cc) * 16u;
-        chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * (p.k / kChunkK8) + ks_begin * 2u) * 512u + lane * 16;
+        const uint32_t row0 = n0 + (kPair ? cta_rank * 128u : 0u) + (wg * kChunksPerWarp + cc) * 16u;
+        chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * (p.k / kChunkK8) + (ks_begin + grp) * 2u) * 512u + lane * 16;
         s8[cc][0] = chunk_live[cc] ? load_scale<kScaleF16>(p.scale, row0 + g) : 0.0f;
         s8[cc][1] = chunk_live[cc] ? load_scale<kScaleF16>(p.scale, row0 + g + 8u) : 0.0f;
       }
@@ -167,7 +187,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
           if (chunk_live[cc] && ks < ksteps) {
             w8_next[cc][0] = *reinterpret_cast<const uint4*>(chunk_ptr[cc]);
             w8_next[cc][1] = *reinterpret_cast<const uint4*>(chunk_ptr[cc] + 512);
-            chunk_ptr[cc] += 1024;
+            chunk_ptr[cc] += 1024 * kGroups;
           }
         }
         return;
@@ -181,7 +201,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
           wq_next[cc] = *reinterpret_cast<const uint4*>(chunk_ptr[cc]);
           if constexpr (kScaleF16) sc_next[cc] = *reinterpret_cast<const uint2*>(chunk_ptr[cc] + scale_off);
           else sc_next[cc] = *reinterpret_cast<const uint4*>(chunk_ptr[cc] + scale_off);
-          chunk_ptr[cc] += kCB;
+          chunk_ptr[cc] += kCB * kGroups;
         }
       }
     };
@@ -191,32 +211,43 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
     uint32_t a_dst[kAPiecesPerThread], a_bytes[kAPiecesPerThread];
 #pragma unroll
     for (int i = 0; i < kAPiecesPerThread; ++i) {
-      const uint32_t piece = tid + i * (kProducerWarps * 32u);
+      const uint32_t piece = tid + i * (kGW * 32u);
       const uint32_t r = piece >> 3, c = piece & 7u;
       const bool in_range = m0 + r < p.m;
-      a_src[i] = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + ks_begin * kBK + c * 8;
+      a_src[i] = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + (ks_begin + grp) * kBK + c * 8;
       a_dst[i] = swz(r, c);
       a_bytes[i] = in_range ? 16u : 0u;
     }
-    fetch_weights(0);
-    for (uint32_t ks = 0; ks < ksteps; ++ks) {
-      const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
-      wait_bounded(bars + (kStagesG + s) * 8, phase ^ 1u, abort_flag, p.status, 1);
-      const uint32_t a_tile = tiles + s * kStageBytes, b_tile = a_tile + kATileBytes;
-      // activations: 256 rows x 8 pieces of 16 B, copied asynchronously straight into the
-      // swizzled tile (rows past m are zero-filled); the copy flies while we dequantise
+    // activations: 256 rows x 8 pieces of 16 B, copied asynchronously straight into the swizzled
+    // tile of the k-step's stage (rows past m are zero-filled), once that stage is free
+    auto copy_activations = [&](uint32_t ks) {
+      if (ks < ksteps) {
+        const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
+        wait_bounded(bars + (kStagesG + s) * 8, phase ^ 1u, abort_flag, p.status, 1);
+        const uint32_t a_tile = tiles + s * kStageBytes;
 #pragma unroll
-      for (int i = 0; i < kAPiecesPerThread; ++i) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_tile + a_dst[i]), "l"(a_src[i]), "r"(a_bytes[i])
-                     : "memory");
-        a_src[i] += kBK;
+        for (int i = 0; i < kAPiecesPerThread; ++i) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_tile + a_dst[i]), "l"(a_src[i]), "r"(a_bytes[i])
+                       : "memory");
+          a_src[i] += kBK * kGroups;
+        }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // With groups, a group's copy for its NEXT k-step starts as soon as the current stage is
+    // handed over: its latency then overlaps the whole next dequant instead of ending the step.
+    constexpr bool kCopyAhead = kGroups > 1;
+    fetch_weights(grp);
+    if constexpr (kCopyAhead) copy_activations(grp);
+    for (uint32_t ks = grp; ks < ksteps; ks += kGroups) {
+      const uint32_t s = ks % kStagesG;
+      if constexpr (!kCopyAhead) copy_activations(ks);  // the copy flies while we dequantise
+      const uint32_t a_tile = tiles + s * kStageBytes, b_tile = a_tile + kATileBytes;
       if constexpr (kInt8) {
         uint4 w8[kChunksPerWarp][2];
 #pragma unroll
         for (int cc = 0; cc < kChunksPerWarp; ++cc) { w8[cc][0] = w8_next[cc][0]; w8[cc][1] = w8_next[cc][1]; }
-        fetch_weights(ks + 1);
+        fetch_weights(ks + kGroups);
 #pragma unroll
         for (int cc = 0; cc < kChunksPerWarp; ++cc) {
           // chunk j, words x | y | z | w = row g k 4t.. | row g+8 same k | row g k 16+4t.. | row g+8:
@@ -224,7 +255,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
           // row.  The 16 lanes of a shared-memory phase (four values of g) must hit 8 different
           // swizzled pieces: the order in which a lane walks its four (j, h) pairs is XORed with
           // a value that differs where the rows' swizzle term (g >> 1) does not.
-          const uint32_t r_a = (warp * kChunksPerWarp + cc) * 16u + g, r_b = r_a + 8u;
+          const uint32_t r_a = (wg * kChunksPerWarp + cc) * 16u + g, r_b = r_a + 8u;
           const bool odd = (g & 1u) != 0;
           const uint32_t sub = (t >> 1), byte = (t & 1u) * 8u;
           uint2 da[4], db[4];  // index 2j + h
@@ -256,7 +287,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
           sc[cc][2] = __uint_as_float(sc_next[cc].z); sc[cc][3] = __uint_as_float(sc_next[cc].w);
         }
       }
-      fetch_weights(ks + 1);
+      fetch_weights(ks + kGroups);
 #pragma unroll
       for (int cc = 0; cc < kChunksPerWarp; ++cc) {
         // words: row g grp 0 | row g+8 grp 0 | row g grp 1 | row g+8 grp 1; the lane's 8
@@ -264,7 +295,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
         // or 4 + t (group 1) of the 128-byte tile row.  Odd g stores group 1 first: the 8
         // lanes of a shared-memory phase (two values of g, four of t) then hit 8 different
         // 16-byte columns of the swizzled rows.
-        const uint32_t r_a = (warp * kChunksPerWarp + cc) * 16u + g, r_b = r_a + 8u;
+        const uint32_t r_a = (wg * kChunksPerWarp + cc) * 16u + g, r_b = r_a + 8u;
         const uint4 a0 = dequant8_bf16(wq[cc].x, sc[cc][0]), a1 = dequant8_bf16(wq[cc].z, sc[cc][2]);
         const uint4 b0 = dequant8_bf16(wq[cc].y, sc[cc][1]), b1 = dequant8_bf16(wq[cc].w, sc[cc][3]);
         const bool odd = (g & 1u) != 0;
@@ -276,7 +307,9 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
-      mbar_arrive(bars + s * 8);
+      if (kPair && cta_rank != 0) mbar_arrive_cluster(map_to_cta(bars + s * 8, 0));  // the issuing CTA's barrier
+      else mbar_arrive(bars + s * 8);
+      if constexpr (kCopyAhead) copy_activations(ks + kGroups);
     }
     // ---------------- epilogue: accumulators -> out ----------------
     wait_bounded(bars + 2 * kStagesG * 8, 0, abort_flag, p.status, 3);
@@ -325,12 +358,13 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
           dst[static_cast<size_t>(row_first + rr) * p.n] = scratch[rr * 36u + lane] + b;
       }
     }
-  } else {
+  } else if (cta_rank == 0) {
     // ---------------- MMA issuer ----------------
-    constexpr uint32_t kIdesc = umma_idesc(128, kBN);
+    constexpr uint32_t kIdesc = umma_idesc(kPair ? 256 : 128, kBN);
     for (uint32_t ks = 0; ks < ksteps; ++ks) {
       const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
-      const bool ok = wait_bounded(bars + s * 8, phase, abort_flag, p.status, 2);
+      const bool ok = kPair ? wait_bounded_cluster(bars + s * 8, phase, abort_flag, p.status, 2)
+                            : wait_bounded(bars + s * 8, phase, abort_flag, p.status, 2);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (lane == 0) {
         const uint32_t a_tile = tiles + s * kStageBytes, b_tile = a_tile + kATileBytes;
@@ -339,29 +373,55 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
           for (uint32_t kk = 0; kk < kBK / 16; ++kk) {
             const uint64_t db = umma_desc(b_tile + kk * 32u);
             const uint32_t acc = (ks | kk) != 0 ? 1u : 0u;
-            umma_bf16(tmem_base, umma_desc(a_tile + kk * 32u), db, kIdesc, acc);
-            umma_bf16(tmem_base + kBN, umma_desc(a_tile + 128u * 128u + kk * 32u), db, kIdesc, acc);
+            if constexpr (kPair) {
+              umma_bf16_pair(tmem_base, umma_desc(a_tile + kk * 32u), db, kIdesc, acc);
+              umma_bf16_pair(tmem_base + kBN, umma_desc(a_tile + 128u * 128u + kk * 32u), db, kIdesc, acc);
+            } else {
+              umma_bf16(tmem_base, umma_desc(a_tile + kk * 32u), db, kIdesc, acc);
+              umma_bf16(tmem_base + kBN, umma_desc(a_tile + 128u * 128u + kk * 32u), db, kIdesc, acc);
+            }
           }
         }
-        umma_commit(bars + (kStagesG + s) * 8);  // the stage is free once these MMAs have read it
+        // the stage is free once these MMAs have read it (in a pair: in both CTAs)
+        if constexpr (kPair) {
+          umma_commit_pair(bars + (kStagesG + s) * 8);
+          umma_commit_pair(map_to_cta(bars + (kStagesG + s) * 8, 1));
+        } else {
+          umma_commit(bars + (kStagesG + s) * 8);
+        }
       }
       __syncwarp();
     }
-    if (lane == 0) umma_commit(bars + 2 * kStagesG * 8);  // all MMAs done: accumulators are final
+    if (lane == 0) {  // all MMAs done: accumulators are final
+      if constexpr (kPair) {
+        umma_commit_pair(bars + 2 * kStagesG * 8);
+        umma_commit_pair(map_to_cta(bars + 2 * kStagesG * 8, 1));
+      } else {
+        umma_commit(bars + 2 * kStagesG * 8);
+      }
+    }
     __syncwarp();
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all();  // neither CTA leaves, or frees TMEM, while the other still works
+  else __syncthreads();
   if (warp == kProducerWarps) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if constexpr (kPair)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
 template <bool kScaleF16>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-qgemm_i4_kernel(const GemmParams p) { qgemm_body<false, kScaleF16>(p); }
+qgemm_i4_kernel(const GemmParams p) { qgemm_body<false, kScaleF16, false, 1>(p); }
+
+template <bool kScaleF16>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+qgemm_i4_pair_kernel(const GemmParams p) { qgemm_body<false, kScaleF16, true, 2>(p); }
 
 // The same kernel over a tiled int8 weight (per-output-channel scales): only the producers'
 // weight path differs.  Replaces the reference's large-M linear variants with in-kernel int8
@@ -369,7 +429,11 @@ qgemm_i4_kernel(const GemmParams p) { qgemm_body<false, kScaleF16>(p); }
 // geometry from packages/runtime/src/kernels/gemm-geometry.ts:243-267).
 template <bool kScaleF16>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-qgemm_i8_kernel(const GemmParams p) { qgemm_body<true, kScaleF16>(p); }
+qgemm_i8_kernel(const GemmParams p) { qgemm_body<true, kScaleF16, false, 1>(p); }
+
+template <bool kScaleF16>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+qgemm_i8_pair_kernel(const GemmParams p) { qgemm_body<true, kScaleF16, true, 2>(p); }
 
 // out = bias + sum over the K slices, slices in ascending order (deterministic).
 __global__ void __launch_bounds__(256)
@@ -413,6 +477,28 @@ cudaError_t launch_gemm_kernel(Kernel kernel, bool* configured, const dim3& grid
   kernel<<<grid, kGemmThreads, smem, stream>>>(p);
   return cudaGetLastError();
 }
+template <typename Kernel>
+cudaError_t launch_pair_kernel(Kernel kernel, bool* configured, const dim3& grid, size_t smem, cudaStream_t stream,
+                               const GemmParams& p) {
+  if (!*configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    *configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
 }  // namespace
 
 cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, const void* x, uint32_t m,
@@ -430,10 +516,15 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
   p.n = w.n;
   p.k = w.k;
   p.status = status_word;
+  // Three stages of 64 KB, or in the pair form four of 48 KB: the same total.
   const size_t smem = kStagesG * kStageBytes + 1024 + 256;
+  // Two or more row tiles: CTA pairs (each pair = two consecutive row tiles of one column tile).
+  const bool pair = m > static_cast<uint32_t>(kBM);
+  const uint32_t n_tiles = (w.n + kBN - 1) / kBN;
+  const uint32_t m_tiles = pair ? (((m + kBM - 1) / kBM + 1u) & ~1u) : (m + kBM - 1) / kBM;
   // Few output tiles: split K over blockIdx.z until the grid covers the machine, as long as a
   // slice keeps at least 8 k-steps and the partial sums fit the context's scratch.
-  const uint32_t tiles = ((w.n + kBN - 1) / kBN) * ((m + kBM - 1) / kBM);
+  const uint32_t tiles = n_tiles * m_tiles;
   const uint32_t ksteps_total = w.k / kBK;
   uint32_t splits = 1;
   while (splits < 8 && tiles * splits * 2 <= static_cast<uint32_t>(env.sm_count) && ksteps_total / (splits * 2) >= 8 &&
@@ -442,16 +533,26 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
   p.splits = splits;
   p.ksteps_per_split = (ksteps_total + splits - 1) / splits;
   p.partial = static_cast<float*>(env.workspace);
-  const dim3 grid((w.n + kBN - 1) / kBN, (m + kBM - 1) / kBM, splits);
-  static bool configured[4] = {false, false, false, false};
+  static bool configured[8] = {false, false, false, false, false, false, false, false};
   cudaError_t e;
   const bool f16 = w.scale_dtype == KQ_F16;
-  if (int8) {
-    e = f16 ? launch_gemm_kernel(qgemm_i8_kernel<true>, &configured[2], grid, smem, env.stream, p)
-            : launch_gemm_kernel(qgemm_i8_kernel<false>, &configured[3], grid, smem, env.stream, p);
+  if (pair) {
+    // x walks m in whole pairs (a CTA past the last row computes on zero-filled rows and stores nothing), y walks n
+    const dim3 grid(m_tiles, n_tiles, splits);
+    if (int8)
+      e = f16 ? launch_pair_kernel(qgemm_i8_pair_kernel<true>, &configured[6], grid, smem, env.stream, p)
+              : launch_pair_kernel(qgemm_i8_pair_kernel<false>, &configured[7], grid, smem, env.stream, p);
+    else
+      e = f16 ? launch_pair_kernel(qgemm_i4_pair_kernel<true>, &configured[4], grid, smem, env.stream, p)
+              : launch_pair_kernel(qgemm_i4_pair_kernel<false>, &configured[5], grid, smem, env.stream, p);
   } else {
-    e = f16 ? launch_gemm_kernel(qgemm_i4_kernel<true>, &configured[0], grid, smem, env.stream, p)
-            : launch_gemm_kernel(qgemm_i4_kernel<false>, &configured[1], grid, smem, env.stream, p);
+    const dim3 grid(n_tiles, m_tiles, splits);
+    if (int8)
+      e = f16 ? launch_gemm_kernel(qgemm_i8_kernel<true>, &configured[2], grid, smem, env.stream, p)
+              : launch_gemm_kernel(qgemm_i8_kernel<false>, &configured[3], grid, smem, env.stream, p);
+    else
+      e = f16 ? launch_gemm_kernel(qgemm_i4_kernel<true>, &configured[0], grid, smem, env.stream, p)
+              : launch_gemm_kernel(qgemm_i4_kernel<false>, &configured[1], grid, smem, env.stream, p);
   }
   if (e != cudaSuccess || splits == 1) return e;
   const size_t quads = static_cast<size_t>(m) * w.n / 4;

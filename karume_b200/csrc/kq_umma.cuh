@@ -62,6 +62,57 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): one MMA spans the two CTAs of a cluster -------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// wait_bounded for a barrier that threads of the peer CTA arrive on
+__device__ __forceinline__ bool wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                     int code) {
+  for (uint32_t spins = 0; spins < kWaitLimit; ++spins) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((spins & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  *reinterpret_cast<volatile int*>(status) = code;
+  return false;
+}
+// M 256 (128 rows per CTA) x N: A and D are each CTA's own rows, B is read half from each CTA.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `cluster_bar` (a shared::cluster address: this CTA's barrier, or the peer's through
+// map_to_cta) once the pair's MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
 // 8 nibbles of one 32-bit word -> 8 bf16 (16 bytes, k ascending), each
 // RNE_bf16(fround((u - 8) * s)).  (word & (0xF << 4e)) | 0x4B000000 is the float
 // 2^23 + u * 16^e exactly; subtracting 2^23 + 8 * 16^e leaves (u - 8) * 16^e exactly, and
