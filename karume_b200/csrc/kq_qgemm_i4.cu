@@ -64,6 +64,14 @@ struct GemmParams {
   // more than one slice, leaves its partial sums (no bias) in partial[z][m][n].
   uint32_t ksteps_per_split, splits;
   float* partial;
+  // Pair form, stream_pairs != 0: the launch is stream_pairs clusters and the pair tiles x k-steps
+  // are dealt to them as one contiguous run each (pair tile t = column tile t / m_pairs, row
+  // pair t % m_pairs).  A pair that starts inside a tile leaves that piece's sums in its slot
+  // (slots[pair][cta][256][256]) and raises flags[2 * pair + cta]; the pair that holds the tile's
+  // first k-step adds the slots of the pairs after it, in order, before it stores.
+  uint32_t stream_pairs, pair_tiles, m_pairs;
+  float* slots;
+  unsigned int* flags;
 };
 
 // Four bytes q + 128 of one weight row -> four bf16 values RNE_bf16(fround(q * s)).  A byte
@@ -114,12 +122,43 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + kStagesG * kStageBytes + 96);
   const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
 
-  // a pair lies along x (the hardware pairs CTAs of consecutive cluster rank): there x walks m
-  const uint32_t n0 = (kPair ? blockIdx.y : blockIdx.x) * kBN, m0 = (kPair ? blockIdx.x : blockIdx.y) * kBM;
-  const uint32_t ks_begin = blockIdx.z * p.ksteps_per_split;
-  const uint32_t ks_end = min(ks_begin + p.ksteps_per_split, p.k / kBK);
-  const uint32_t ksteps = ks_end - ks_begin;  // k-steps of this slice; stage and phase count from 0
-  const uint32_t chunks_per_row = p.k / kChunkK;
+  const uint32_t chunks_per_row = p.k / kChunkK, ksteps_all = p.k / kBK;
+  // What this CTA computes, as a list of fragments (tile, k range).  Without streaming there is one:
+  // the tile and K slice the block index names.  With streaming the pair's run of units is cut
+  // at the tile boundaries.
+  const bool streaming = kPair && p.stream_pairs != 0;
+  const uint32_t pair_index = blockIdx.x >> 1;
+  const uint64_t units = static_cast<uint64_t>(p.pair_tiles) * ksteps_all;
+  uint32_t unit_begin = 0, unit_end = 0, first_tile = 0, frag_count = 1;
+  if (streaming) {
+    unit_begin = static_cast<uint32_t>(pair_index * units / p.stream_pairs);
+    unit_end = static_cast<uint32_t>((pair_index + 1) * units / p.stream_pairs);
+    first_tile = unit_begin / ksteps_all;
+    frag_count = unit_end > unit_begin ? (unit_end - 1) / ksteps_all - first_tile + 1 : 0;
+  }
+  enum : uint32_t { kFinal = 0, kSlice = 1, kPiece = 2, kOwner = 3 };
+  // the current fragment: tile origin, first k-step, k-steps, what happens to the sums, the unit
+  // after the tile's last, and how many k-steps this CTA ran before (stages and phases count on)
+  uint32_t n0 = 0, m0 = 0, ks_begin = 0, ksteps = 0, kind = kFinal, tile_end_unit = 0, it_base = 0;
+  auto select_fragment = [&](uint32_t f) {
+    if (streaming) {
+      const uint32_t t = first_tile + f, tile_unit = t * ksteps_all;
+      ks_begin = max(unit_begin, tile_unit) - tile_unit;
+      ksteps = min(unit_end, tile_unit + ksteps_all) - tile_unit - ks_begin;
+      tile_end_unit = tile_unit + ksteps_all;
+      n0 = (t / p.m_pairs) * kBN;
+      m0 = ((t % p.m_pairs) * 2u + cta_rank) * kBM;
+      kind = ks_begin != 0 ? kPiece : (ksteps < ksteps_all ? kOwner : kFinal);
+    } else {
+      // a pair lies along x (the hardware pairs CTAs of consecutive cluster rank): there x walks m
+      n0 = (kPair ? blockIdx.y : blockIdx.x) * kBN;
+      m0 = (kPair ? blockIdx.x : blockIdx.y) * kBM;
+      ks_begin = blockIdx.z * p.ksteps_per_split;
+      ksteps = min(ks_begin + p.ksteps_per_split, ksteps_all) - ks_begin;
+      kind = p.splits == 1 ? kFinal : kSlice;
+    }
+  };
+  const uint32_t tmem_free = bars + 72;  // pair form: both CTAs have drained the accumulators of a fragment
 
   if (warp == kProducerWarps) {
     if (lane == 0) {
@@ -128,6 +167,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
         mbar_init(bars + (kStagesG + s) * 8, 1);       // empty: one tcgen05.commit
       }
       mbar_init(bars + 2 * kStagesG * 8, 1);           // accumulators complete
+      mbar_init(tmem_free, kPair ? 2 : 1);
       *abort_flag = 0;
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -151,6 +191,10 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
     const uint32_t grp = warp / kGW, wg = warp % kGW;  // group, warp within it
     const uint32_t tid = threadIdx.x % (kGW * 32u);    // thread within the group
     const uint32_t g = lane >> 2, t = lane & 3u;
+    for (uint32_t f = 0; f < frag_count; ++f) {
+    select_fragment(f);
+    // group j fills the stages of the k-steps whose running count is j modulo the group count
+    const uint32_t ks_first = (grp + kGroups - it_base % kGroups) % kGroups;
     // The lane's two weight chunks (and their scales) of a k-step, fetched one k-step ahead.
     uint4 wq_next[kChunksPerWarp];
     typename std::conditional<kScaleF16, uint2, uint4>::type sc_next[kChunksPerWarp];
@@ -163,7 +207,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
       // first output channel of the row block; in a pair two warps share a block of this CTA's 128 channels
       const uint32_t row0 = n0 + (kPair ? cta_rank * 128u : 0u) + (wg * kChunksPerWarp + cc) * 16u;
       chunk_live[cc] = row0 < p.n;
-      chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks_begin + grp) * kCB + lane * 16;
+      chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * chunks_per_row + ks_begin + ks_first) * kCB + lane * 16;
     }
     const uint32_t scale_off = kChunkWeightBytes - lane * 16 + g * (kScaleF16 ? 8u : 16u);
     // int8: a 16-row block's k-step is two adjacent 512-byte chunks (32 k each), one 16-byte
@@ -174,7 +218,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
 #pragma unroll
       for (int cc = 0; cc < kChunksPerWarp; ++cc) {
         const uint32_t row0 = n0 + (kPair ? cta_rank * 128u : 0u) + (wg * kChunksPerWarp + cc) * 16u;
-        chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * (p.k / kChunkK8) + (ks_begin + grp) * 2u) * 512u + lane * 16;
+        chunk_ptr[cc] = p.w + (static_cast<size_t>(row0 >> 4) * (p.k / kChunkK8) + (ks_begin + ks_first) * 2u) * 512u + lane * 16;
         s8[cc][0] = chunk_live[cc] ? load_scale<kScaleF16>(p.scale, row0 + g) : 0.0f;
         s8[cc][1] = chunk_live[cc] ? load_scale<kScaleF16>(p.scale, row0 + g + 8u) : 0.0f;
       }
@@ -214,7 +258,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
       const uint32_t piece = tid + i * (kGW * 32u);
       const uint32_t r = piece >> 3, c = piece & 7u;
       const bool in_range = m0 + r < p.m;
-      a_src[i] = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + (ks_begin + grp) * kBK + c * 8;
+      a_src[i] = p.x + static_cast<size_t>(in_range ? m0 + r : 0) * p.k + (ks_begin + ks_first) * kBK + c * 8;
       a_dst[i] = swz(r, c);
       a_bytes[i] = in_range ? 16u : 0u;
     }
@@ -222,7 +266,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
     // tile of the k-step's stage (rows past m are zero-filled), once that stage is free
     auto copy_activations = [&](uint32_t ks) {
       if (ks < ksteps) {
-        const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
+        const uint32_t it = it_base + ks, s = it % kStagesG, phase = (it / kStagesG) & 1u;
         wait_bounded(bars + (kStagesG + s) * 8, phase ^ 1u, abort_flag, p.status, 1);
         const uint32_t a_tile = tiles + s * kStageBytes;
 #pragma unroll
@@ -237,10 +281,10 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
     // With groups, a group's copy for its NEXT k-step starts as soon as the current stage is
     // handed over: its latency then overlaps the whole next dequant instead of ending the step.
     constexpr bool kCopyAhead = kGroups > 1;
-    fetch_weights(grp);
-    if constexpr (kCopyAhead) copy_activations(grp);
-    for (uint32_t ks = grp; ks < ksteps; ks += kGroups) {
-      const uint32_t s = ks % kStagesG;
+    fetch_weights(ks_first);
+    if constexpr (kCopyAhead) copy_activations(ks_first);
+    for (uint32_t ks = ks_first; ks < ksteps; ks += kGroups) {
+      const uint32_t s = (it_base + ks) % kStagesG;
       if constexpr (!kCopyAhead) copy_activations(ks);  // the copy flies while we dequantise
       const uint32_t a_tile = tiles + s * kStageBytes, b_tile = a_tile + kATileBytes;
       if constexpr (kInt8) {
@@ -312,8 +356,32 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
       if constexpr (kCopyAhead) copy_activations(ks + kGroups);
     }
     // ---------------- epilogue: accumulators -> out ----------------
-    wait_bounded(bars + 2 * kStagesG * 8, 0, abort_flag, p.status, 3);
+    it_base += ksteps;
+    wait_bounded(bars + 2 * kStagesG * 8, f & 1u, abort_flag, p.status, 3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // kOwner: the pairs after this one that hold pieces of the tile; their flags must be up
+    uint32_t partners = 0;
+    if (kind == kOwner) {
+      while (pair_index + partners + 1 < p.stream_pairs &&
+             static_cast<uint32_t>((pair_index + partners + 1) * units / p.stream_pairs) < tile_end_unit)
+        ++partners;
+      if (lane == 0) {
+        for (uint32_t q = 1; q <= partners; ++q) {
+          const unsigned int* flag = p.flags + (pair_index + q) * 2u + cta_rank;
+          uint32_t spins = 0, up = 0;
+          while (up == 0 && spins < kWaitLimit && !*abort_flag) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(up) : "l"(flag) : "memory");
+            ++spins;
+          }
+          if (up == 0 && !*abort_flag) {
+            *abort_flag = 1;
+            *reinterpret_cast<volatile int*>(p.status) = 6;
+          }
+        }
+      }
+      __syncwarp();
+    }
+    const size_t slot_floats = static_cast<size_t>(kBM) * kBN;
     // a warp may only touch the TMEM lane quarter warp % 4; the warps sharing a quarter split
     // the two accumulators (rows 0-127 / 128-255) and, with 16 producers, the column halves
     const uint32_t quarter = warp & 3u, group = warp >> 2;
@@ -347,9 +415,35 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
         *reinterpret_cast<float4*>(scratch + lane * 36u + j) =
             make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
       __syncwarp();
-      const bool final_sum = p.splits == 1;
+      const bool final_sum = kind == kFinal;
       const uint32_t col = col0 + lane;
-      if (col < p.n) {
+      if (kind == kPiece) {
+        // a piece of a tile: the whole 256 x 256 block of sums, no bias, into this CTA's slot
+        float* dst = p.slots + (pair_index * 2u + cta_rank) * slot_floats + (half * 128u + quarter * 32u) * kBN + cb * 32u + lane;
+        for (uint32_t rr = 0; rr < 32u; ++rr) dst[rr * kBN] = scratch[rr * 36u + lane];
+      } else if (kind == kOwner) {
+        if (col < p.n) {
+          const float b = p.bias[col];
+          const uint32_t row_first = row - lane;
+          const uint32_t rows_here = row_first < p.m ? min(32u, p.m - row_first) : 0u;
+          const float* piece = p.slots + ((pair_index + 1u) * 2u + cta_rank) * slot_floats + (half * 128u + quarter * 32u) * kBN + cb * 32u + lane;
+          // all of a piece's 32 loads are in flight together (one after the other, each row would
+          // cost a trip to memory); pieces are added in pair order
+          float sums[32];
+#pragma unroll
+          for (uint32_t rr = 0; rr < 32u; ++rr) sums[rr] = scratch[rr * 36u + lane];
+          for (uint32_t q = 0; q < partners; ++q) {
+            float piece_rows[32];
+#pragma unroll
+            for (uint32_t rr = 0; rr < 32u; ++rr) piece_rows[rr] = __ldcg(piece + q * 2u * slot_floats + rr * kBN);
+#pragma unroll
+            for (uint32_t rr = 0; rr < 32u; ++rr) sums[rr] += piece_rows[rr];
+          }
+#pragma unroll
+          for (uint32_t rr = 0; rr < 32u; ++rr)
+            if (rr < rows_here) p.out[static_cast<size_t>(row_first + rr) * p.n + col] = sums[rr] + b;
+        }
+      } else if (col < p.n) {
         const float b = final_sum ? p.bias[col] : 0.0f;
         const uint32_t row_first = row - lane;  // first row of this warp's 32
         float* dst = (final_sum ? p.out : p.partial + static_cast<size_t>(blockIdx.z) * p.m * p.n) + col;
@@ -358,11 +452,34 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
           dst[static_cast<size_t>(row_first + rr) * p.n] = scratch[rr * 36u + lane] + b;
       }
     }
+    if (streaming) {
+      // Every producer warp has drained its part of the accumulators and left its scratch (the
+      // stage buffers) before the next fragment starts; then one thread publishes the piece,
+      // lowers the flags it consumed, and tells the issuing CTA that TMEM may be overwritten.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"r"(kProducerWarps * 32) : "memory");
+      if (threadIdx.x == 0) {
+        if (kind == kPiece) {
+          __threadfence();
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.flags + pair_index * 2u + cta_rank), "r"(1u) : "memory");
+        } else if (kind == kOwner) {
+          for (uint32_t q = 1; q <= partners; ++q) p.flags[(pair_index + q) * 2u + cta_rank] = 0u;
+        }
+        if (f + 1 < frag_count) mbar_arrive_cluster(map_to_cta(tmem_free, 0));
+      }
+    }
+    }  // fragments
   } else if (cta_rank == 0) {
     // ---------------- MMA issuer ----------------
     constexpr uint32_t kIdesc = umma_idesc(kPair ? 256 : 128, kBN);
+    for (uint32_t f = 0; f < frag_count; ++f) {
+    select_fragment(f);
+    if (f != 0) {  // both CTAs have read the previous fragment's sums out of TMEM
+      wait_bounded_cluster(tmem_free, (f - 1u) & 1u, abort_flag, p.status, 7);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
     for (uint32_t ks = 0; ks < ksteps; ++ks) {
-      const uint32_t s = ks % kStagesG, phase = (ks / kStagesG) & 1u;
+      const uint32_t it = it_base + ks, s = it % kStagesG, phase = (it / kStagesG) & 1u;
       const bool ok = kPair ? wait_bounded_cluster(bars + s * 8, phase, abort_flag, p.status, 2)
                             : wait_bounded(bars + s * 8, phase, abort_flag, p.status, 2);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -401,6 +518,8 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p) {
       }
     }
     __syncwarp();
+    it_base += ksteps;
+    }  // fragments
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -477,9 +596,11 @@ cudaError_t launch_gemm_kernel(Kernel kernel, bool* configured, const dim3& grid
   kernel<<<grid, kGemmThreads, smem, stream>>>(p);
   return cudaGetLastError();
 }
+// `resident_pairs`, when given, receives how many pairs of this kernel the device holds at once
+// (0 if the query fails) and nothing is launched.
 template <typename Kernel>
 cudaError_t launch_pair_kernel(Kernel kernel, bool* configured, const dim3& grid, size_t smem, cudaStream_t stream,
-                               const GemmParams& p) {
+                               const GemmParams& p, int* resident_pairs = nullptr) {
   if (!*configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
@@ -497,6 +618,13 @@ cudaError_t launch_pair_kernel(Kernel kernel, bool* configured, const dim3& grid
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (resident_pairs != nullptr) {
+    if (cudaOccupancyMaxActiveClusters(resident_pairs, kernel, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      *resident_pairs = 0;
+    }
+    return cudaSuccess;
+  }
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 }  // namespace
@@ -537,6 +665,46 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
   cudaError_t e;
   const bool f16 = w.scale_dtype == KQ_F16;
   if (pair) {
+    const int which = int8 ? (f16 ? 6 : 7) : (f16 ? 4 : 5);
+    auto launch = [&](const dim3& grid, int* resident) {
+      switch (which) {
+        case 4: return launch_pair_kernel(qgemm_i4_pair_kernel<true>, &configured[4], grid, smem, env.stream, p, resident);
+        case 5: return launch_pair_kernel(qgemm_i4_pair_kernel<false>, &configured[5], grid, smem, env.stream, p, resident);
+        case 6: return launch_pair_kernel(qgemm_i8_pair_kernel<true>, &configured[6], grid, smem, env.stream, p, resident);
+        default: return launch_pair_kernel(qgemm_i8_pair_kernel<false>, &configured[7], grid, smem, env.stream, p, resident);
+      }
+    };
+    // Streaming: as many pairs as the device holds at once, each given one contiguous run of
+    // (pair tile, k-step) units, so that no SM waits for a last, nearly empty wave of tiles.  The
+    // pieces of tiles that two pairs share go through the context's scratch and are added by the
+    // tile's first pair.  Taken when the last wave of whole tiles would leave 15 % or more of
+    // the machine's time unused and a run is at least one tile long (a tile then has at most
+    // two owners); measured slower than whole tiles otherwise.  A pure function of the shapes.
+    static int resident_pairs[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
+    if (resident_pairs[which] < 0) {
+      e = launch(dim3(2, 1, 1), &resident_pairs[which]);
+      if (e != cudaSuccess) return e;
+    }
+    const uint32_t pair_tiles = n_tiles * (m_tiles / 2);
+    const uint64_t all_units = static_cast<uint64_t>(pair_tiles) * ksteps_total;
+    const uint32_t stream_pairs = static_cast<uint32_t>(std::max(resident_pairs[which], 0));
+    const uint32_t waves = stream_pairs ? (pair_tiles + stream_pairs - 1) / stream_pairs : 0;
+    const bool unbalanced = stream_pairs >= 2 && pair_tiles > stream_pairs &&
+                            static_cast<uint64_t>(pair_tiles) * 100 <= static_cast<uint64_t>(waves) * stream_pairs * 85 &&
+                            all_units / stream_pairs >= ksteps_total;
+    const uint64_t slot_bytes = static_cast<uint64_t>(stream_pairs) * 2 * kBM * kBN * sizeof(float);
+    if (unbalanced && env.workspace != nullptr && slot_bytes <= env.workspace_bytes && env.counters != nullptr &&
+        stream_pairs * 2 <= env.counter_count && all_units < (1ull << 31)) {
+      p.splits = 1;
+      p.stream_pairs = stream_pairs;
+      p.pair_tiles = pair_tiles;
+      p.m_pairs = m_tiles / 2;
+      p.slots = static_cast<float*>(env.workspace);
+      p.flags = env.counters;
+      e = cudaMemsetAsync(p.flags, 0, stream_pairs * 2 * sizeof(unsigned int), env.stream);  // flags a failed launch may have left up
+      if (e != cudaSuccess) return e;
+      return launch(dim3(stream_pairs * 2, 1, 1), nullptr);
+    }
     // x walks m in whole pairs (a CTA past the last row computes on zero-filled rows and stores nothing), y walks n
     const dim3 grid(m_tiles, n_tiles, splits);
     if (int8)

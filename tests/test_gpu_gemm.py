@@ -282,3 +282,32 @@ def test_int8_weight_with_k_not_a_multiple_of_64_keeps_the_gemv_panels(gpu):
     rep = oracle.allclose(out.cpu().numpy(), ref, atol=1e-5, rtol=1e-3)
     assert rep["pass"], rep
     w.free()
+
+
+@pytest.mark.parametrize("storage", ["i4", "i8"])
+def test_streamed_tiles_agree_with_row_panels_on_every_output(gpu, storage):
+    """m = 2048, 4096 -> 14336 is the shape whose 224 pair tiles are dealt to the SM pairs as
+    contiguous runs of k-steps: 73 tiles are shared by two pairs and summed through scratch.
+    Every output is compared with the same product computed 256 rows at a time (one row tile
+    per call: whole tiles, no pairs, no pieces).  Only the order of the f32 additions differs."""
+    import torch
+    m, k, n = 2048, 4096, 14336
+    if storage == "i4":
+        data, scale = cases.synth_i4(n, k, seed=21)
+        w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    else:
+        data, scale = cases.synth_i8(n, k, seed=21)
+        w = gpu.upload_weight("i8", data, scale, (n, k))
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g)
+    whole = gpu.linear(x, w, bias)
+    panels = torch.empty_like(whole)
+    for r in range(0, m, 256):
+        gpu.linear(x[r:r + 256].contiguous(), w, bias, out=panels[r:r + 256])
+    gpu.sync()
+    assert bool(torch.isfinite(whole).all())
+    rms = float(panels.double().pow(2).mean().sqrt())
+    worst = float((whole - panels).abs().max())
+    assert worst <= 1e-4 * rms, (worst, rms)
+    w.free()
