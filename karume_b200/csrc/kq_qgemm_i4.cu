@@ -1,33 +1,51 @@
-// qgemm_i4 — the prefill kernel of libkq: out[m, n] = x[m, k] . W[n, k]^T + bias for large m,
-// bf16 activations, W in the tiled int4 / group-32 layout (kq_common.cuh).
+// qgemm_i4 — the prefill kernels of libkq: out[m, n] = x[m, k] . W[n, k]^T + bias for large m,
+// bf16 activations, W in the tiled int4 / group-32 or the tiled int8 layout (kq_common.cuh).
 //
-// Replaces the reference's large-M linear variants with in-kernel int4 dequant
+// Replaces the reference's large-M linear variants with in-kernel dequant
 // (linear:v2:f32:reg64x32r4x4w8:wi4g32 and reg128x128r8x8w16 —
 // packages/runtime/src/kernels/gemm-geometry.ts:243-267, kernel text
 // packages/runtime/tests/fixtures/wgsl/linear_wi4_v4.wgsl): the same "dequantise a weight
 // tile into shared memory, then contract" structure, on Blackwell's tensor cores.
 //
-//   CTA tile 256 (m) x 256 (n), k-step 64, three shared-memory stages.
-//   warps 0-7  producers.  Per k-step they copy the 256 x 64 bf16 activation tile and
-//              dequantise the 256 x 64 weight tile (16 chunks of the tiled layout, read with
-//              128-bit loads) into the canonical K-major 128-byte-swizzled layout that
-//              tcgen05.mma reads.  A dequantised element is RNE_bf16(fround((u - 8) * s)):
-//              the reference's single-rounding f32 value (kq::dequant_i4's rule, computed
-//              here with an exact integer-to-float trick instead of a conversion), rounded
-//              once more to the tensor core's input type.  After the epilogue they also
-//              drain the accumulators.
-//   warp 8     one elected thread issues tcgen05.mma (M 128 x N 256 x K 16, bf16 in, f32
+// One body, two forms.
+//
+// Single CTA (at most 256 activation rows):
+//   CTA tile 256 (m) x 256 (n), k-step 64, three shared-memory stages of 64 KB.
+//   warps 0-15 producers.  Per k-step they copy the 256 x 64 bf16 activation tile (cp.async,
+//              straight into the swizzled tile) and dequantise the 256 x 64 weight tile (16-row
+//              blocks of the tiled layout, read with 128-bit loads one k-step ahead) into the
+//              canonical K-major 128-byte-swizzled layout that tcgen05.mma reads.  A dequantised
+//              element is RNE_bf16(fround((u - 8) * s)) or RNE_bf16(fround(q * s)): the
+//              reference's single-rounding f32 value (kq::dequant_i4 / dequant_i8, computed
+//              with an exact integer-to-float trick instead of a conversion), rounded once
+//              more to the tensor core's input type.  After the main loop they drain the
+//              accumulators.
+//   warp 16    one elected thread issues tcgen05.mma (M 128 x N 256 x K 16, bf16 in, f32
 //              accumulate) — two per k16 slice, one per 128-row half of the tile, sharing
 //              the weight operand — and commits each stage back to the producers.
 //   TMEM       512 columns: two 128 x 256 f32 accumulators.
+//
+// CTA pair (more than 256 rows): a cluster of two CTAs = two consecutive 256-row tiles of the
+//   same 256 output channels runs ONE tcgen05.mma.cta_group::2 stream (M 256 = 128 rows of each
+//   CTA, N 256).  Each CTA keeps its own activation tile and accumulators and dequantises only
+//   HALF of the weight tile; the tensor cores read the other half from the peer's shared
+//   memory.  Stages are 48 KB, four of them.  The producers work as two groups of eight warps
+//   that fill alternate k-steps, and a group starts the activation copy of its next k-step as
+//   soon as it has handed the current stage over: the waits, fences and arrivals that end a
+//   step (each costs a memory round trip or more while loads are in flight) overlap the other
+//   group's arithmetic.  The CTA of cluster rank 0 issues the MMAs; the peer's producers
+//   arrive on its "full" barriers, and it commits each stage to both CTAs' "empty" barriers.
+//   Shapes whose last wave of tiles would idle the machine are streamed: one persistent pair
+//   per SM pair takes a contiguous run of (tile, k-step) units, and a tile cut between two
+//   pairs is summed through scratch by the pair that holds its first k-step.
 //
 // Parity contract (there is no bf16-compute variant in the reference): the result equals
 // the reference's math (f64-accumulate oracle) applied to the bf16 activations and to the
 // bf16-rounded dequantised weights, within atol 1e-5 + rtol 1e-3.
 //
-// Every mbarrier wait is bounded; a wait that gives up sets a status word and a CTA-wide
-// abort flag that makes all later waits return at once, so the kernel always reaches the
-// TMEM deallocation and exits.
+// Every mbarrier wait and every flag wait is bounded; a wait that gives up sets a status word
+// and a CTA-wide abort flag that makes all later waits return at once, so the kernel always
+// reaches the TMEM deallocation and exits.
 #include <cuda_bf16.h>
 
 #include <type_traits>
