@@ -65,6 +65,9 @@ constexpr int kBM = 256, kBN = 256, kBK = 64, kStagesG = 3;
 #define KQ_GEMM_PRODUCER_WARPS 16
 #endif
 constexpr int kProducerWarps = KQ_GEMM_PRODUCER_WARPS;  // 8 or 16
+#ifndef KQ_GEMM_PAIR_STAGES
+#define KQ_GEMM_PAIR_STAGES 4  // 2 .. 4 (four stages of 48 KB fill the shared memory)
+#endif
 constexpr int kGemmThreads = kProducerWarps * 32 + 32;
 constexpr uint32_t kATileBytes = kBM * kBK * 2;  // 32 KB
 constexpr uint32_t kBTileBytes = kBN * kBK * 2;  // 32 KB
@@ -133,7 +136,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p, const CUtensorMa
   constexpr int kAPiecesPerThread = 2048 / (kGW * 32);
   constexpr uint32_t kScaleBytes = kScaleF16 ? 2u : 4u;
   constexpr uint32_t kCB = kChunkWeightBytes + 32u * kScaleBytes;
-  constexpr int kStagesG = kPair ? 4 : kq::kStagesG;  // a pair's stage is 48 KB instead of 64
+  constexpr int kStagesG = kPair ? KQ_GEMM_PAIR_STAGES : kq::kStagesG;  // a pair's stage is 48 KB instead of 64
   constexpr uint32_t kStageBytes = kATileBytes + (kPair ? kBTileBytes / 2 : kBTileBytes);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
