@@ -311,3 +311,29 @@ def test_streamed_tiles_agree_with_row_panels_on_every_output(gpu, storage):
     worst = float((whole - panels).abs().max())
     assert worst <= 1e-4 * rms, (worst, rms)
     w.free()
+
+
+def test_streamed_gemm_replays_from_a_graph_with_the_same_bits(gpu):
+    """The streamed launch is a memset of its flags, the kernel and nothing else: recorded into a
+    CUDA graph and replayed twice, it gives the bits of the eager call."""
+    import torch
+    m, k, n = 2048, 4096, 14336
+    data, scale = cases.synth_i4(n, k, seed=33)
+    w = gpu.upload_weight("i4", data, scale, (n, k), 32)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g)
+    eager = gpu.linear(x, w, bias)
+    gpu.sync()
+    out = torch.full((m, n), float("nan"), device="cuda")
+    gpu.graph_begin()
+    gpu.linear(x, w, bias, out=out)
+    graph = gpu.graph_end()
+    for _ in range(2):
+        out.fill_(float("nan"))
+        gpu.sync()
+        gpu.graph_launch(graph)
+        gpu.sync()
+        assert torch.equal(out, eager)
+    gpu.graph_free(graph)
+    w.free()
