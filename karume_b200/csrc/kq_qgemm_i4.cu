@@ -124,9 +124,10 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint2 v) {
 template <bool kInt8, bool kScaleF16, bool kPair, int kGroups>
 __device__ __forceinline__ void qgemm_body(const GemmParams& p, const CUtensorMap* x_map) {
   // Pair form, int4 weights: a stage's activation tile is ONE tensor-map copy (TMA, 128-byte
-  // swizzle, rows past m filled with zeros) started by one thread of the filling group and tracked
-  // by a barrier of its own.  The other forms copy 16-byte pieces with cp.async (with int8
-  // weights the tensor-map copy measured 5 % slower, with int4 weights equal or 1 % faster).
+  // swizzle, rows past m filled with zeros) started by one thread of the filling group; both
+  // CTAs' copies report their bytes straight to the issuing CTA's "full" barrier.  The other
+  // forms copy 16-byte pieces with cp.async (with int8 weights the tensor-map copy measured
+  // 5-6 % slower, twice; with int4 weights 1-6 % faster).
   constexpr bool kTmaA = kPair && !kInt8;
   static_assert(!kPair || (kProducerWarps == 16 && kGroups == 2), "the pair form: two groups of 8 warps");
   // The producer warps work in kGroups groups, group j filling the stages of k-steps j, j + kGroups, ...:
@@ -186,18 +187,15 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p, const CUtensorMa
     }
   };
   const uint32_t tmem_free = bars + 72;  // pair form: both CTAs have drained the accumulators of a fragment
-  const uint32_t a_ready = bars + 128;   // pair form, [stage]: the activation tile's bytes have landed
 
   if (warp == kProducerWarps) {
     if (lane == 0) {
       for (int s = 0; s < kStagesG; ++s) {
-        mbar_init(bars + s * 8, (kPair ? 2 : 1) * kGW * 32);  // full: every thread of the filling group (of both CTAs) arrives
+        mbar_init(bars + s * 8, (kPair ? 2 : 1) * kGW * 32 + (kTmaA ? 1 : 0));  // full: every thread of the filling group (of both CTAs) arrives; + the tensor copies' bytes
         mbar_init(bars + (kStagesG + s) * 8, 1);       // empty: one tcgen05.commit
       }
       mbar_init(bars + 2 * kStagesG * 8, 1);           // accumulators complete
       mbar_init(tmem_free, kPair ? 2 : 1);
-      if constexpr (kTmaA)
-        for (int s = 0; s < kStagesG; ++s) mbar_init(a_ready + s * 8, 1);  // the issuing thread's arrive + the bytes
       *abort_flag = 0;
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -301,10 +299,15 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p, const CUtensorMa
         const uint32_t a_tile = tiles + s * kStageBytes;
         if constexpr (kTmaA) {
           if (tid == 0) {
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a_ready + s * 8), "r"(kATileBytes) : "memory");
+            // Both CTAs' copies report their bytes to the issuing CTA's "full" barrier (the
+            // cta_group::2 form of the copy may signal a barrier of the peer CTA), which that CTA
+            // arms for the two tiles: no thread has to wait for the tile and vouch for it.
+            const uint32_t full_bar = map_to_cta(bars + s * 8, 0);
+            if (cta_rank == 0)
+              asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bars + s * 8), "r"(2u * kATileBytes) : "memory");
             asm volatile(
-                "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                ::"r"(a_tile), "l"(x_map), "r"((ks_begin + ks) * kBK), "r"(m0), "r"(a_ready + s * 8)
+                "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                ::"r"(a_tile), "l"(x_map), "r"((ks_begin + ks) * kBK), "r"(m0), "r"(full_bar)
                 : "memory");
           }
         } else {
@@ -389,11 +392,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p, const CUtensorMa
         sts128(b_tile + swz(r_b, odd ? t : 4u + t), odd ? b0 : b1);
       }
       }
-      if constexpr (kTmaA) {  // one thread vouches for the activation tile with its arrival
-        if (tid == 0) wait_bounded(a_ready + s * 8, ((it_base + ks) / kStagesG) & 1u, abort_flag, p.status, 8);
-      } else {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-      }
+      if constexpr (!kTmaA) asm volatile("cp.async.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
       if (kPair && cta_rank != 0) mbar_arrive_cluster(map_to_cta(bars + s * 8, 0));  // the issuing CTA's barrier
       else mbar_arrive(bars + s * 8);
