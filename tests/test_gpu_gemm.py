@@ -284,14 +284,14 @@ def test_int8_weight_with_k_not_a_multiple_of_64_keeps_the_gemv_panels(gpu):
     w.free()
 
 
-@pytest.mark.parametrize("storage", ["i4", "i8"])
-def test_streamed_tiles_agree_with_row_panels_on_every_output(gpu, storage):
+@pytest.mark.parametrize("storage,k", [("i4", 4096), ("i8", 4096), ("i4", 192), ("i4", 64)])
+def test_streamed_tiles_agree_with_row_panels_on_every_output(gpu, storage, k):
     """m = 2048, 4096 -> 14336 is the shape whose 224 pair tiles are dealt to the SM pairs as
     contiguous runs of k-steps: 73 tiles are shared by two pairs and summed through scratch.
     Every output is compared with the same product computed 256 rows at a time (one row tile
     per call: whole tiles, no pairs, no pieces).  Only the order of the f32 additions differs."""
     import torch
-    m, k, n = 2048, 4096, 14336
+    m, n = 2048, 14336  # k = 192 and 64: runs of a few k-steps, tiles of three and of one
     if storage == "i4":
         data, scale = cases.synth_i4(n, k, seed=21)
         w = gpu.upload_weight("i4", data, scale, (n, k), 32)
