@@ -22,7 +22,7 @@ OUT = os.path.join(HERE, "libkq.so")
 
 SOURCES = ["kq_api.cu", "kq_generic.cu", "kq_qgemv_i4.cu", "kq_qgemv_i4_tc.cu", "kq_plan.cu", "kq_qgemm_i4.cu", "kq_qgemm_i4_x32.cu", "kq_qgemv_i8.cu",
            "kq_comm.cu", "kq_idot.cu", "kq_fused_ops.cu", "kq_container.cu"]
-HEADERS = ["kq_common.cuh", "kq_gemv_core.cuh", "kq_umma.cuh", "kq_internal.h", os.path.join("..", "..", "include", "kq.h")]
+HEADERS = ["kq_common.cuh", "kq_gemv_core.cuh", "kq_umma.cuh", "kq_gemm_stream.h", "kq_internal.h", os.path.join("..", "..", "include", "kq.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -52,6 +52,7 @@
 #include <type_traits>
 
 #include "kq_common.cuh"
+#include "kq_gemm_stream.h"
 #include "kq_umma.cuh"
 #include "kq_internal.h"
 
@@ -157,26 +158,25 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p, const CUtensorMa
   const bool streaming = kPair && p.stream_pairs != 0;
   const uint32_t pair_index = blockIdx.x >> 1;
   const uint64_t units = static_cast<uint64_t>(p.pair_tiles) * ksteps_all;
-  uint32_t unit_begin = 0, unit_end = 0, first_tile = 0, frag_count = 1;
+  uint32_t unit_begin = 0, unit_end = 0, frag_count = 1;
   if (streaming) {
-    unit_begin = static_cast<uint32_t>(pair_index * units / p.stream_pairs);
-    unit_end = static_cast<uint32_t>((pair_index + 1) * units / p.stream_pairs);
-    first_tile = unit_begin / ksteps_all;
-    frag_count = unit_end > unit_begin ? (unit_end - 1) / ksteps_all - first_tile + 1 : 0;
+    unit_begin = stream::run_begin(pair_index, units, p.stream_pairs);
+    unit_end = stream::run_begin(pair_index + 1, units, p.stream_pairs);
+    frag_count = stream::fragment_count(unit_begin, unit_end, ksteps_all);
   }
-  enum : uint32_t { kFinal = 0, kSlice = 1, kPiece = 2, kOwner = 3 };
+  using stream::kFinal; using stream::kSlice; using stream::kPiece; using stream::kOwner;
   // the current fragment: tile origin, first k-step, k-steps, what happens to the sums, the unit
   // after the tile's last, and how many k-steps this CTA ran before (stages and phases count on)
   uint32_t n0 = 0, m0 = 0, ks_begin = 0, ksteps = 0, kind = kFinal, tile_end_unit = 0, it_base = 0;
   auto select_fragment = [&](uint32_t f) {
     if (streaming) {
-      const uint32_t t = first_tile + f, tile_unit = t * ksteps_all;
-      ks_begin = max(unit_begin, tile_unit) - tile_unit;
-      ksteps = min(unit_end, tile_unit + ksteps_all) - tile_unit - ks_begin;
-      tile_end_unit = tile_unit + ksteps_all;
-      n0 = (t / p.m_pairs) * kBN;
-      m0 = ((t % p.m_pairs) * 2u + cta_rank) * kBM;
-      kind = ks_begin != 0 ? kPiece : (ksteps < ksteps_all ? kOwner : kFinal);
+      const stream::Fragment fr = stream::fragment(unit_begin, unit_end, ksteps_all, f);
+      ks_begin = fr.ks_begin;
+      ksteps = fr.ksteps;
+      tile_end_unit = fr.tile_end_unit;
+      kind = fr.kind;
+      n0 = (fr.tile / p.m_pairs) * kBN;
+      m0 = ((fr.tile % p.m_pairs) * 2u + cta_rank) * kBM;
     } else {
       // a pair lies along x (the hardware pairs CTAs of consecutive cluster rank): there x walks m
       n0 = (kPair ? blockIdx.y : blockIdx.x) * kBN;
@@ -405,9 +405,7 @@ __device__ __forceinline__ void qgemm_body(const GemmParams& p, const CUtensorMa
     // kOwner: the pairs after this one that hold pieces of the tile; their flags must be up
     uint32_t partners = 0;
     if (kind == kOwner) {
-      while (pair_index + partners + 1 < p.stream_pairs &&
-             static_cast<uint32_t>((pair_index + partners + 1) * units / p.stream_pairs) < tile_end_unit)
-        ++partners;
+      partners = stream::partners(pair_index, tile_end_unit, units, p.stream_pairs);
       if (lane == 0) {
         for (uint32_t q = 1; q <= partners; ++q) {
           const unsigned int* flag = p.flags + (pair_index + q) * 2u + cta_rank;
@@ -761,15 +759,11 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
       if (e != cudaSuccess) return e;
     }
     const uint32_t pair_tiles = n_tiles * (m_tiles / 2);
-    const uint64_t all_units = static_cast<uint64_t>(pair_tiles) * ksteps_total;
     const uint32_t stream_pairs = static_cast<uint32_t>(std::max(resident_pairs[which], 0));
-    const uint32_t waves = stream_pairs ? (pair_tiles + stream_pairs - 1) / stream_pairs : 0;
-    const bool unbalanced = stream_pairs >= 2 && pair_tiles > stream_pairs &&
-                            static_cast<uint64_t>(pair_tiles) * 100 <= static_cast<uint64_t>(waves) * stream_pairs * 85 &&
-                            all_units / stream_pairs >= ksteps_total;
+    const bool unbalanced = stream::worth_streaming(pair_tiles, stream_pairs, ksteps_total);
     const uint64_t slot_bytes = static_cast<uint64_t>(stream_pairs) * 2 * kBM * kBN * sizeof(float);
     if (unbalanced && env.workspace != nullptr && slot_bytes <= env.workspace_bytes && env.counters != nullptr &&
-        stream_pairs * 2 <= env.counter_count && all_units < (1ull << 31)) {
+        stream_pairs * 2 <= env.counter_count) {
       p.splits = 1;
       p.stream_pairs = stream_pairs;
       p.pair_tiles = pair_tiles;
