@@ -731,7 +731,15 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
   p.splits = splits;
   p.ksteps_per_split = (ksteps_total + splits - 1) / splits;
   p.partial = static_cast<float*>(env.workspace);
-  static bool configured[8] = {false, false, false, false, false, false, false, false};
+  // What is remembered per kernel — the shared-memory attribute set, the pairs resident at once —
+  // is a property of the device the context runs on: one row per device.
+  constexpr int kMaxDevices = 64;
+  static bool configured_all[kMaxDevices][8] = {};
+  static int resident_all[kMaxDevices][8] = {};  // 0: not asked yet; -1: the query failed
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  bool* configured = configured_all[device];
+  int* resident_pairs = resident_all[device];
   cudaError_t e;
   const bool f16 = w.scale_dtype == KQ_F16;
   if (pair) {
@@ -753,10 +761,10 @@ cudaError_t launch_qgemm_i4(const LaunchEnv& env, const LinearTarget& target, co
     // tile's first pair.  Taken when the last wave of whole tiles would leave 15 % or more of
     // the machine's time unused and a run is at least one tile long (a tile then has at most
     // two owners); measured slower than whole tiles otherwise.  A pure function of the shapes.
-    static int resident_pairs[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
-    if (resident_pairs[which] < 0) {
+    if (resident_pairs[which] == 0) {
       e = launch(dim3(2, 1, 1), &resident_pairs[which]);
       if (e != cudaSuccess) return e;
+      if (resident_pairs[which] <= 0) resident_pairs[which] = -1;
     }
     const uint32_t pair_tiles = n_tiles * (m_tiles / 2);
     const uint32_t stream_pairs = static_cast<uint32_t>(std::max(resident_pairs[which], 0));
