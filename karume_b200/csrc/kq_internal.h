@@ -57,6 +57,20 @@ struct FusedCommDev {
   int* status;          // host-mapped: non-zero once a bounded wait gave up
 };
 
+// What a launcher remembers about a kernel — attributes set before its first launch, limits learnt
+// from the device — belongs to a device, not to the process: a host may drive several GPUs from
+// one process.  slot() is the entry of the calling thread's current device (nullptr if that
+// cannot be told).
+template <typename T, int kDevices = 64>
+struct PerDevice {
+  T value[kDevices] = {};
+  T* slot() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kDevices) return nullptr;
+    return &value[device];
+  }
+};
+
 struct LaunchEnv {
   cudaStream_t stream;
   bool overlap;          // programmatic dependent launch

@@ -389,19 +389,23 @@ cudaError_t launch_x32(const LaunchEnv& env, const LinearTarget& target, const X
     p.partial = partial;
     const dim3 grid((w.n + kXN - 1) / kXN, (pm + kXM - 1) / kXM, splits);
     if (w.scale_dtype == KQ_F16) {
-      static bool configured = false;
-      if (!configured) {
+      static PerDevice<bool> configured_on;
+      bool* configured = configured_on.slot();
+      if (configured == nullptr) return cudaErrorInvalidDevice;
+      if (!*configured) {
         e = cudaFuncSetAttribute(qgemm_i4_x32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        configured = true;
+        *configured = true;
       }
       qgemm_i4_x32_kernel<true><<<grid, kXThreads, smem, env.stream>>>(p);
     } else {
-      static bool configured = false;
-      if (!configured) {
+      static PerDevice<bool> configured_on;
+      bool* configured = configured_on.slot();
+      if (configured == nullptr) return cudaErrorInvalidDevice;
+      if (!*configured) {
         e = cudaFuncSetAttribute(qgemm_i4_x32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        configured = true;
+        *configured = true;
       }
       qgemm_i4_x32_kernel<false><<<grid, kXThreads, smem, env.stream>>>(p);
     }

@@ -706,11 +706,13 @@ uint32_t group_smem_bytes(uint32_t m) {
 template <typename XT, bool kScaleF16, int kCols, int kRB>
 cudaError_t launch_typed(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets) {
   auto kernel = qgemv_i4_kernel<XT, kScaleF16, kCols, kRB>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDevice<bool> configured_on;
+  bool* configured = configured_on.slot();
+  if (configured == nullptr) return cudaErrorInvalidDevice;
+  if (!*configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return e;
-    configured = true;
+    *configured = true;
   }
   constexpr uint32_t kTileRowsCta = kWarps * kRB * 16;
   uint32_t tiles = 0;
@@ -810,16 +812,20 @@ template <typename XT, bool kScaleF16, int kG, int kD>
 cudaError_t launch_typed_gp_depth(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets,
                                   bool probe_only, uint32_t* ctas_out, uint32_t* capacity_out) {
   auto kernel = qgemv_i4_gp_kernel<XT, kScaleF16, kG, kD>;
-  static bool configured = false;
-  static uint32_t max_cluster = kMaxCluster;
-  if (!configured) {
+  struct Setup { bool done; uint32_t max_cluster; };
+  static PerDevice<Setup> setup_on;
+  Setup* setup = setup_on.slot();
+  if (setup == nullptr) return cudaErrorInvalidDevice;
+  uint32_t& max_cluster = setup->max_cluster;
+  if (!setup->done) {
+    max_cluster = kMaxCluster;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return e;
     // few row tiles and a long k (8960 -> 1536): sixteen splits, the largest cluster the device
     // takes with this opt-in, halve each CTA's share again
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) max_cluster = 16;
     else (void)cudaGetLastError();
-    configured = true;
+    setup->done = true;
   }
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kCpg = 8 / kG, kCU = kG / 2;
@@ -1232,11 +1238,13 @@ template <typename XT, bool kScaleF16, int kTiles, int kRB, int kD>
 cudaError_t launch_typed_wide(const LaunchEnv& env, GemvParams& p, int count, const LinearTarget* targets,
                               int* extra_launches) {
   auto kernel = qgemv_i4_wide_kernel<XT, kScaleF16, kTiles, kRB, kD>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDevice<bool> configured_on;
+  bool* configured = configured_on.slot();
+  if (configured == nullptr) return cudaErrorInvalidDevice;
+  if (!*configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e != cudaSuccess) return e;
-    configured = true;
+    *configured = true;
   }
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kTileRowsCta = kWarps * kRB * 16;

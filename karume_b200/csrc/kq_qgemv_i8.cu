@@ -333,15 +333,19 @@ qgemv_i8_kernel(const Gemv8Params p) {
 template <typename XT, bool kScaleF16, int kCols, int kRB>
 cudaError_t launch_typed8(const LaunchEnv& env, Gemv8Params& p) {
   auto kernel = qgemv_i8_kernel<XT, kScaleF16, kCols, kRB>;
-  static bool configured = false;
-  static uint32_t max_cluster = kMaxCluster8;
-  if (!configured) {
+  struct Setup { bool done; uint32_t max_cluster; };
+  static PerDevice<Setup> setup_on;
+  Setup* setup = setup_on.slot();
+  if (setup == nullptr) return cudaErrorInvalidDevice;
+  uint32_t& max_cluster = setup->max_cluster;
+  if (!setup->done) {
+    max_cluster = kMaxCluster8;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return e;
     // few row tiles and a long k: sixteen splits (the largest cluster, by opt-in)
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) max_cluster = 16;
     else (void)cudaGetLastError();
-    configured = true;
+    setup->done = true;
   }
   constexpr bool kHasLo = !std::is_same<XT, __half>::value;
   constexpr uint32_t kTileRowsCta = kWarps8 * kRB * 16;
