@@ -4,7 +4,7 @@ The generators restate, in numpy, the input builders the reference's GPU tests u
 (packages/runtime/tests/helpers/graph.ts:80-96 `fill`,
  packages/runtime/tests/gpu_i4_weights_test.ts:34-45 `SIGNED` / `groupVarying`,
  packages/runtime/tests/helpers/i4.ts:43-85 `quantizeI4`,
- packages/runtime/tests/helpers/i8.ts:43-71 `quantizeI8`)
+ packages/runtime/tests/helpers/i8.ts:40-66 `quantizeI8`)
 so that the shapes and values a parity test runs are the reference's own cases.
 The encoders here are test-only: expected values always come from the oracle's
 DECODER, never from an encoder (the discipline stated in helpers/i8.ts:9-10).
