@@ -8,7 +8,7 @@ import re
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REFERENCE = os.environ.get("KQ_REFERENCE_TREE", "/root/reference")
+REFERENCE = os.environ.get("KQ_REFERENCE_TREE", os.path.join(os.path.dirname(ROOT), "reference"))  # a checkout beside this one
 CITATION = re.compile(r"((?:packages|docs|tools|scripts|apps)/[\w/.\-]+\.(?:ts|wgsl|md|json|py|js)):(\d+)(?:-(\d+))?")
 
 
