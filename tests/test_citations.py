@@ -1,5 +1,5 @@
-"""Every `path:line` or `path:first-last` citation of a reference file in the sources, headers,
-tests and documents names a file of the reference tree that has that many lines.  The
+"""Every `path:line` or `path:first-last` citation of a reference file in the sources, headers
+and tests names a file of the reference tree that has that many lines.  The
 reference tree is only present where the library is developed; elsewhere the test is skipped."""
 import glob
 import os
@@ -16,9 +16,8 @@ def cited_files():
     names = glob.glob(os.path.join(ROOT, "include", "*.h"))
     for sub in ("karume_b200", "oracle", "tests"):
         names += glob.glob(os.path.join(ROOT, sub, "**", "*.*"), recursive=True)
-    names += [os.path.join(ROOT, n) for n in ("DESIGN.md", "INTEGRATION.md", "README.md", "bench.py", "bench_workload.py",
-                                              "__graft_entry__.py")]
-    keep = (".h", ".cuh", ".cu", ".c", ".cpp", ".py", ".md")
+    names += glob.glob(os.path.join(ROOT, "*.py"))
+    keep = (".h", ".cuh", ".cu", ".c", ".cpp", ".py")
     return [n for n in names if os.path.isfile(n) and n.endswith(keep) and os.sep + "build" + os.sep not in n]
 
 
