@@ -189,6 +189,7 @@ def run_reference(args):
         "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "timed_steps": timed_steps,  # at most 10 (each is seconds of CPU work); ms_per_step is their mean
     }
     print(json.dumps(line))
 
